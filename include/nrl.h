@@ -1,0 +1,220 @@
+/* nrl — the token-level reinforcement-learning ops of noetic-tensor's `nn::rl`, fused for
+ * NVIDIA B200 (sm_100a), behind a C ABI.
+ *
+ * This header is what the noetic-tensor crate's hand-written FFI layer would declare beside its
+ * driver-API declarations (src/tensor/cuda/ffi.rs:30-63). The conventions are that file's:
+ *   - device pointers are `CUdeviceptr` values (uint64_t, src/tensor/cuda/ffi.rs:12), streams are
+ *     `CUstream` (void*, src/tensor/cuda/ffi.rs:14); argument blocks are plain `#[repr(C)]` structs
+ *     passed by pointer, with their size in the first field (the crate asserts its kernel
+ *     parameter structs' sizes the same way, src/tensor/cuda/backend.rs:1038-1043);
+ *   - every function returns an int: 0 on success, a positive value is a CUDA error code passed
+ *     through (the crate wraps results with `cu(r, what)`, src/tensor/cuda/mod.rs:140-153), a
+ *     negative value is one of NRL_E_* below; nothing throws, aborts or traps;
+ *   - the library allocates no device memory and frees none: inputs, outputs and scratch are the
+ *     caller's buffers (the crate allocates outputs from its stream-ordered pool,
+ *     src/tensor/cuda/backend.rs:245-264);
+ *   - work is enqueued on the caller's stream and the call returns without synchronising; the
+ *     device is the one whose context is current on the calling thread (the crate makes its
+ *     primary context current on entry, src/tensor/cuda/backend.rs:148-159);
+ *   - tensors are contiguous and row-major: logits `[rows, V]` with rows = S·B·T, as F32 or as
+ *     BF16 bit patterns (src/tensor/half.rs:16-27); tokens are I32 on the device (the crate
+ *     uploads gather indices as I32, src/tensor/gpu/mod.rs:355-357); masks are one byte per element
+ *     (src/tensor/gpu/mod.rs:39-40); every floating-point output is F32
+ *     (src/tensor/gpu/mod.rs:335-342).
+ *
+ * Everything is computed in f32 with f64 only in per-row finalisation; no atomics and a fixed
+ * reduction order, so results are bitwise identical from run to run on the same device.
+ */
+#ifndef NRL_H
+#define NRL_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef uint64_t nrl_devptr; /* CUdeviceptr */
+typedef void* nrl_stream;    /* CUstream */
+
+/* storage dtypes of logits */
+enum { NRL_F32 = 0, NRL_BF16 = 1 };
+
+/* error codes (negative); positive return values are cudaError_t / CUresult numbers */
+enum {
+    NRL_OK = 0,
+    NRL_E_BAD_ARG = -1,     /* null pointer, zero size, struct_size mismatch, misaligned pointer */
+    NRL_E_UNSUPPORTED = -2, /* dtype / option this build has no kernel for */
+    NRL_E_WORKSPACE = -3,   /* scratch buffer missing or too small */
+    NRL_E_ROW_STATUS = -4,  /* reported by nrl_check_status: a row had no allowed token or a NaN */
+    NRL_E_NO_DEVICE = -5    /* no CUDA device / no current context */
+};
+
+/* ---------------------------------------------------------------------------------------------
+ * Library identity.
+ * nrl_key replaces `CudaBackend::key` (src/tensor/cuda/backend.rs:962-966): a provenance string
+ * naming what results depend on, ending in the first 16 hex digits of the SHA-256 of the kernel
+ * sources. */
+int nrl_version(void);
+const char* nrl_key(void);
+const char* nrl_error_string(int code);
+/* Kernels launched by this library in this process so far (the crate's `launches()`,
+ * src/tensor/cuda/backend.rs:1032-1036). */
+uint64_t nrl_launch_count(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Row forward: one streaming pass over each vocabulary row.
+ *
+ * Replaces, for a `Device::Cuda` tensor, the op sequences of
+ *   tempered_logits      src/nn/rl.rs:475-486   (z = logits / temperature + additive mask)
+ *   sample_categorical   src/nn/rl.rs:510-529   (here: inverse CDF against one uniform per row,
+ *                                                or the first maximum when NRL_FWD_GREEDY)
+ *   token_log_probs      src/nn/rl.rs:134-141   (log_softmax(z)[token], src/tensor/activation.rs:30-35)
+ *   categorical_kl /     src/nn/rl.rs:327-351   (per-row exact KL(softmax z ‖ softmax z_ref), both
+ *   reference_kl                                 sides tempered and masked alike)
+ *   categorical_entropy  src/nn/rl.rs:405-414   (per-row entropy)
+ * and saves the per-row statistics the backward needs in place of log_softmax's saved output
+ * (src/tensor/autodiff.rs:110-119).
+ *
+ * Sampling: with z the tempered, masked logits of a row in f32, m = max z, e_v = exp(z_v − m),
+ * Z = Σ e_v, the token is min{k : Σ_{v≤k} e_v > u·Z} for the row's uniform u in [0, 1).
+ * A row with no allowed token or with a NaN gets token −1, NaN outputs and a non-zero status byte
+ * (bit 0: no allowed token; bit 1: NaN), where the reference panics (src/nn/rl.rs:516-519).
+ */
+enum {
+    NRL_FWD_SAMPLE = 1u << 0,  /* draw tokens (needs `uniforms`, writes `tokens`) */
+    NRL_FWD_GREEDY = 1u << 1,  /* tokens = first maximum of z (temperature 0); writes `tokens` */
+    NRL_FWD_TOKENS_IN = 1u << 2 /* `tokens` is an input (token_log_probs of given tokens) */
+};
+
+typedef struct nrl_row_fwd_args {
+    uint32_t struct_size;      /* sizeof(nrl_row_fwd_args) */
+    uint32_t flags;            /* NRL_FWD_* ; at most one of SAMPLE / GREEDY / TOKENS_IN */
+    uint32_t dtype;            /* dtype of `logits` and of `ref_logits` */
+    uint32_t V;                /* vocabulary size, ≥ 1 */
+    uint64_t rows;             /* S·B·T */
+    float temperature;         /* τ as f32; 1.0 leaves the logits as they are; must be > 0 */
+    uint32_t reserved0;
+    nrl_devptr logits;         /* [rows, V] */
+    nrl_devptr ref_logits;     /* [rows, V] or 0: frozen reference (detached) */
+    nrl_devptr allow_mask;     /* u8, non-zero = allowed; [rows, V], or [1, V] with stride 0; or 0 */
+    uint64_t allow_row_stride; /* elements between rows of allow_mask: V or 0 */
+    nrl_devptr add_mask;       /* f32 additive mask (−inf or −1e9 exclude), [rows, V] or [1, V]; or 0 */
+    uint64_t add_row_stride;   /* V or 0 */
+    nrl_devptr uniforms;       /* f32 [rows] in [0,1), for NRL_FWD_SAMPLE; else 0 */
+    nrl_devptr tokens;         /* i32 [rows]: output (SAMPLE, GREEDY) or input (TOKENS_IN); or 0 */
+    nrl_devptr logp;           /* out f32 [rows]: log-prob of the token under z; or 0 */
+    nrl_devptr ref_logp;       /* out f32 [rows]: log-prob of the token under z_ref; or 0 */
+    nrl_devptr kl;             /* out f32 [rows]: exact KL; or 0 */
+    nrl_devptr entropy;        /* out f32 [rows]; or 0 */
+    nrl_devptr rowstats;       /* out f32 [rows, 4] = (m, ln Z, m_ref, ln Z_ref) for nrl_row_bwd; or 0 */
+    nrl_devptr status;         /* out u8 [rows]; or 0 */
+    nrl_devptr workspace;      /* scratch, nrl_row_fwd_workspace_bytes(rows, V) bytes; may be 0 if that is 0 */
+    uint64_t workspace_bytes;
+} nrl_row_fwd_args;
+
+/* Scratch bytes nrl_row_fwd needs for this shape: 0 when every row gets a whole thread block,
+ * non-zero when few long rows are split over several blocks each. */
+uint64_t nrl_row_fwd_workspace_bytes(uint64_t rows, uint32_t V);
+int nrl_row_fwd(const nrl_row_fwd_args* args, nrl_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Row backward: d(logits) in one streaming pass.
+ *
+ * Replaces the tape's backward of the same functions (gather → scatter_add into a dense
+ * one-hot, src/tensor/float.rs:1004-1011, 1049-1054; log_softmax backward g − exp(y)·Σg,
+ * src/tensor/activation.rs:36-41; the exp / mul / mask_fill / sum_dim nodes of categorical_kl and
+ * categorical_entropy). With π = softmax(z), ρ = softmax(z_ref) and the per-row upstream
+ * gradients g_lp, g_kl, g_ent of the row's log-prob, KL and entropy:
+ *   dz_j = g_lp·(1[j = token] − π_j) + g_kl·π_j·(log π_j − log ρ_j − KL) − g_ent·π_j·(log π_j + H)
+ * and d(logits) = dz / temperature. Entries with π_j = 0 get exactly 0; rows whose three
+ * upstream gradients are all zero (unscored positions) are written as exact zeros without
+ * reading the logits.
+ */
+typedef struct nrl_row_bwd_args {
+    uint32_t struct_size;
+    uint32_t dtype;
+    uint32_t V;
+    float temperature;
+    uint64_t rows;
+    nrl_devptr logits;
+    nrl_devptr ref_logits; /* or 0 (then g_kl must be 0) */
+    nrl_devptr allow_mask;
+    uint64_t allow_row_stride;
+    nrl_devptr add_mask;
+    uint64_t add_row_stride;
+    nrl_devptr tokens;   /* i32 [rows], or 0 (then g_lp must be 0) */
+    nrl_devptr rowstats; /* f32 [rows, 4] from nrl_row_fwd */
+    nrl_devptr kl;       /* f32 [rows] from nrl_row_fwd, or 0 when g_kl is 0 */
+    nrl_devptr entropy;  /* f32 [rows] from nrl_row_fwd, or 0 when g_ent is 0 */
+    nrl_devptr g_logp;   /* f32 [rows] or 0 */
+    nrl_devptr g_kl;     /* f32 [rows] or 0 */
+    nrl_devptr g_ent;    /* f32 [rows] or 0 */
+    nrl_devptr d_logits; /* out f32 [rows, V] */
+} nrl_row_bwd_args;
+
+int nrl_row_bwd(const nrl_row_bwd_args* args, nrl_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Token-level losses over `[S, B, T]` values, forward and the derivative with respect to logp.
+ *
+ *   NRL_LOSS_PG   policy_gradient_loss  src/nn/rl.rs:228-235   l = −w·logp
+ *   NRL_LOSS_PPO  clipped_policy_loss   src/nn/rl.rs:265-287   with Clip (src/nn/rl.rs:160-198),
+ *                 log_ratio (:239-246), select_max (:124-129), the dual clip (:276-285)
+ *   NRL_LOSS_K1/K2/K3  kl_estimate      src/nn/rl.rs:380-400   δ = other − logp, optional clamp
+ * Unscored positions (mask 0) give exactly 0 and exactly zero derivative, by a select
+ * (zero_masked, src/nn/rl.rs:99-102). The derivative follows the tape's rules: clamps and
+ * selects pass no gradient where they are active (src/tensor/float.rs:578-594, 984-1000).
+ */
+enum { NRL_LOSS_PG = 0, NRL_LOSS_PPO = 1, NRL_LOSS_K1 = 2, NRL_LOSS_K2 = 3, NRL_LOSS_K3 = 4 };
+
+typedef struct nrl_token_loss_args {
+    uint32_t struct_size;
+    uint32_t kind;        /* NRL_LOSS_* */
+    uint64_t S, B, T;
+    nrl_devptr logp;      /* f32 [S,B,T] */
+    nrl_devptr other;     /* PPO: old log-probs; K1..K3: reference log-probs; PG: 0 */
+    nrl_devptr weights;   /* PG: weights; PPO: advantages; [S,B,T] or [S,B]; K*: 0 */
+    uint32_t weights_per_sequence; /* 1: weights are [S,B] */
+    uint32_t has_dual;
+    nrl_devptr mask;      /* f32 [S,B,T] of 0/1, or 0 (every position scored) */
+    double clip_low, clip_high; /* PPO: the ratio is clipped to [(f32)(1 − low), (f32)(1 + high)] */
+    double dual;          /* PPO: dual-clip constant c > 1, used when has_dual */
+    double clamp;         /* PPO: log-ratio clamp; K*: δ clamp; used when has_clamp */
+    uint32_t has_clamp;
+    uint32_t reserved0;
+    nrl_devptr loss;      /* out f32 [S,B,T], 0 at unscored positions; or 0 */
+    nrl_devptr upstream;  /* f32 [S,B,T] gradient of the per-token loss (from nrl_reduce_tokens_bwd), or 0 for ones */
+    nrl_devptr dloss_dlogp; /* out f32 [S,B,T] = upstream · d loss / d logp; or 0 */
+} nrl_token_loss_args;
+
+int nrl_token_loss(const nrl_token_loss_args* args, nrl_stream stream);
+
+/* clip_fraction (src/nn/rl.rs:293-317): per seed, the fraction of scored tokens whose gradient a
+ * bound of clipped_policy_loss removes. Same inputs as NRL_LOSS_PPO; out f32 [S]. */
+int nrl_clip_fraction(const nrl_token_loss_args* args, nrl_devptr out_fraction, nrl_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * TokenReduction (src/nn/rl.rs:36-55, reduce_tokens :69-86, per_sequence :88-92).
+ * `per` must already be zero at unscored positions (the losses above and nrl_mask_rows do that).
+ * Forward: out is [S] (SUM, TOKEN_MEAN, SEQUENCE_MEAN), [S,B] (PER_SEQUENCE) or a copy (NONE).
+ * Backward: d_per[s,b,t] from the upstream gradient of the reduced value, exactly 0 at unscored
+ * positions. Sums run in a fixed tree order.
+ */
+enum { NRL_REDUCE_NONE = 0, NRL_REDUCE_SUM = 1, NRL_REDUCE_TOKEN_MEAN = 2, NRL_REDUCE_PER_SEQUENCE = 3, NRL_REDUCE_SEQUENCE_MEAN = 4 };
+
+int nrl_reduce_tokens(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
+int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr mask, nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream);
+
+/* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
+int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
+
+/* Reads `status` (u8 [rows], device) back and returns NRL_E_ROW_STATUS with the first bad row in
+ * *first_bad_row if any byte is non-zero. Synchronises the stream: this is the host read the
+ * reference's sampler does (src/nn/rl.rs:516-519). */
+int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64_t* first_bad_row, uint32_t* bits);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NRL_H */

@@ -1,0 +1,61 @@
+"""Builds libnrl.so (the C-ABI CUDA library of include/nrl.h) in-tree with nvcc for sm_100a."""
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libnrl.so")
+SOURCES = ["nrl_api.cu"]
+HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_bwd.cuh", "token_ops.cuh"]
+INCLUDE = os.path.join(os.path.dirname(HERE), "include", "nrl.h")
+
+
+def source_hash():
+    """First 16 hex digits of the SHA-256 of the kernel sources (part of nrl_key())."""
+    h = hashlib.sha256()
+    for f in SOURCES + HEADERS:
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(fh.read())
+    with open(INCLUDE, "rb") as fh:
+        h.update(fh.read())
+    return h.hexdigest()[:16]
+
+
+def nvcc_path():
+    return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+
+
+def up_to_date():
+    if not os.path.exists(LIB):
+        return False
+    t = os.path.getmtime(LIB)
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [INCLUDE, os.path.abspath(__file__)]
+    return all(os.path.getmtime(d) <= t for d in deps)
+
+
+def build(force=False, verbose=False):
+    if not force and up_to_date():
+        return LIB
+    cmd = [
+        nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+        "--shared", "-Xcompiler", "-fPIC", "-cudart", "static", "--fmad=true",
+        f'-DNRL_SRC_HASH="{source_hash()}"',
+        "-o", LIB,
+    ] + [os.path.join(CSRC, s) for s in SOURCES]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("nvcc failed building libnrl.so")
+    if verbose:
+        sys.stderr.write(r.stderr)
+    return LIB
+
+
+if __name__ == "__main__":
+    build(force=True, verbose="-v" in sys.argv)
+    print(LIB)

@@ -1,0 +1,93 @@
+"""ctypes declarations of the C ABI in include/nrl.h, one to one.
+
+This module is the Python analogue of the `extern "C"` block the noetic-tensor crate would add to
+src/tensor/cuda/ffi.rs: structs are laid out exactly as the header's, functions take device
+pointers as integers and a stream handle. It raises if libnrl.so is missing: there is no CPU
+fallback.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libnrl.so")
+
+F32, BF16 = 0, 1
+FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN = 1, 2, 4
+LOSS_PG, LOSS_PPO, LOSS_K1, LOSS_K2, LOSS_K3 = range(5)
+REDUCE_NONE, REDUCE_SUM, REDUCE_TOKEN_MEAN, REDUCE_PER_SEQUENCE, REDUCE_SEQUENCE_MEAN = range(5)
+E_BAD_ARG, E_UNSUPPORTED, E_WORKSPACE, E_ROW_STATUS, E_NO_DEVICE = -1, -2, -3, -4, -5
+
+u32, u64, f32, f64, ptr = C.c_uint32, C.c_uint64, C.c_float, C.c_double, C.c_uint64
+
+
+class RowFwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("flags", u32), ("dtype", u32), ("V", u32), ("rows", u64), ("temperature", f32), ("reserved0", u32),
+        ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
+        ("uniforms", ptr), ("tokens", ptr), ("logp", ptr), ("ref_logp", ptr), ("kl", ptr), ("entropy", ptr), ("rowstats", ptr), ("status", ptr),
+        ("workspace", ptr), ("workspace_bytes", u64),
+    ]
+
+
+class RowBwdArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("dtype", u32), ("V", u32), ("temperature", f32), ("rows", u64),
+        ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
+        ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr),
+    ]
+
+
+class TokenLossArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("kind", u32), ("S", u64), ("B", u64), ("T", u64),
+        ("logp", ptr), ("other", ptr), ("weights", ptr), ("weights_per_sequence", u32), ("has_dual", u32), ("mask", ptr),
+        ("clip_low", f64), ("clip_high", f64), ("dual", f64), ("clamp", f64), ("has_clamp", u32), ("reserved0", u32),
+        ("loss", ptr), ("upstream", ptr), ("dloss_dlogp", ptr),
+    ]
+
+
+# every symbol include/nrl.h declares, with its signature
+SYMBOLS = {
+    "nrl_version": (C.c_int, []),
+    "nrl_key": (C.c_char_p, []),
+    "nrl_error_string": (C.c_char_p, [C.c_int]),
+    "nrl_launch_count": (u64, []),
+    "nrl_row_fwd_workspace_bytes": (u64, [u64, u32]),
+    "nrl_row_fwd": (C.c_int, [C.POINTER(RowFwdArgs), C.c_void_p]),
+    "nrl_row_bwd": (C.c_int, [C.POINTER(RowBwdArgs), C.c_void_p]),
+    "nrl_token_loss": (C.c_int, [C.POINTER(TokenLossArgs), C.c_void_p]),
+    "nrl_clip_fraction": (C.c_int, [C.POINTER(TokenLossArgs), ptr, C.c_void_p]),
+    "nrl_reduce_tokens": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_reduce_tokens_bwd": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_mask_rows": (C.c_int, [u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
+}
+
+_lib = None
+
+
+class NrlError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        msg = lib().nrl_error_string(code).decode() if _lib is not None else str(code)
+        super().__init__(f"{what}: {msg} ({code})")
+
+
+def lib():
+    """The loaded libnrl.so. Raises if it has not been built: there is no fallback path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m noetic_tensor_b200._build` (nvcc, sm_100a); there is no CPU fallback")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def check(code, what):
+    if code != 0:
+        raise NrlError(code, what)

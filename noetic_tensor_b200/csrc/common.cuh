@@ -1,0 +1,205 @@
+// Shared device helpers of the nrl kernels (sm_100a): 128-bit streaming loads, bf16 unpacking,
+// NaN-propagating maxima, the exponential used in the streaming loops and the online-softmax
+// partial that every level of the fixed reduction tree merges.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <float.h>
+#include <math.h>
+
+#include "../../include/nrl.h"
+
+namespace nrl {
+
+constexpr int kThreads = 512;              // threads per block of the row kernels
+constexpr int kWarps = kThreads / 32;      // 16 warps: each owns a contiguous part of the row
+constexpr int kVec = 8;                    // elements per thread per step (16 B of bf16)
+constexpr int kTile = 32 * kVec;           // elements one warp covers per step
+constexpr int kPartFloats = 8;             // floats per stored partial (m, S, W, D, mr, Sr, amax index, pad)
+constexpr float kLog2e = 1.4426950408889634f;
+#define NRL_NEG_INF (-__int_as_float(0x7f800000))
+
+// ---- loads that bypass L1 allocation: every input byte is read once ----------------------------
+__device__ __forceinline__ uint4 ldg_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg_stream8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+// streaming (evict-first) 16-byte store for gradients that are written once and not re-read here
+__device__ __forceinline__ void stg_stream16(void* p, float a, float b, float c, float d) {
+    asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// max that returns NaN if either input is NaN (the reference's maxima propagate NaN,
+// src/tensor/kernels.rs:184-209)
+__device__ __forceinline__ float fmax_nan(float a, float b) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
+// 2^x, hardware approximation (relative error about 2^-22)
+__device__ __forceinline__ float ex2_approx(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+
+// ---- the raw 8-element vector of one input stream ----------------------------------------------
+template <int DT>
+struct Raw;
+template <>
+struct Raw<NRL_BF16> {
+    uint4 q;
+    __device__ __forceinline__ void load(const void* base, uint64_t elem) { q = ldg_stream16((const uint16_t*)base + elem); }
+    __device__ __forceinline__ void load_scalar(const void* base, uint64_t elem, int n) {
+        const uint16_t* p = (const uint16_t*)base + elem;
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint32_t lo = (2 * i < n) ? (uint32_t)__ldg(p + 2 * i) : 0xff80u;
+            uint32_t hi = (2 * i + 1 < n) ? (uint32_t)__ldg(p + 2 * i + 1) : 0xff80u;
+            w[i] = lo | (hi << 16);
+        }
+        q = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    __device__ __forceinline__ void unpack(float z[8]) const {
+        z[0] = bf16_lo(q.x); z[1] = bf16_hi(q.x); z[2] = bf16_lo(q.y); z[3] = bf16_hi(q.y);
+        z[4] = bf16_lo(q.z); z[5] = bf16_hi(q.z); z[6] = bf16_lo(q.w); z[7] = bf16_hi(q.w);
+    }
+};
+template <>
+struct Raw<NRL_F32> {
+    uint4 a, b;
+    __device__ __forceinline__ void load(const void* base, uint64_t elem) {
+        a = ldg_stream16((const float*)base + elem);
+        b = ldg_stream16((const float*)base + elem + 4);
+    }
+    __device__ __forceinline__ void load_scalar(const void* base, uint64_t elem, int n) {
+        const float* p = (const float*)base + elem;
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) w[i] = (i < n) ? __float_as_uint(__ldg(p + i)) : 0xff800000u;
+        a = make_uint4(w[0], w[1], w[2], w[3]);
+        b = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    __device__ __forceinline__ void unpack(float z[8]) const {
+        z[0] = __uint_as_float(a.x); z[1] = __uint_as_float(a.y); z[2] = __uint_as_float(a.z); z[3] = __uint_as_float(a.w);
+        z[4] = __uint_as_float(b.x); z[5] = __uint_as_float(b.y); z[6] = __uint_as_float(b.z); z[7] = __uint_as_float(b.w);
+    }
+};
+
+// eight allow-mask bytes
+struct RawMask {
+    uint2 q;
+    __device__ __forceinline__ void load(const uint8_t* base, uint64_t elem) { q = ldg_stream8(base + elem); }
+    __device__ __forceinline__ void load_scalar(const uint8_t* base, uint64_t elem, int n) {
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            if (i < n) lo |= (uint32_t)__ldg(base + elem + i) << (8 * i);
+            if (i + 4 < n) hi |= (uint32_t)__ldg(base + elem + i + 4) << (8 * i);
+        }
+        q = make_uint2(lo, hi);
+    }
+    __device__ __forceinline__ bool allowed(int i) const { return (((i < 4 ? q.x : q.y) >> (8 * (i & 3))) & 0xffu) != 0u; }
+    __device__ __forceinline__ bool any() const { return (q.x | q.y) != 0u; }
+};
+
+// ---- online-softmax partial ---------------------------------------------------------------------
+// Over a set of elements with tempered logits z (policy) and zr (reference):
+//   m  = max z,  S = Σ exp(z − m),  W = Σ exp(z − m)·(z − m),  D = Σ exp(z − m)·(z − zr)
+//   mr = max zr, Sr = Σ exp(zr − mr)
+// An empty set is m = −inf, S = W = D = 0.
+struct Partial {
+    float m, S, W, D, mr, Sr;
+};
+
+__device__ __forceinline__ Partial partial_empty() {
+    Partial p;
+    p.m = NRL_NEG_INF; p.S = 0.f; p.W = 0.f; p.D = 0.f; p.mr = NRL_NEG_INF; p.Sr = 0.f;
+    return p;
+}
+
+// Move a partial to a larger (or NaN) maximum `mn`; exact when the maximum does not change.
+__device__ __forceinline__ void partial_rebase(float& m, float& S, float& W, float& D, float mn) {
+    if (m != mn) {
+        if (m == NRL_NEG_INF) {
+            S = 0.f; W = 0.f; D = 0.f;
+        } else {
+            float dm = m - mn;      // ≤ 0, or NaN
+            float c = expf(dm);     // accurate: rebasing happens a handful of times per row
+            W = c * (W + S * dm);
+            S = c * S;
+            D = c * D;
+        }
+        m = mn;
+    }
+}
+__device__ __forceinline__ void partial_rebase_ref(float& mr, float& Sr, float mn) {
+    if (mr != mn) {
+        Sr = (mr == NRL_NEG_INF) ? 0.f : Sr * expf(mr - mn);
+        mr = mn;
+    }
+}
+
+// a ⊕ b, used at every level of the fixed tree (lanes of a warp, then parts of a row)
+__device__ __forceinline__ Partial partial_merge(Partial a, const Partial& b) {
+    float mn = fmax_nan(a.m, b.m);
+    float bm = b.m, bS = b.S, bW = b.W, bD = b.D;
+    partial_rebase(a.m, a.S, a.W, a.D, mn);
+    partial_rebase(bm, bS, bW, bD, mn);
+    a.S = __fadd_rn(a.S, bS);
+    a.W = __fadd_rn(a.W, bW);
+    a.D = __fadd_rn(a.D, bD);
+    float mrn = fmax_nan(a.mr, b.mr);
+    float bmr = b.mr, bSr = b.Sr;
+    partial_rebase_ref(a.mr, a.Sr, mrn);
+    partial_rebase_ref(bmr, bSr, mrn);
+    a.Sr = __fadd_rn(a.Sr, bSr);
+    return a;
+}
+
+__device__ __forceinline__ Partial partial_shfl_xor(const Partial& p, int mask) {
+    Partial o;
+    o.m = __shfl_xor_sync(0xffffffffu, p.m, mask);
+    o.S = __shfl_xor_sync(0xffffffffu, p.S, mask);
+    o.W = __shfl_xor_sync(0xffffffffu, p.W, mask);
+    o.D = __shfl_xor_sync(0xffffffffu, p.D, mask);
+    o.mr = __shfl_xor_sync(0xffffffffu, p.mr, mask);
+    o.Sr = __shfl_xor_sync(0xffffffffu, p.Sr, mask);
+    return o;
+}
+
+// Butterfly over the 32 lanes in a fixed order; lane 0's result is the one used.
+__device__ __forceinline__ Partial partial_warp_reduce(Partial p) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        Partial o = partial_shfl_xor(p, s);
+        // the lower lane of each pair merges (own, other) and the upper (other, own): same operands
+        // in the same order, so both hold the same bits
+        bool low = (threadIdx.x & s) == 0;
+        p = low ? partial_merge(p, o) : partial_merge(o, p);
+    }
+    return p;
+}
+
+// inclusive scan of doubles over a warp, lower lanes first
+__device__ __forceinline__ double warp_scan_incl(double x, int lane) {
+#pragma unroll
+    for (int s = 1; s < 32; s <<= 1) {
+        double y = __shfl_up_sync(0xffffffffu, x, s);
+        if (lane >= s) x = y + x;
+    }
+    return x;
+}
+
+}  // namespace nrl

@@ -1,0 +1,317 @@
+// The C ABI of include/nrl.h: argument checking, kernel selection and launches. No allocation,
+// no synchronisation (except nrl_check_status, which is a host read by definition).
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "row_bwd.cuh"
+#include "row_fwd_kernels.cuh"
+#include "token_ops.cuh"
+
+#define NRL_STR2(x) #x
+#define NRL_STR(x) NRL_STR2(x)
+#ifndef NRL_SRC_HASH
+#define NRL_SRC_HASH "unknown"
+#endif
+
+using namespace nrl;
+
+static std::atomic<uint64_t> g_launches{0};
+
+static inline int cuda_rc(cudaError_t e) { return e == cudaSuccess ? NRL_OK : (int)e; }
+static inline int after_launch(int n = 1) {
+    g_launches.fetch_add((uint64_t)n, std::memory_order_relaxed);
+    return cuda_rc(cudaGetLastError());
+}
+
+extern "C" int nrl_version(void) { return 100; }
+
+extern "C" const char* nrl_key(void) {
+    // what results depend on: the target, the arithmetic options, the kernel sources
+    return "cuda-sm100a-nvcc" NRL_STR(__CUDACC_VER_MAJOR__) "." NRL_STR(__CUDACC_VER_MINOR__) "-nofastmath-ex2approx-nrl-" NRL_SRC_HASH;
+}
+
+extern "C" uint64_t nrl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+extern "C" const char* nrl_error_string(int code) {
+    switch (code) {
+        case NRL_OK: return "success";
+        case NRL_E_BAD_ARG: return "nrl: bad argument (null pointer, zero size, struct size mismatch or misaligned pointer)";
+        case NRL_E_UNSUPPORTED: return "nrl: unsupported dtype or option";
+        case NRL_E_WORKSPACE: return "nrl: scratch buffer missing or too small";
+        case NRL_E_ROW_STATUS: return "nrl: a row has no allowed token (every logit -inf) or a NaN";
+        case NRL_E_NO_DEVICE: return "nrl: no CUDA device or no current context";
+        default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "nrl: unknown error";
+    }
+}
+
+// ---- decomposition of the forward -------------------------------------------------------------
+
+// Blocks per row: 1 once there are at least two waves of rows; otherwise enough to reach that,
+// keeping at least 16 tiles (4096 elements) per block. A function of (rows, V) only.
+static uint32_t fwd_nsplit(uint64_t rows, uint32_t V) {
+    const uint64_t want = 2 * 148;
+    if (rows >= want) return 1;
+    uint32_t tiles = (V + kTile - 1) / kTile;
+    uint32_t max_split = tiles / 16;
+    if (max_split < 1) max_split = 1;
+    if (max_split > 16) max_split = 16;
+    uint64_t need = (want + rows - 1) / rows;
+    return (uint32_t)(need < max_split ? need : max_split);
+}
+
+extern "C" uint64_t nrl_row_fwd_workspace_bytes(uint64_t rows, uint32_t V) {
+    if (rows == 0 || V == 0) return 0;
+    uint32_t ns = fwd_nsplit(rows, V);
+    return ns == 1 ? 0 : rows * ns * kWarps * kPartFloats * sizeof(float);
+}
+
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+static int launch_fwd(const FwdParams& p, cudaStream_t st) {
+    if (p.nsplit == 1) {
+        row_fwd_fused<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)p.rows, kThreads, 0, st>>>(p);
+        return after_launch();
+    }
+    row_fwd_parts<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)(p.rows * p.nsplit), kThreads, 0, st>>>(p);
+    int rc = after_launch();
+    if (rc) return rc;
+    row_fwd_finish<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)p.rows, kThreads, 0, st>>>(p);
+    return after_launch();
+}
+
+// GENERAL = additive mask, temperature ≠ 1 or the scalar-load path; VEC = 16-byte loads.
+#define NRL_DISPATCH(FN, dt, ref, allow, general, vec, ...)                                                        \
+    do {                                                                                                           \
+        if (vec && !general) {                                                                                     \
+            if (dt == NRL_BF16) { if (ref) { if (allow) return FN<NRL_BF16, true, true, false, true>(__VA_ARGS__); else return FN<NRL_BF16, true, false, false, true>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_BF16, false, true, false, true>(__VA_ARGS__); else return FN<NRL_BF16, false, false, false, true>(__VA_ARGS__); } } \
+            else                { if (ref) { if (allow) return FN<NRL_F32, true, true, false, true>(__VA_ARGS__); else return FN<NRL_F32, true, false, false, true>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_F32, false, true, false, true>(__VA_ARGS__); else return FN<NRL_F32, false, false, false, true>(__VA_ARGS__); } } \
+        } else if (vec) {                                                                                          \
+            if (dt == NRL_BF16) { if (ref) { if (allow) return FN<NRL_BF16, true, true, true, true>(__VA_ARGS__); else return FN<NRL_BF16, true, false, true, true>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_BF16, false, true, true, true>(__VA_ARGS__); else return FN<NRL_BF16, false, false, true, true>(__VA_ARGS__); } } \
+            else                { if (ref) { if (allow) return FN<NRL_F32, true, true, true, true>(__VA_ARGS__); else return FN<NRL_F32, true, false, true, true>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_F32, false, true, true, true>(__VA_ARGS__); else return FN<NRL_F32, false, false, true, true>(__VA_ARGS__); } } \
+        } else {                                                                                                   \
+            if (dt == NRL_BF16) { if (ref) { if (allow) return FN<NRL_BF16, true, true, true, false>(__VA_ARGS__); else return FN<NRL_BF16, true, false, true, false>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_BF16, false, true, true, false>(__VA_ARGS__); else return FN<NRL_BF16, false, false, true, false>(__VA_ARGS__); } } \
+            else                { if (ref) { if (allow) return FN<NRL_F32, true, true, true, false>(__VA_ARGS__); else return FN<NRL_F32, true, false, true, false>(__VA_ARGS__); } \
+                                  else     { if (allow) return FN<NRL_F32, false, true, true, false>(__VA_ARGS__); else return FN<NRL_F32, false, false, true, false>(__VA_ARGS__); } } \
+        }                                                                                                          \
+    } while (0)
+
+static bool aligned16(uint64_t p) { return (p & 15u) == 0; }
+
+// Can every stream of this call use 16-byte (8-byte for the byte mask) vector loads?
+static bool can_vectorise(uint32_t V, uint64_t logits, uint64_t ref, uint64_t allow, uint64_t allow_stride, uint64_t add, uint64_t add_stride) {
+    if (V % kVec != 0) return false;
+    if (!aligned16(logits) || (ref && !aligned16(ref))) return false;
+    if (allow && ((allow & 7u) != 0 || allow_stride % kVec != 0)) return false;
+    if (add && (!aligned16(add) || add_stride % 4 != 0)) return false;
+    return true;
+}
+
+static int fill_fwd_params(FwdParams& p, uint32_t dtype, uint32_t V, uint64_t rows, float tau, uint64_t logits, uint64_t ref, uint64_t allow, uint64_t allow_stride,
+                           uint64_t add, uint64_t add_stride) {
+    if (rows == 0 || V == 0 || !logits) return NRL_E_BAD_ARG;
+    if (dtype != NRL_F32 && dtype != NRL_BF16) return NRL_E_UNSUPPORTED;
+    if (!(tau > 0.f) || !isfinite(tau)) return NRL_E_BAD_ARG;
+    if (allow && allow_stride != 0 && allow_stride != V) return NRL_E_BAD_ARG;
+    if (add && add_stride != 0 && add_stride != V) return NRL_E_BAD_ARG;
+    if ((logits & (dtype == NRL_F32 ? 3u : 1u)) || (ref & (dtype == NRL_F32 ? 3u : 1u)) || (add & 3u)) return NRL_E_BAD_ARG;
+    memset(&p, 0, sizeof p);
+    p.logits = (const void*)logits;
+    p.ref = (const void*)ref;
+    p.allow = (const uint8_t*)allow;
+    p.add = (const float*)add;
+    p.rows = rows;
+    p.allow_stride = allow_stride;
+    p.add_stride = add_stride;
+    p.V = V;
+    p.tau = tau;
+    p.nsplit = 1;
+    p.tiles_per_block = (V + kTile - 1) / kTile;
+    return NRL_OK;
+}
+
+static int dispatch_fwd(const FwdParams& p, uint32_t dt, bool ref, bool allow, bool general, bool vec, cudaStream_t st) {
+    NRL_DISPATCH(launch_fwd, dt, ref, allow, general, vec, p, st);
+    return NRL_E_UNSUPPORTED;
+}
+
+extern "C" int nrl_row_fwd(const nrl_row_fwd_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_row_fwd_args)) return NRL_E_BAD_ARG;
+    FwdParams p;
+    int rc = fill_fwd_params(p, a->dtype, a->V, a->rows, a->temperature, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    if (rc) return rc;
+    uint32_t mode = a->flags & (NRL_FWD_SAMPLE | NRL_FWD_GREEDY | NRL_FWD_TOKENS_IN);
+    if (mode & (mode - 1)) return NRL_E_BAD_ARG;  // more than one mode
+    if (a->flags & ~(uint32_t)(NRL_FWD_SAMPLE | NRL_FWD_GREEDY | NRL_FWD_TOKENS_IN)) return NRL_E_BAD_ARG;
+    if ((mode & NRL_FWD_SAMPLE) && !a->uniforms) return NRL_E_BAD_ARG;
+    if (mode && !a->tokens) return NRL_E_BAD_ARG;
+    if (!mode && (a->logp || a->ref_logp)) return NRL_E_BAD_ARG;  // log-prob of which token?
+    if ((a->kl || a->ref_logp) && !a->ref_logits) return NRL_E_BAD_ARG;
+    if (a->rowstats & 15u) return NRL_E_BAD_ARG;
+    if (a->rows * (uint64_t)16 > 0x7fffffffull) return NRL_E_UNSUPPORTED;  // grid size; callers slice along S
+    p.uniforms = (const float*)a->uniforms;
+    p.tokens = (int32_t*)a->tokens;
+    p.logp = (float*)a->logp;
+    p.ref_logp = (float*)a->ref_logp;
+    p.kl = (float*)a->kl;
+    p.entropy = (float*)a->entropy;
+    p.rowstats = (float*)a->rowstats;
+    p.status = (uint8_t*)a->status;
+    p.flags = a->flags;
+    p.nsplit = fwd_nsplit(a->rows, a->V);
+    if (p.nsplit > 1) {
+        uint64_t need = nrl_row_fwd_workspace_bytes(a->rows, a->V);
+        if (!a->workspace || a->workspace_bytes < need || (a->workspace & 15u)) return NRL_E_WORKSPACE;
+        p.parts = (float*)a->workspace;
+        uint32_t tiles = (a->V + kTile - 1) / kTile;
+        p.tiles_per_block = (tiles + p.nsplit - 1) / p.nsplit;
+    }
+    bool vec = can_vectorise(a->V, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    bool general = !vec || a->add_mask != 0 || a->temperature != 1.0f;
+    return dispatch_fwd(p, a->dtype, a->ref_logits != 0, a->allow_mask != 0, general, vec, (cudaStream_t)stream);
+}
+
+// ---- backward ------------------------------------------------------------------------------------
+
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+static int launch_bwd(const BwdParams& p, cudaStream_t st) {
+    row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)(p.in.rows * p.chunks_per_row), kBwdThreads, 0, st>>>(p);
+    return after_launch();
+}
+
+static int dispatch_bwd(const BwdParams& p, uint32_t dt, bool ref, bool allow, bool general, bool vec, cudaStream_t st) {
+    NRL_DISPATCH(launch_bwd, dt, ref, allow, general, vec, p, st);
+    return NRL_E_UNSUPPORTED;
+}
+
+extern "C" int nrl_row_bwd(const nrl_row_bwd_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_row_bwd_args)) return NRL_E_BAD_ARG;
+    BwdParams p;
+    memset(&p, 0, sizeof p);
+    int rc = fill_fwd_params(p.in, a->dtype, a->V, a->rows, a->temperature, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    if (rc) return rc;
+    if (!a->d_logits || !a->rowstats || (a->rowstats & 15u) || (a->d_logits & 3u)) return NRL_E_BAD_ARG;
+    if (a->g_logp && !a->tokens) return NRL_E_BAD_ARG;
+    if (a->g_kl && (!a->ref_logits || !a->kl)) return NRL_E_BAD_ARG;
+    if (a->g_ent && !a->entropy) return NRL_E_BAD_ARG;
+    p.tokens = (const int32_t*)a->tokens;
+    p.rowstats = (const float*)a->rowstats;
+    p.kl = (const float*)a->kl;
+    p.entropy = (const float*)a->entropy;
+    p.g_logp = (const float*)a->g_logp;
+    p.g_kl = (const float*)a->g_kl;
+    p.g_ent = (const float*)a->g_ent;
+    p.d_logits = (float*)a->d_logits;
+    // blocks per row: about 16K elements each, so short rows are one block and long rows spread out
+    uint32_t chunks = (a->V + 16383) / 16384;
+    if (chunks < 1) chunks = 1;
+    p.chunks_per_row = chunks;
+    if (a->rows * (uint64_t)chunks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    bool vec = can_vectorise(a->V, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    bool general = !vec || a->add_mask != 0 || a->temperature != 1.0f;
+    // without an upstream KL gradient the reference stream is not read at all
+    bool ref = a->ref_logits != 0 && a->g_kl != 0;
+    return dispatch_bwd(p, a->dtype, ref, a->allow_mask != 0, general, vec, (cudaStream_t)stream);
+}
+
+// ---- token-level ---------------------------------------------------------------------------------
+
+static int fill_tok(TokParams& p, const nrl_token_loss_args* a) {
+    if (!a || a->struct_size != sizeof(nrl_token_loss_args)) return NRL_E_BAD_ARG;
+    if (a->S == 0 || a->B == 0 || a->T == 0 || !a->logp) return NRL_E_BAD_ARG;
+    if (a->kind > NRL_LOSS_K3) return NRL_E_UNSUPPORTED;
+    bool needs_w = a->kind == NRL_LOSS_PG || a->kind == NRL_LOSS_PPO;
+    bool needs_o = a->kind != NRL_LOSS_PG;
+    if ((needs_w && !a->weights) || (needs_o && !a->other)) return NRL_E_BAD_ARG;
+    if (a->kind == NRL_LOSS_PPO) {
+        // Clip::check (src/nn/rl.rs:189-197)
+        if (!(a->clip_low >= 0.0 && a->clip_low < 1.0 && a->clip_high >= 0.0) || !isfinite(a->clip_low) || !isfinite(a->clip_high)) return NRL_E_BAD_ARG;
+        if (a->has_dual && !(a->dual > 1.0 && isfinite(a->dual))) return NRL_E_BAD_ARG;
+    }
+    if (a->has_clamp && !(a->clamp > 0.0)) return NRL_E_BAD_ARG;
+    memset(&p, 0, sizeof p);
+    p.logp = (const float*)a->logp;
+    p.other = (const float*)a->other;
+    p.weights = (const float*)a->weights;
+    p.mask = (const float*)a->mask;
+    p.loss = (float*)a->loss;
+    p.upstream = (const float*)a->upstream;
+    p.dloss = (float*)a->dloss_dlogp;
+    p.n = a->S * a->B * a->T;
+    p.T = a->T;
+    p.kind = a->kind;
+    p.w_per_seq = a->weights_per_sequence;
+    p.has_dual = a->has_dual;
+    p.has_clamp = a->has_clamp;
+    p.ratio_lo = (float)(1.0 - a->clip_low);
+    p.ratio_hi = (float)(1.0 + a->clip_high);
+    p.neg_dual = (float)(-a->dual);
+    p.clamp = (float)a->clamp;
+    return NRL_OK;
+}
+
+extern "C" int nrl_token_loss(const nrl_token_loss_args* a, nrl_stream stream) {
+    TokParams p;
+    int rc = fill_tok(p, a);
+    if (rc) return rc;
+    uint64_t blocks = (p.n + 255) / 256;
+    if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    token_loss_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    return after_launch();
+}
+
+extern "C" int nrl_clip_fraction(const nrl_token_loss_args* a, nrl_devptr out, nrl_stream stream) {
+    TokParams p;
+    int rc = fill_tok(p, a);
+    if (rc) return rc;
+    if (a->kind != NRL_LOSS_PPO || !out) return NRL_E_BAD_ARG;
+    clip_fraction_kernel<<<(unsigned)a->S, kRedThreads, 0, (cudaStream_t)stream>>>(p, a->B * a->T, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_reduce_tokens(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr out, nrl_stream stream) {
+    if (S == 0 || B == 0 || T == 0 || !per || !out || reduction > NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_BAD_ARG;
+    if (reduction == NRL_REDUCE_NONE) {
+        if (per == out) return NRL_OK;
+        return cuda_rc(cudaMemcpyAsync((void*)out, (const void*)per, S * B * T * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    }
+    reduce_tokens_kernel<<<(unsigned)S, kRedThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)per, (const float*)mask, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr mask, nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream) {
+    if (S == 0 || B == 0 || T == 0 || !g_out || !d_per || reduction > NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_BAD_ARG;
+    reduce_tokens_bwd_kernel<<<(unsigned)S, kRedThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)mask, (const float*)g_out, (float*)d_per);
+    return after_launch();
+}
+
+extern "C" int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream) {
+    if (n == 0 || !x || !out) return NRL_E_BAD_ARG;
+    mask_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, (const float*)x, (const float*)mask, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64_t* first_bad_row, uint32_t* bits) {
+    if (!status || rows == 0) return NRL_E_BAD_ARG;
+    uint8_t* host = (uint8_t*)malloc(rows);
+    if (!host) return NRL_E_BAD_ARG;
+    cudaError_t e = cudaMemcpyAsync(host, (const void*)status, rows, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    int rc = cuda_rc(e);
+    if (!rc) {
+        for (uint64_t i = 0; i < rows; i++)
+            if (host[i]) {
+                if (first_bad_row) *first_bad_row = i;
+                if (bits) *bits = host[i];
+                rc = NRL_E_ROW_STATUS;
+                break;
+            }
+    }
+    free(host);
+    return rc;
+}

@@ -1,0 +1,93 @@
+// Row backward: d(logits) [rows, V] f32 in one streaming pass from the logits and the per-row
+// statistics the forward saved. Purely element-wise given those statistics, so there is no
+// reduction here and nothing to order; the pass is bound by the 4-byte-per-element write.
+#pragma once
+#include "row_fwd.cuh"
+
+namespace nrl {
+
+struct BwdParams {
+    FwdParams in;  // logits / ref / masks / V / rows / tau (the forward's view of the inputs)
+    const int32_t* tokens;
+    const float* rowstats;
+    const float* kl;
+    const float* entropy;
+    const float* g_logp;
+    const float* g_kl;
+    const float* g_ent;
+    float* d_logits;
+    uint32_t chunks_per_row;  // blocks per row
+};
+
+constexpr int kBwdThreads = 256;
+
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+__global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
+    const FwdParams& f = p.in;
+    const uint64_t row = blockIdx.x / p.chunks_per_row;
+    const uint32_t chunk = blockIdx.x % p.chunks_per_row;
+    const uint32_t V = f.V;
+    // this block's range of the row, in whole vectors
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    const uint32_t vec_per = (nvec + p.chunks_per_row - 1) / p.chunks_per_row;
+    const uint32_t v_begin = min(chunk * vec_per, nvec) * kVec;
+    const uint32_t v_end = min(min((chunk + 1) * vec_per, nvec) * kVec, V);
+    float* out = p.d_logits + row * V;
+
+    const float glp = p.g_logp ? p.g_logp[row] : 0.f;
+    const float gkl = (REF && p.g_kl) ? p.g_kl[row] : 0.f;
+    const float gen = p.g_ent ? p.g_ent[row] : 0.f;
+    const bool vec_out = VEC && ((reinterpret_cast<uintptr_t>(p.d_logits) & 15u) == 0);
+
+    if (glp == 0.f && gkl == 0.f && gen == 0.f) {
+        // an unscored position: exact zeros, the inputs are not read
+        for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
+            if (vec_out) {
+                stg_stream16(out + v, 0.f, 0.f, 0.f, 0.f);
+                stg_stream16(out + v + 4, 0.f, 0.f, 0.f, 0.f);
+            } else {
+                for (uint32_t i = 0; i < kVec && v + i < v_end; i++) out[v + i] = 0.f;
+            }
+        }
+        return;
+    }
+
+    const float4 st = reinterpret_cast<const float4*>(p.rowstats)[row];
+    const float m = st.x, lnZ = st.y, mr = st.z, lnZr = st.w;
+    const float klv = (REF && p.kl && gkl != 0.f) ? p.kl[row] : 0.f;
+    const float hv = (p.entropy && gen != 0.f) ? p.entropy[row] : 0.f;
+    const int32_t tok = (p.tokens && glp != 0.f) ? p.tokens[row] : -1;
+    const float shift = m + lnZ;      // log π_j = z_j − shift
+    const float rshift = mr + lnZr;   // log ρ_j = zr_j − rshift
+
+    VecLoader<DT, REF, ALLOW, GENERAL, VEC> ld;
+    for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
+        ld.load(f, row, v, v_end);
+        float z[8], zr[8], g[8];
+        ld.values(f, z, zr);
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            float zc = fmaxf(z[i], -FLT_MAX);
+            float lp = (zc - m) - lnZ;
+            float pi = ex2_approx(lp * kLog2e);
+            float c = -glp;                                   // d logp / dz_j = 1[j = tok] − π_j
+            if (REF) c = fmaf(gkl, (lp - (zr[i] - rshift)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+            c = fmaf(-gen, lp + hv, c);                       // d H / dz_j = −π_j (log π_j + H)
+            float d = pi > 0.f ? pi * c : 0.f;                // a zero-probability token gets exactly 0
+            if ((int32_t)(v + i) == tok) d += glp;
+            if (GENERAL && f.tau != 1.0f) d = __fdiv_rn(d, f.tau);
+            g[i] = d;
+        }
+        (void)shift;
+        if (vec_out) {
+            stg_stream16(out + v, g[0], g[1], g[2], g[3]);
+            stg_stream16(out + v + 4, g[4], g[5], g[6], g[7]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (v + i < v_end) out[v + i] = g[i];
+        }
+    }
+}
+
+}  // namespace nrl

@@ -1,0 +1,227 @@
+// Token-level losses over [S, B, T] values and the TokenReduction kernels. These touch rows,
+// not rows·V, elements: their cost is launch latency. Every sum runs in a fixed order.
+#pragma once
+#include "common.cuh"
+
+namespace nrl {
+
+struct TokParams {
+    const float* logp;
+    const float* other;
+    const float* weights;
+    const float* mask;
+    const float* upstream;
+    float* loss;
+    float* dloss;
+    uint64_t n;  // S·B·T
+    uint64_t T;
+    uint32_t kind;
+    uint32_t w_per_seq;
+    uint32_t has_dual;
+    uint32_t has_clamp;
+    float ratio_lo, ratio_hi;  // (f32)(1 − low), (f32)(1 + high)
+    float neg_dual;            // (f32)(−c)
+    float clamp;
+};
+
+// clamp(x, −b, b) as the reference builds it: clamp_max then clamp_min, each a mask_fill of a
+// comparison (src/tensor/float.rs:578-594); `pass` is false where a bound replaced the value.
+__device__ __forceinline__ float clamp_sym(float x, float b, bool& pass) {
+    pass = true;
+    if (x > b) { x = b; pass = false; }
+    if (x < -b) { x = -b; pass = false; }
+    return x;
+}
+
+__global__ void token_loss_kernel(TokParams p) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    const bool scored = p.mask ? (p.mask[i] != 0.f) : true;
+    const float lp = p.logp[i];
+    float per = 0.f, dl = 0.f;
+    if (p.kind == NRL_LOSS_PG) {
+        float w = p.weights[p.w_per_seq ? i / p.T : i];
+        per = -(lp * w);
+        dl = -w;
+    } else if (p.kind == NRL_LOSS_PPO) {
+        float a = p.weights[p.w_per_seq ? i / p.T : i];
+        float d = scored ? lp - p.other[i] : 0.f;  // log_ratio zeroes unscored positions first
+        bool pass_d = true;
+        if (p.has_clamp) d = clamp_sym(d, p.clamp, pass_d);
+        float r = expf(d);
+        float unclipped = -(r * a);
+        float rc = r;
+        bool pass_r = true;
+        if (rc > p.ratio_hi) { rc = p.ratio_hi; pass_r = false; }
+        if (rc < p.ratio_lo) { rc = p.ratio_lo; pass_r = false; }
+        float clipped = -(rc * a);
+        bool u_wins = (unclipped - clipped) > 0.f;  // select_max: a tie or NaN takes the clipped branch
+        float ppo = u_wins ? unclipped : clipped;
+        float g_ppo = 1.f;  // upstream of ppo
+        per = ppo;
+        if (p.has_dual) {
+            float cap = a * p.neg_dual;                 // −c·A
+            bool ppo_side = ((-ppo) - (-cap)) > 0.f;    // select_max(−ppo, −cap)
+            float capped = -(ppo_side ? -ppo : -cap);   // min(ppo, −c·A)
+            if (a < 0.f) {
+                per = capped;
+                g_ppo = ppo_side ? 1.f : 0.f;
+            }
+        }
+        // d per / d r through the two branches of select_max, then exp's g·y
+        float g_u = u_wins ? g_ppo : 0.f, g_c = u_wins ? 0.f : g_ppo;
+        float g_r = (-g_u) * a + (pass_r ? (-g_c) * a : 0.f);
+        float g_d = g_r * r;
+        dl = pass_d ? g_d : 0.f;
+    } else {
+        float d = scored ? p.other[i] - lp : 0.f;  // δ = ref − logp
+        bool pass_d = true;
+        if (p.has_clamp) d = clamp_sym(d, p.clamp, pass_d);
+        float g_d;
+        if (p.kind == NRL_LOSS_K1) {
+            per = -d;
+            g_d = -1.f;
+        } else if (p.kind == NRL_LOSS_K2) {
+            per = (d * d) / 2.0f;
+            g_d = d;
+        } else {
+            float e = expf(d);
+            per = e - (d + 1.0f);
+            g_d = e + (-1.f);
+        }
+        dl = pass_d ? -g_d : 0.f;
+    }
+    if (!scored) { per = 0.f; dl = 0.f; }  // zero_masked: a select, so garbage never leaks
+    if (p.loss) p.loss[i] = per;
+    if (p.dloss) p.dloss[i] = (p.upstream && scored) ? p.upstream[i] * dl : dl;
+}
+
+// block-wide sum of (a, b) in a fixed tree; result valid on thread 0
+template <int NT>
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* sm) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, s);
+        b += __shfl_xor_sync(0xffffffffu, b, s);
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) { sm[warp] = a; sm[NT / 32 + warp] = b; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float x = 0.f, y = 0.f;
+        for (int w = 0; w < NT / 32; w++) { x += sm[w]; y += sm[NT / 32 + w]; }
+        a = x; b = y;
+    }
+}
+
+constexpr int kRedThreads = 256;
+
+// clip_fraction (src/nn/rl.rs:293-317): one block per seed.
+__global__ void __launch_bounds__(kRedThreads) clip_fraction_kernel(TokParams p, uint64_t per_seed, float* out) {
+    __shared__ float sm[2 * kRedThreads / 32];
+    const uint64_t s = blockIdx.x;
+    float hits = 0.f, cnt = 0.f;
+    for (uint64_t j = threadIdx.x; j < per_seed; j += kRedThreads) {
+        uint64_t i = s * per_seed + j;
+        float mk = p.mask ? p.mask[i] : 1.f;
+        bool scored = mk != 0.f;
+        float a = p.weights[p.w_per_seq ? i / p.T : i];
+        float d = scored ? p.logp[i] - p.other[i] : 0.f;
+        float r = expf(d);
+        float pos = a > 0.f ? 1.f : 0.f, neg = a < 0.f ? 1.f : 0.f;
+        float hit = (r > p.ratio_hi ? 1.f : 0.f) * pos + (r < p.ratio_lo ? 1.f : 0.f) * neg;
+        if (p.has_dual) hit = hit + (r > -p.neg_dual ? 1.f : 0.f) * neg;
+        if (p.has_clamp) hit = hit + (fabsf(d) > p.clamp ? 1.f : 0.f);
+        if (hit > 1.f) hit = 1.f;
+        hits += hit * mk;
+        cnt += mk;
+    }
+    block_sum2<kRedThreads>(hits, cnt, sm);
+    if (threadIdx.x == 0) out[s] = hits / fmaxf(cnt, 1.f);
+}
+
+// TokenReduction forward: one block per seed; each sequence is summed by the block in a fixed
+// tree, sequences are combined in index order in f64.
+__global__ void __launch_bounds__(kRedThreads) reduce_tokens_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* per, const float* mask, float* out) {
+    __shared__ float sm[2 * kRedThreads / 32];
+    const uint64_t s = blockIdx.x;
+    double tot = 0.0, count = 0.0, seq_tot = 0.0, nonempty = 0.0;
+    for (uint64_t b = 0; b < B; b++) {
+        const uint64_t base = (s * B + b) * T;
+        float v = 0.f, c = 0.f;
+        for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) {
+            v += per[base + t];
+            c += mask ? mask[base + t] : 1.f;
+        }
+        block_sum2<kRedThreads>(v, c, sm);
+        if (threadIdx.x == 0) {
+            tot += (double)v;
+            count += (double)c;
+            float ps = v / fmaxf(c, 1.f);
+            if (reduction == NRL_REDUCE_PER_SEQUENCE) out[s * B + b] = ps;
+            seq_tot += (double)ps;
+            nonempty += (double)fminf(c, 1.f);
+        }
+    }
+    if (threadIdx.x == 0) {
+        if (reduction == NRL_REDUCE_SUM) out[s] = (float)tot;
+        if (reduction == NRL_REDUCE_TOKEN_MEAN) out[s] = (float)tot / fmaxf((float)count, 1.f);
+        if (reduction == NRL_REDUCE_SEQUENCE_MEAN) out[s] = (float)seq_tot / fmaxf((float)nonempty, 1.f);
+    }
+}
+
+// TokenReduction backward: d_per from the reduced value's upstream gradient.
+__global__ void __launch_bounds__(kRedThreads) reduce_tokens_bwd_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* mask, const float* g_out, float* d_per) {
+    __shared__ float sm[2 * kRedThreads / 32];
+    __shared__ float sh_scale;
+    const uint64_t s = blockIdx.x;
+    // the seed-level divisor
+    float seed_scale = 1.f;
+    if (reduction == NRL_REDUCE_TOKEN_MEAN || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
+        double count = 0.0, nonempty = 0.0;
+        for (uint64_t b = 0; b < B; b++) {
+            const uint64_t base = (s * B + b) * T;
+            float c = 0.f, z = 0.f;
+            for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) c += mask ? mask[base + t] : 1.f;
+            block_sum2<kRedThreads>(c, z, sm);
+            if (threadIdx.x == 0) {
+                count += (double)c;
+                nonempty += (double)fminf(c, 1.f);
+            }
+        }
+        if (threadIdx.x == 0) sh_scale = reduction == NRL_REDUCE_TOKEN_MEAN ? fmaxf((float)count, 1.f) : fmaxf((float)nonempty, 1.f);
+        __syncthreads();
+        seed_scale = sh_scale;
+    }
+    for (uint64_t b = 0; b < B; b++) {
+        const uint64_t base = (s * B + b) * T;
+        float g;
+        if (reduction == NRL_REDUCE_PER_SEQUENCE || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
+            float c = 0.f, z = 0.f;
+            for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) c += mask ? mask[base + t] : 1.f;
+            block_sum2<kRedThreads>(c, z, sm);
+            if (threadIdx.x == 0) sh_scale = fmaxf(c, 1.f);
+            __syncthreads();
+            float seq_scale = sh_scale;
+            __syncthreads();
+            g = reduction == NRL_REDUCE_PER_SEQUENCE ? g_out[s * B + b] / seq_scale : (g_out[s] / seed_scale) / seq_scale;
+        } else if (reduction == NRL_REDUCE_TOKEN_MEAN) {
+            g = g_out[s] / seed_scale;
+        } else {
+            g = g_out[s];  // SUM
+        }
+        for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) {
+            bool scored = mask ? mask[base + t] != 0.f : true;
+            float gi = reduction == NRL_REDUCE_NONE ? g_out[base + t] : g;
+            d_per[base + t] = scored ? gi : 0.f;
+        }
+    }
+}
+
+__global__ void mask_rows_kernel(uint64_t n, const float* x, const float* mask, float* out) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = (mask && mask[i] == 0.f) ? 0.f : x[i];
+}
+
+}  // namespace nrl

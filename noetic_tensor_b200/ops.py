@@ -1,0 +1,224 @@
+"""Calls into the C ABI with torch tensors as the device buffers.
+
+torch is used for device memory and the current stream only; every computation happens in
+libnrl.so. The functions here are thin: they check devices/dtypes, allocate the outputs the C ABI
+wants the caller to own, fill the argument struct and launch on torch's current stream.
+"""
+import ctypes as C
+
+import torch
+
+from . import capi
+
+
+def _dt(t):
+    if t.dtype == torch.float32:
+        return capi.F32
+    if t.dtype == torch.bfloat16:
+        return capi.BF16
+    raise TypeError(f"logits must be float32 or bfloat16, got {t.dtype}")
+
+
+def _p(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream(dev):
+    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _need(t, dtype, shape, what, dev):
+    if t.device != dev or t.dtype != dtype or tuple(t.shape) != tuple(shape) or not t.is_contiguous():
+        raise ValueError(f"{what}: expected contiguous {dtype} {tuple(shape)} on {dev}, got {t.dtype} {tuple(t.shape)} on {t.device}")
+
+
+def _masks(V, rows, allow, add, dev):
+    a_stride = d_stride = 0
+    if allow is not None:
+        allow = allow.view(torch.uint8) if allow.dtype == torch.bool else allow
+        if allow.dtype != torch.uint8 or not allow.is_contiguous() or allow.device != dev or allow.numel() not in (V, rows * V):
+            raise ValueError("allow mask: contiguous uint8/bool of [rows, V] or [1, V]")
+        a_stride = 0 if allow.numel() == V and rows != 1 else V
+    if add is not None:
+        if add.dtype != torch.float32 or not add.is_contiguous() or add.device != dev or add.numel() not in (V, rows * V):
+            raise ValueError("additive mask: contiguous float32 of [rows, V] or [1, V]")
+        d_stride = 0 if add.numel() == V and rows != 1 else V
+    return allow, a_stride, add, d_stride
+
+
+class RowForward:
+    """Outputs of nrl_row_fwd over [rows, V] logits (fields are None when not requested)."""
+
+    __slots__ = ("tokens", "logp", "ref_logp", "kl", "entropy", "rowstats", "status")
+
+
+def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, uniforms=None, tokens=None, greedy=False,
+                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None):
+    """Fused sample / log-prob / KL / entropy over logits [rows, V] (f32 or bf16, CUDA).
+
+    Exactly one of: `uniforms` (sample by inverse CDF), `greedy=True`, `tokens` (given, int32), or
+    none (row statistics, entropy and KL only)."""
+    dev = logits.device
+    if dev.type != "cuda":
+        raise ValueError("row_forward needs CUDA tensors: this library has no CPU path")
+    if logits.dim() != 2 or not logits.is_contiguous():
+        raise ValueError("logits: contiguous [rows, V]")
+    rows, V = logits.shape
+    a = capi.RowFwdArgs()
+    a.struct_size = C.sizeof(a)
+    a.dtype, a.V, a.rows, a.temperature = _dt(logits), V, rows, float(temperature)
+    a.logits = _p(logits)
+    if ref_logits is not None:
+        _need(ref_logits, logits.dtype, logits.shape, "ref_logits", dev)
+        a.ref_logits = _p(ref_logits)
+    allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
+    a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
+    out = RowForward()
+    f32 = dict(dtype=torch.float32, device=dev)
+    mode = 0
+    if uniforms is not None:
+        _need(uniforms, torch.float32, (rows,), "uniforms", dev)
+        mode, a.uniforms = capi.FWD_SAMPLE, _p(uniforms)
+        out.tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    elif greedy:
+        mode = capi.FWD_GREEDY
+        out.tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    elif tokens is not None:
+        _need(tokens, torch.int32, (rows,), "tokens", dev)
+        mode = capi.FWD_TOKENS_IN
+        out.tokens = tokens
+    else:
+        out.tokens = None
+    a.flags, a.tokens = mode, _p(out.tokens)
+    has_ref = ref_logits is not None
+    want_kl = has_ref if want_kl is None else want_kl
+    want_ref_logp = (has_ref and mode != 0) if want_ref_logp is None else want_ref_logp
+    out.logp = torch.empty(rows, **f32) if (want_logp and mode) else None
+    out.ref_logp = torch.empty(rows, **f32) if want_ref_logp else None
+    out.kl = torch.empty(rows, **f32) if want_kl else None
+    out.entropy = torch.empty(rows, **f32) if want_entropy else None
+    out.rowstats = torch.empty(rows, 4, **f32)
+    out.status = torch.empty(rows, dtype=torch.uint8, device=dev)
+    a.logp, a.ref_logp, a.kl, a.entropy, a.rowstats, a.status = _p(out.logp), _p(out.ref_logp), _p(out.kl), _p(out.entropy), _p(out.rowstats), _p(out.status)
+    need = capi.lib().nrl_row_fwd_workspace_bytes(rows, V)
+    if need:
+        if workspace is None or workspace.numel() * workspace.element_size() < need:
+            workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+        a.workspace, a.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_row_fwd(C.byref(a), _stream(dev)), "nrl_row_fwd")
+    return out
+
+
+def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None):
+    """d(logits) [rows, V] f32 from the forward's saved statistics and per-row upstream gradients."""
+    dev = logits.device
+    rows, V = logits.shape
+    a = capi.RowBwdArgs()
+    a.struct_size = C.sizeof(a)
+    a.dtype, a.V, a.rows, a.temperature = _dt(logits), V, rows, float(temperature)
+    a.logits, a.ref_logits = _p(logits), _p(ref_logits)
+    allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
+    a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
+    for name, g in (("g_logp", g_logp), ("g_kl", g_kl), ("g_ent", g_ent)):
+        if g is not None:
+            _need(g, torch.float32, (rows,), name, dev)
+    a.tokens, a.rowstats, a.kl, a.entropy = _p(fwd.tokens), _p(fwd.rowstats), _p(fwd.kl), _p(fwd.entropy)
+    a.g_logp, a.g_kl, a.g_ent = _p(g_logp), _p(g_kl), _p(g_ent)
+    if out is None:
+        out = torch.empty(rows, V, dtype=torch.float32, device=dev)
+    else:
+        _need(out, torch.float32, (rows, V), "d_logits", dev)
+    a.d_logits = _p(out)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_row_bwd(C.byref(a), _stream(dev)), "nrl_row_bwd")
+    return out
+
+
+def _tok_args(kind, logp, other, weights, mask, clip_low=0.0, clip_high=0.0, dual=None, clamp=None):
+    S, B, T = logp.shape
+    dev = logp.device
+    a = capi.TokenLossArgs()
+    a.struct_size = C.sizeof(a)
+    a.kind, a.S, a.B, a.T = kind, S, B, T
+    _need(logp, torch.float32, (S, B, T), "logp", dev)
+    a.logp = _p(logp)
+    if other is not None:
+        _need(other, torch.float32, (S, B, T), "old/ref log-probs", dev)
+        a.other = _p(other)
+    if weights is not None:
+        if weights.dim() == 2:
+            _need(weights, torch.float32, (S, B), "weights", dev)
+            a.weights_per_sequence = 1
+        else:
+            _need(weights, torch.float32, (S, B, T), "weights", dev)
+        a.weights = _p(weights)
+    if mask is not None:
+        _need(mask, torch.float32, (S, B, T), "mask", dev)
+        a.mask = _p(mask)
+    a.clip_low, a.clip_high = clip_low, clip_high
+    if dual is not None:
+        a.has_dual, a.dual = 1, dual
+    if clamp is not None:
+        a.has_clamp, a.clamp = 1, clamp
+    return a
+
+
+def token_loss(kind, logp, *, other=None, weights=None, mask=None, clip_low=0.0, clip_high=0.0, dual=None, clamp=None, want_grad=True, upstream=None):
+    """Per-token loss [S,B,T] (0 at unscored positions) and upstream · its derivative w.r.t. logp."""
+    dev = logp.device
+    a = _tok_args(kind, logp, other, weights, mask, clip_low, clip_high, dual, clamp)
+    if upstream is not None:
+        _need(upstream, torch.float32, logp.shape, "upstream", dev)
+        a.upstream = _p(upstream)
+    loss = torch.empty_like(logp)
+    dl = torch.empty_like(logp) if want_grad else None
+    a.loss, a.dloss_dlogp = _p(loss), _p(dl)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_token_loss(C.byref(a), _stream(dev)), "nrl_token_loss")
+    return loss, dl
+
+
+def clip_fraction(logp, old_logp, advantages, *, mask=None, clip_low, clip_high, dual=None, clamp=None):
+    dev = logp.device
+    a = _tok_args(capi.LOSS_PPO, logp, old_logp, advantages, mask, clip_low, clip_high, dual, clamp)
+    out = torch.empty(logp.shape[0], dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_clip_fraction(C.byref(a), _p(out), _stream(dev)), "nrl_clip_fraction")
+    return out
+
+
+def reduce_tokens(per, mask, reduction):
+    S, B, T = per.shape
+    dev = per.device
+    shape = {capi.REDUCE_NONE: (S, B, T), capi.REDUCE_PER_SEQUENCE: (S, B)}.get(reduction, (S,))
+    out = torch.empty(shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_reduce_tokens(reduction, S, B, T, _p(per), _p(mask), _p(out), _stream(dev)), "nrl_reduce_tokens")
+    return out
+
+
+def reduce_tokens_backward(shape, mask, reduction, g_out):
+    S, B, T = shape
+    dev = g_out.device
+    d = torch.empty(shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_reduce_tokens_bwd(reduction, S, B, T, _p(mask), _p(g_out), _p(d), _stream(dev)), "nrl_reduce_tokens_bwd")
+    return d
+
+
+def mask_rows(x, mask):
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        capi.check(capi.lib().nrl_mask_rows(x.numel(), _p(x), _p(mask), _p(out), _stream(x.device)), "nrl_mask_rows")
+    return out
+
+
+def check_status(status):
+    """Raises the reference's error (src/nn/rl.rs:517-519) if any row was refused."""
+    bad, bits = C.c_uint64(0), C.c_uint32(0)
+    with torch.cuda.device(status.device):
+        rc = capi.lib().nrl_check_status(_p(status), status.numel(), _stream(status.device), C.byref(bad), C.byref(bits))
+    if rc == capi.E_ROW_STATUS:
+        raise RuntimeError(f"sample_categorical: position {bad.value} has no allowed token (every logit −∞ or a NaN)")
+    capi.check(rc, "nrl_check_status")

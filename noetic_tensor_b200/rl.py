@@ -1,0 +1,192 @@
+"""`nn::rl` over the fused kernels: the reference's function names and argument meanings
+(src/nn/rl.rs), for logits that live on a CUDA device.
+
+Each loss returns a `Loss`: `.value` is the reduced tensor the reference function returns and
+`.backward(upstream)` gives d(logits) [S,B,T,V] f32 for sum(value · upstream), what the tape's
+`(value * upstream).sum().backward()` yields in the reference. Where the reference builds ~40
+tape nodes per PPO step, this path has one forward and one backward pass over the logits.
+
+Masks: `mask` is the scoring mask [S,B,T] of 0/1 floats (src/nn/rl.rs:9-14); `vocab_mask` is
+either a float additive mask broadcastable as [1,V] or [rows,V] (the reference's form,
+src/nn/rl.rs:471-486) or a uint8/bool allow-mask of the same shapes.
+"""
+import torch
+
+from . import capi, ops
+
+NONE, SUM, TOKEN_MEAN, PER_SEQUENCE, SEQUENCE_MEAN = range(5)
+K1, K2, K3 = capi.LOSS_K1, capi.LOSS_K2, capi.LOSS_K3
+LOG_RATIO_CLAMP = 20.0  # src/nn/rl.rs:146
+KL_DELTA_CLAMP = 20.0  # src/nn/rl.rs:150
+
+
+class Clip:
+    """`Clip` (src/nn/rl.rs:160-198)."""
+
+    def __init__(self, low, high, dual=None, log_ratio_clamp=LOG_RATIO_CLAMP):
+        self.low, self.high, self.dual, self.log_ratio_clamp = low, high, dual, log_ratio_clamp
+
+    @staticmethod
+    def symmetric(eps):
+        return Clip(eps, eps)
+
+    def with_dual(self, c):
+        return Clip(self.low, self.high, c, self.log_ratio_clamp)
+
+    def with_log_ratio_clamp(self, b):
+        return Clip(self.low, self.high, self.dual, b)
+
+
+class Tempered:
+    """`tempered_logits(logits, temperature, mask)` (src/nn/rl.rs:475-486) without materialising
+    it: the kernels apply the temperature and the mask as they stream the row."""
+
+    def __init__(self, logits, temperature=1.0, vocab_mask=None):
+        if not (temperature > 0.0):
+            raise ValueError(f"tempered_logits: temperature {temperature} (must be positive)")
+        self.logits = logits
+        self.shape = tuple(logits.shape)
+        self.V = logits.shape[-1]
+        self.flat = logits.reshape(-1, self.V)
+        self.temperature = float(temperature)
+        self.allow = self.add = None
+        if vocab_mask is not None:
+            if vocab_mask.shape[-1] != self.V:
+                raise ValueError("tempered_logits: mask does not broadcast to the logits")
+            m = vocab_mask.reshape(-1, self.V)
+            if m.dtype in (torch.uint8, torch.bool):
+                self.allow = m.contiguous()
+            else:
+                self.add = m.to(torch.float32).contiguous()
+
+    def kw(self):
+        return dict(allow=self.allow, add_mask=self.add, temperature=self.temperature)
+
+
+def _tempered(x):
+    return x if isinstance(x, Tempered) else Tempered(x)
+
+
+class Loss:
+    def __init__(self, value, backward):
+        self.value = value
+        self._backward = backward
+
+    def backward(self, upstream=None):
+        if upstream is None:
+            upstream = torch.ones_like(self.value)
+        return self._backward(upstream.to(torch.float32).contiguous())
+
+
+def sample_categorical(logits, temperature=1.0, vocab_mask=None, uniforms=None):
+    """Tokens [...] (int32) from softmax(logits/τ + mask): inverse CDF against `uniforms` (one per
+    position); τ = 0 is the first maximum. Refuses a position with no allowed token or a NaN with
+    the reference's message (src/nn/rl.rs:516-519). Returns (tokens, log-probs of the tokens)."""
+    if temperature < 0:
+        raise ValueError(f"sample_categorical: temperature {temperature} (must be ≥ 0)")
+    z = Tempered(logits, 1.0 if temperature == 0.0 else temperature, vocab_mask)
+    lead = z.shape[:-1]
+    if temperature == 0.0:
+        f = ops.row_forward(z.flat, greedy=True, want_entropy=False, **z.kw())
+    else:
+        f = ops.row_forward(z.flat, uniforms=uniforms.reshape(-1).contiguous(), want_entropy=False, **z.kw())
+    ops.check_status(f.status)
+    return f.tokens.reshape(lead), f.logp.reshape(lead)
+
+
+class _TokenLogProbs:
+    """token_log_probs (src/nn/rl.rs:134-141) and its backward to the logits."""
+
+    def __init__(self, logits, tokens):
+        self.z = _tempered(logits)
+        self.lead = self.z.shape[:-1]
+        self.fwd = ops.row_forward(self.z.flat, tokens=tokens.reshape(-1).to(torch.int32).contiguous(), want_entropy=False, **self.z.kw())
+        self.logp = self.fwd.logp.reshape(self.lead)
+
+    def grad_logits(self, g_logp):
+        d = ops.row_backward(self.z.flat, self.fwd, g_logp=g_logp.reshape(-1).contiguous(), **self.z.kw())
+        return d.reshape(self.z.shape)
+
+
+def token_log_probs(logits, tokens, mask=None):
+    t = _TokenLogProbs(logits, tokens)
+    value = t.logp if mask is None else ops.mask_rows(t.logp, mask)
+
+    def backward(up):
+        g = up if mask is None else ops.mask_rows(up, mask)
+        return t.grad_logits(g)
+
+    return Loss(value, backward)
+
+
+def _token_level(kind, logits, tokens, mask, reduction, **kw):
+    t = _TokenLogProbs(logits, tokens)
+    lp = t.logp.reshape(t.lead) if len(t.lead) == 3 else None
+    if lp is None:
+        raise ValueError("logp must be [S, B, T]")
+    per, _ = ops.token_loss(kind, lp, mask=mask, want_grad=False, **kw)
+    value = ops.reduce_tokens(per, mask, reduction)
+
+    def backward(up):
+        d_per = ops.reduce_tokens_backward(tuple(lp.shape), mask, reduction, up)
+        _, g_logp = ops.token_loss(kind, lp, mask=mask, upstream=d_per, **kw)
+        return t.grad_logits(g_logp)
+
+    return Loss(value, backward)
+
+
+def policy_gradient_loss(logits, tokens, weights, mask=None, reduction=TOKEN_MEAN):
+    """policy_gradient_loss(token_log_probs(logits, tokens), weights, mask, reduction), src/nn/rl.rs:228-235."""
+    return _token_level(capi.LOSS_PG, logits, tokens, mask, reduction, weights=weights)
+
+
+def clipped_policy_loss(logits, tokens, old_logp, advantages, mask=None, clip=None, reduction=TOKEN_MEAN):
+    """clipped_policy_loss (src/nn/rl.rs:265-287) of the tokens' log-probabilities."""
+    clip = clip or Clip.symmetric(0.2)
+    return _token_level(capi.LOSS_PPO, logits, tokens, mask, reduction, other=old_logp, weights=advantages, clip_low=clip.low, clip_high=clip.high,
+                        dual=clip.dual, clamp=clip.log_ratio_clamp)
+
+
+def kl_estimate(logits, tokens, ref_logp, estimator, delta_clamp=None, mask=None, reduction=TOKEN_MEAN):
+    """kl_estimate (src/nn/rl.rs:380-400) of the tokens' log-probabilities."""
+    return _token_level(estimator, logits, tokens, mask, reduction, other=ref_logp, clamp=delta_clamp)
+
+
+def clip_fraction(logp, old_logp, advantages, mask=None, clip=None):
+    """clip_fraction (src/nn/rl.rs:293-317), untracked."""
+    clip = clip or Clip.symmetric(0.2)
+    return ops.clip_fraction(logp, old_logp, advantages, mask=mask, clip_low=clip.low, clip_high=clip.high, dual=clip.dual, clamp=clip.log_ratio_clamp)
+
+
+def _row_level(which, logits, ref_logits, mask, reduction):
+    z = _tempered(logits)
+    if len(z.shape) != 4:
+        raise ValueError("logits [S, B, T, V]")
+    lead = z.shape[:-1]
+    ref = None if ref_logits is None else ref_logits.reshape(-1, z.V)
+    f = ops.row_forward(z.flat, ref_logits=ref, want_entropy=(which == "entropy"), want_kl=(which == "kl"), want_ref_logp=False, **z.kw())
+    raw = (f.kl if which == "kl" else f.entropy).reshape(lead)
+    per = raw if mask is None else ops.mask_rows(raw, mask)
+    value = ops.reduce_tokens(per, mask, reduction)
+
+    def backward(up):
+        d_per = ops.reduce_tokens_backward(lead, mask, reduction, up).reshape(-1)
+        kw = dict(g_kl=d_per) if which == "kl" else dict(g_ent=d_per)
+        return ops.row_backward(z.flat, f, ref_logits=ref, **kw, **z.kw()).reshape(z.shape)
+
+    return Loss(value, backward)
+
+
+def categorical_kl(logits, ref_logits, mask=None, reduction=TOKEN_MEAN):
+    """categorical_kl (src/nn/rl.rs:327-338). Pass `Tempered(...)` logits for reference_kl."""
+    return _row_level("kl", logits, ref_logits, mask, reduction)
+
+
+def reference_kl(logits, ref_logits, temperature, vocab_mask=None, mask=None, reduction=TOKEN_MEAN):
+    """reference_kl (src/nn/rl.rs:347-351): both sides at the sampling temperature, same vocabulary mask."""
+    return _row_level("kl", Tempered(logits, temperature, vocab_mask), ref_logits, mask, reduction)
+
+
+def categorical_entropy(logits, mask=None, reduction=TOKEN_MEAN):
+    """categorical_entropy (src/nn/rl.rs:405-414)."""
+    return _row_level("entropy", logits, None, mask, reduction)
