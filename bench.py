@@ -1,0 +1,317 @@
+#!/usr/bin/env python
+"""Benchmark of the fused sample + log-prob + KL + entropy forward at the Llama-3 vocabulary.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("headline"): config 3 of the baseline — logits [S=8, B=32, T=1024, V=128256] bf16
+~N(0,3) plus a log-Zipf(1.1) token prior, a U8 grammar mask per row (1–4 bands of width 64–4096
+plus 1 % random tokens) — with a bf16 frozen-reference stream (policy + N(0, 0.05)), one uniform
+per row. A step is one pass of the fused forward over the resident batch: every element of the
+logits, the reference and the mask is read from HBM once (5 bytes per element). Inputs are
+seeded synthetic data; the batch (tens of GB) is far larger than L2, so nothing is flushed
+between steps. One rank per GPU, rows partitioned across ranks, no collective on the data path.
+
+Prints one JSON line (see DESIGN.md for the fields).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+V = 128256
+S_FULL, B, T = 8, 32, 1024
+ROWS_PER_SEED = B * T
+BYTES_PER_ELEM = 2 + 2 + 1  # bf16 logits + bf16 reference + u8 mask: the algorithmic bytes per element
+METRIC = "rows/s fused sample+logprob+KL+entropy, V=128256 bf16"
+FALLBACK_HBM_GBS = 6650.0
+# DRAM bytes per launch ÷ algorithmic bytes per launch, from the ncu capture summarised in
+# profiles/ (None until a capture exists for the current kernel).
+NCU_TRAFFIC_RATIO = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            pass
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_inputs(rows, seed, device):
+    import torch
+
+    from noetic_tensor_b200 import synth
+
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    bias = synth.zipf_bias(V, 1.1, gen, device)
+    logits = synth.normal_logits(rows, V, 3.0, torch.bfloat16, gen, device, bias=bias)
+    ref = synth.perturbed(logits, 0.05, gen)
+    mask = synth.grammar_masks(rows, V, gen, device)
+    u = synth.uniforms(rows, gen, device)
+    return logits, ref, mask, u
+
+
+def cpu_reference_rows(logits_bits, ref_bits, allow, root, fast, threads):
+    """The reference's own path for the same quantities on a row sample: sample_categorical
+    (Gumbel-max, one ChaCha20 u64 per logit) + token_log_probs + reference_kl + categorical_entropy,
+    each under the same additive −inf vocabulary mask. Returns seconds."""
+    import numpy as np
+
+    import oracle
+
+    oracle.set_backend(fast, threads)
+    rows = logits_bits.shape[0]
+    shape = (1, 1, rows, V)
+    add = np.where(allow != 0, 0.0, -np.inf).astype(np.float32)
+    t0 = time.perf_counter()
+    tok = oracle.sample_gumbel(logits_bits, 1.0, root, "bench", add_mask=add)
+    vm = add.astype(np.float64)
+    oracle.rl_eval(oracle.OP_TOKEN_LOG_PROBS, shape, logits=logits_bits, tokens=tok, vocab_mask=vm)
+    oracle.rl_eval(oracle.OP_REFERENCE_KL, shape, logits=logits_bits, ref_logits=ref_bits, vocab_mask=vm)
+    oracle.rl_eval(oracle.OP_ENTROPY, shape, logits=logits_bits, vocab_mask=vm)
+    dt = time.perf_counter() - t0
+    oracle.set_backend(False, 1)
+    return dt
+
+
+def host_sample(rows, seed):
+    """A row sample of the workload on the host (bf16 bit patterns), for the CPU arms."""
+    import numpy as np
+    import torch
+
+    g = torch.Generator()
+    g.manual_seed(seed)
+    perm = torch.randperm(V, generator=g)
+    rank = torch.empty(V)
+    rank[perm] = torch.arange(1, V + 1, dtype=torch.float32)
+    bias = -1.1 * torch.log(rank)
+    x = (torch.randn(rows, V, generator=g) * 3.0 + bias).to(torch.bfloat16)
+    r = (x.float() + torch.randn(rows, V, generator=g) * 0.05).to(torch.bfloat16)
+    m = torch.rand(rows, V, generator=g) < 0.01
+    col = torch.arange(V)[None, :]
+    nb = torch.randint(1, 5, (rows,), generator=g)
+    for k in range(4):
+        w = torch.randint(64, 4097, (rows, 1), generator=g)
+        s0 = (torch.rand(rows, 1, generator=g) * (V - 4096)).long()
+        m |= (nb > k)[:, None] & (col >= s0) & (col < s0 + w)
+    bits = lambda t: t.view(torch.int16).numpy().view(np.uint16)
+    return bits(x), bits(r), m.to(torch.uint8).numpy()
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    sample_rows = 64
+    xb, rb, al = host_sample(sample_rows, 1234)
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_reference_rows(xb[:8], rb[:8], al[:8], 1, True, threads)
+    times = [cpu_reference_rows(xb, rb, al, 2 + i, True, threads) for i in range(args.steps)]
+    dt = sum(times) / len(times)
+    value = sample_rows / dt
+    line = {
+        "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (bf16 storage)", "data": "synthetic", "impl": "reference",
+        "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)", "rows_per_step": sample_rows, "V": V},
+        "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
+                         "sample": f"{sample_rows} rows of the workload per step; C++ restatement of the reference's Cpu(Fast) op sequence "
+                                   "(sample_categorical Gumbel-max + token_log_probs + reference_kl + categorical_entropy); the Rust reference cannot be built here"},
+        "e2e": {"value": value, "unit": "rows/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from noetic_tensor_b200 import capi, ops
+    from noetic_tensor_b200.hostpath import HostForward
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the hot path has no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    capi.lib()
+
+    # resident batch: as many whole seeds of the config as fit, leaving headroom
+    free, total = torch.cuda.mem_get_info(dev)
+    per_seed = ROWS_PER_SEED * V * BYTES_PER_ELEM
+    headroom = 14 << 30
+    s_res = int(max(1, min(S_FULL, (free - headroom) // per_seed)))
+    if args.seeds:
+        s_res = min(s_res, args.seeds)
+    rows = s_res * ROWS_PER_SEED
+    logits, ref, mask, u = make_inputs(rows, 1000 + rank, dev)
+    torch.cuda.synchronize()
+
+    def step():
+        return ops.row_forward(logits, ref_logits=ref, allow=mask, uniforms=u)
+
+    for _ in range(max(3, args.warmup)):
+        out = step()
+    torch.cuda.synchronize()
+    bad = int((out.status != 0).sum().item())
+
+    sampler = ClockSampler(local)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    launches0 = capi.lib().nrl_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        out = step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    launches = capi.lib().nrl_launch_count() - launches0
+    clocks = sampler.stop()
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_max = float(t.item())
+    ms_per_step = ms_max / args.steps
+    value = world * rows / (ms_per_step * 1e-3)
+
+    # bitwise reproducibility of the step, checked outside the timed region
+    again = step()
+    torch.cuda.synchronize()
+    reproducible = bool(torch.equal(out.tokens, again.tokens) and torch.equal(out.logp.view(torch.int32), again.logp.view(torch.int32))
+                        and torch.equal(out.kl.view(torch.int32), again.kl.view(torch.int32)) and torch.equal(out.entropy.view(torch.int32), again.entropy.view(torch.int32)))
+
+    # roofline of the one kernel a step launches (this rank's own launch time)
+    peak, peak_kind = measured_peak()
+    alg_bytes = rows * V * BYTES_PER_ELEM
+    launch_ms = ms / args.steps
+    achieved = alg_bytes / (launch_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
+                "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_fwd_fused<bf16, ref, allow>", "algorithmic_bytes_per_launch": alg_bytes,
+                "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * alg_bytes}
+
+    # end to end from host memory: pinned inputs cross PCIe every step, results come back
+    e2e_rows = args.e2e_rows
+    hf = HostForward(V, torch.bfloat16, chunk_rows=512, device=dev)
+    hx, hr, hm, hu = (t_[:e2e_rows].cpu().pin_memory() for t_ in (logits, ref, mask, u))
+    hf.run(hx, hu, ref=hr, mask=hm)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e2e_steps = 3
+    for _ in range(e2e_steps):
+        hout = hf.run(hx, hu, ref=hr, mask=hm)
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
+    h2d, d2h = hf.bytes_per_row()
+    e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": e2e_rows * h2d, "d2h_bytes_per_step": e2e_rows * d2h,
+           "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
+           "note": "host-resident bf16 logits + reference + mask streamed over PCIe in 512-row chunks, double-buffered; bound by the host link, not by HBM"}
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        n = 24
+        xb, rb, al = host_sample(n, 1234)
+        cpu_reference_rows(xb[:2], rb[:2], al[:2], 1, False, 1)
+        dt = cpu_reference_rows(xb, rb, al, 2, False, 1)
+        cpu_baseline = {"value": n / dt, "unit": "rows/s", "cores": 1, "kind": "port",
+                        "sample": f"{n} rows of the workload; C++ restatement of the reference's Cpu(Reference) op sequence (sample_categorical Gumbel-max + "
+                                  "token_log_probs + reference_kl + categorical_entropy), single thread as Cpu(Reference) is"}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (bf16 storage)", "data": "synthetic",
+            "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
+                       "rows_per_gpu_per_step": rows, "cache": "inputs (tens of GB) far larger than the 126 MB L2; no flush needed", "partition": f"rows split across {world} rank(s), no collective"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
+            "bitwise_reproducible": reproducible, "refused_rows": bad,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
+    ap.add_argument("--e2e-rows", type=int, default=2048)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -57,8 +57,6 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     const float klv = (REF && p.kl && gkl != 0.f) ? p.kl[row] : 0.f;
     const float hv = (p.entropy && gen != 0.f) ? p.entropy[row] : 0.f;
     const int32_t tok = (p.tokens && glp != 0.f) ? p.tokens[row] : -1;
-    const float shift = m + lnZ;      // log π_j = z_j − shift
-    const float rshift = mr + lnZr;   // log ρ_j = zr_j − rshift
 
     VecLoader<DT, REF, ALLOW, GENERAL, VEC> ld;
     for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
@@ -71,14 +69,13 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             float lp = (zc - m) - lnZ;
             float pi = ex2_approx(lp * kLog2e);
             float c = -glp;                                   // d logp / dz_j = 1[j = tok] − π_j
-            if (REF) c = fmaf(gkl, (lp - (zr[i] - rshift)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+            if (REF) c = fmaf(gkl, (lp - ((zr[i] - mr) - lnZr)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
             c = fmaf(-gen, lp + hv, c);                       // d H / dz_j = −π_j (log π_j + H)
             float d = pi > 0.f ? pi * c : 0.f;                // a zero-probability token gets exactly 0
             if ((int32_t)(v + i) == tok) d += glp;
             if (GENERAL && f.tau != 1.0f) d = __fdiv_rn(d, f.tau);
             g[i] = d;
         }
-        (void)shift;
         if (vec_out) {
             stg_stream16(out + v, g[0], g[1], g[2], g[3]);
             stg_stream16(out + v + 4, g[4], g[5], g[6], g[7]);

@@ -141,10 +141,11 @@ __device__ __forceinline__ void accumulate(Partial& a, const float z[8], const f
         for (int i = 1; i < 8; i++) rmax = fmax_nan(rmax, zr[i]);
         if (rmax != NRL_NEG_INF) {
             if (!(rmax <= a.mr)) partial_rebase_ref(a.mr, a.Sr, fmax_nan(a.mr, rmax));
-            float nb = -a.mr * kLog2e;
+            // (zr − mr) first, then the scale: folding mr·log2e into one fma would shift every
+            // term of the row by the rounding of that product, and ln Zr with it
             float s8 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 8; i++) s8 += ex2_approx(fmaf(zr[i], kLog2e, nb));
+            for (int i = 0; i < 8; i++) s8 += ex2_approx((zr[i] - a.mr) * kLog2e);
             a.Sr += s8;
         }
     }

@@ -45,7 +45,7 @@ class _Case(C.Structure):
         ("ref_logp", C.c_void_p), ("weights", C.c_void_p), ("weights_rank", C.c_int32), ("estimator", C.c_int32),
         ("mask", C.c_void_p), ("vocab_mask", C.c_void_p), ("temperature", C.c_double),
         ("clip_low", C.c_double), ("clip_high", C.c_double), ("dual", C.c_double), ("log_ratio_clamp", C.c_double), ("delta_clamp", C.c_double),
-        ("has_dual", C.c_int32), ("has_log_ratio_clamp", C.c_int32), ("has_delta_clamp", C.c_int32), ("pad_", C.c_int32),
+        ("has_dual", C.c_int32), ("has_log_ratio_clamp", C.c_int32), ("has_delta_clamp", C.c_int32), ("vocab_mask_full", C.c_int32),
         ("upstream", C.c_void_p), ("out_value", C.c_void_p), ("out_capacity", C.c_int64), ("out_len", C.c_void_p), ("out_grad", C.c_void_p),
     ]
 
@@ -148,7 +148,8 @@ def rl_eval(op, shape, *, dtype=F32, logits=None, ref_logits=None, tokens=None, 
             c.weights_rank = 3
     if vocab_mask is not None:
         a = _f64(vocab_mask)
-        assert a.size == V
+        assert a.size in (V, n * V)
+        c.vocab_mask_full = 1 if (a.size == n * V and n != 1) else 0
         keep.append(a)
         c.vocab_mask = _ptr(a)
     c.temperature = float(temperature)

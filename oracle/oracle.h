@@ -49,7 +49,8 @@ typedef struct orc_rl_case {
     const double* vocab_mask; /* additive [V] (broadcast [1,1,1,V]), or NULL */
     double temperature;       /* 1.0 leaves the logits as they are */
     double clip_low, clip_high, dual, log_ratio_clamp, delta_clamp;
-    int32_t has_dual, has_log_ratio_clamp, has_delta_clamp, pad_;
+    int32_t has_dual, has_log_ratio_clamp, has_delta_clamp;
+    int32_t vocab_mask_full; /* 1: vocab_mask is [S,B,T,V] (a per-position vocabulary mask) */
     const double* upstream; /* shape of the value, or NULL for no backward */
     double* out_value;
     int64_t out_capacity;

@@ -49,7 +49,7 @@ static int eval(const orc_rl_case* c) {
     Tensor logp;      // [S,B,T] log-probabilities entering the token-level losses
     Tensor logits;
     std::optional<Tensor> vmask;
-    if (c->vocab_mask) vmask = small(c->vocab_mask, Shape{1, 1, 1, V});
+    if (c->vocab_mask) vmask = c->vocab_mask_full ? small(c->vocab_mask, lsh) : small(c->vocab_mask, Shape{1, 1, 1, V});
     bool needs_logits = c->logits != nullptr;
     if (needs_logits) {
         logits = Tensor(load<T>(c->logits, c->logits_dtype, n * V), lsh);

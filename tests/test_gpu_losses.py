@@ -226,7 +226,15 @@ def test_token_losses_and_reductions_match_cpu_reference(oracle, shape):
                 val = ops.reduce_tokens(per, m_t, r)
                 d_per = ops.reduce_tokens_backward(shape, m_t, r, t32(up, val.shape))
                 _, gl = ops.token_loss(kind, lpt, mask=m_t, upstream=d_per, **kw)
-                assert rel(val.cpu().numpy(), want_v) <= 1e-5, (name, r, use_mask)
+                # a long signed sum cancels: the f32 reference itself is then only accurate to
+                # eps·Σ|terms|, so the reduced value is held to the f64 path with that allowance,
+                # and to CpuRef where the sums are short
+                true_v = oracle.rl_eval(op, lsh, dtype=oracle.F64, logp=lp, mask=m_np, reduction=r, **okw)
+                slack = 0.0 if r == 0 else 2e-7 * float(per.abs().sum().item()) / S
+                dv = np.abs(val.cpu().numpy().astype(np.float64).ravel() - true_v)
+                assert (dv <= 1e-5 * (1.0 + np.abs(true_v)) + slack).all(), (name, r, use_mask, float(dv.max()))
+                if n <= 64:
+                    assert rel(val.cpu().numpy(), want_v) <= 1e-5, (name, r, use_mask)
                 assert rel(gl.cpu().numpy(), want_g) <= 1e-5, (name, r, use_mask)
                 if use_mask:
                     assert (gl.cpu().numpy().ravel()[mask == 0.0] == 0.0).all()
