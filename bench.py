@@ -201,6 +201,8 @@ def run_ours(args):
     if args.seeds:
         s_res = min(s_res, args.seeds)
     rows = s_res * ROWS_PER_SEED
+    if args.rows:
+        rows = min(rows, args.rows)  # a small case for profiler captures
     logits, ref, mask, u = make_inputs(rows, 1000 + rank, dev)
     torch.cuda.synchronize()
 
@@ -252,26 +254,28 @@ def run_ours(args):
                 "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * alg_bytes}
 
     # end to end from host memory: pinned inputs cross PCIe every step, results come back
-    e2e_rows = args.e2e_rows
-    hf = HostForward(V, torch.bfloat16, chunk_rows=512, device=dev)
-    hx, hr, hm, hu = (t_[:e2e_rows].cpu().pin_memory() for t_ in (logits, ref, mask, u))
-    hf.run(hx, hu, ref=hr, mask=hm)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    e2e_steps = 3
-    for _ in range(e2e_steps):
-        hout = hf.run(hx, hu, ref=hr, mask=hm)
-    e2e_s = (time.perf_counter() - t0) / e2e_steps
-    te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
-    h2d, d2h = hf.bytes_per_row()
-    e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": e2e_rows * h2d, "d2h_bytes_per_step": e2e_rows * d2h,
-           "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
-           "note": "host-resident bf16 logits + reference + mask streamed over PCIe in 512-row chunks, double-buffered; bound by the host link, not by HBM"}
+    e2e = None
+    if not args.no_e2e:
+        e2e_rows = min(args.e2e_rows, rows)
+        hf = HostForward(V, torch.bfloat16, chunk_rows=512, device=dev)
+        hx, hr, hm, hu = (t_[:e2e_rows].cpu().pin_memory() for t_ in (logits, ref, mask, u))
+        hf.run(hx, hu, ref=hr, mask=hm)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e2e_steps = 3
+        for _ in range(e2e_steps):
+            hout = hf.run(hx, hu, ref=hr, mask=hm)
+        e2e_s = (time.perf_counter() - t0) / e2e_steps
+        te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
+        h2d, d2h = hf.bytes_per_row()
+        e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": e2e_rows * h2d, "d2h_bytes_per_step": e2e_rows * d2h,
+               "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
+               "note": "host-resident bf16 logits + reference + mask streamed over PCIe in 512-row chunks, double-buffered; bound by the host link, not by HBM"}
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -306,6 +310,8 @@ def main():
     ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
     ap.add_argument("--e2e-rows", type=int, default=2048)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
