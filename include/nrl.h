@@ -118,6 +118,29 @@ typedef struct nrl_row_fwd_args {
 uint64_t nrl_row_fwd_workspace_bytes(uint64_t rows, uint32_t V);
 int nrl_row_fwd(const nrl_row_fwd_args* args, nrl_stream stream);
 
+/* The same forward for callers that have no device allocator to take scratch memory from.
+ * (No counterpart in the reference: there every op allocates its outputs from the crate's own
+ * stream-ordered pool.) Some hosts of this library cannot call cudaMalloc at the point where they
+ * sample: an inference server that has handed all device memory to its own arena at start-up, a
+ * decode loop running under a no-allocation rule, or a plugin that is given buffers but no
+ * allocator. For them this entry point needs only the inputs and outputs in `args`: when few long
+ * rows are split over several thread blocks, the per-block partial results go to a fixed
+ * NRL_STATIC_SCRATCH_BYTES array that lives inside the library's device image (each GPU that loads
+ * the library holds that much memory until the process exits). `args->workspace` and
+ * `args->workspace_bytes` are ignored. It never calls cudaMalloc, cudaFree or any allocating
+ * routine.
+ *   - A shape whose scratch need (nrl_row_fwd_workspace_bytes) exceeds NRL_STATIC_SCRATCH_BYTES is
+ *     refused with NRL_E_WORKSPACE before anything is launched.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress, with that device current). Make that first call outside any stream
+ *     capture.
+ *   - All calls on a device share the one array. Nothing in it needs to start at zero (every slot
+ *     that is read is written earlier in the same call), and it keeps the last call's contents.
+ *     Two calls whose kernels may overlap on the GPU (different streams, no ordering) race on
+ *     it: order them, or use nrl_row_fwd with separate workspaces. */
+#define NRL_STATIC_SCRATCH_BYTES (256u * 1024u)
+int nrl_row_fwd_static(const nrl_row_fwd_args* args, nrl_stream stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Row backward: d(logits) in one streaming pass.
  *

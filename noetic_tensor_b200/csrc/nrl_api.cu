@@ -4,6 +4,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "row_bwd.cuh"
 #include "row_fwd_kernels.cuh"
@@ -39,7 +40,7 @@ extern "C" const char* nrl_error_string(int code) {
         case NRL_OK: return "success";
         case NRL_E_BAD_ARG: return "nrl: bad argument (null pointer, zero size, struct size mismatch or misaligned pointer)";
         case NRL_E_UNSUPPORTED: return "nrl: unsupported dtype or option";
-        case NRL_E_WORKSPACE: return "nrl: scratch buffer missing or too small";
+        case NRL_E_WORKSPACE: return "nrl: scratch buffer missing or too small (for nrl_row_fwd_static: the shape needs more than the fixed NRL_STATIC_SCRATCH_BYTES)";
         case NRL_E_ROW_STATUS: return "nrl: a row has no allowed token (every logit -inf) or a NaN";
         case NRL_E_NO_DEVICE: return "nrl: no CUDA device or no current context";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "nrl: unknown error";
@@ -174,6 +175,48 @@ extern "C" int nrl_row_fwd(const nrl_row_fwd_args* a, nrl_stream stream) {
     bool vec = can_vectorise(a->V, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
     bool general = !vec || a->add_mask != 0 || a->temperature != 1.0f;
     return dispatch_fwd(p, a->dtype, a->ref_logits != 0, a->allow_mask != 0, general, vec, (cudaStream_t)stream);
+}
+
+// ---- forward without a caller-provided workspace -------------------------------------------------
+//
+// For callers that may not allocate device memory (see include/nrl.h). The scratch of the split
+// forward lives in this array, inside the library's device image, once per GPU that loads it.
+static __device__ __align__(256) unsigned char g_static_scratch[NRL_STATIC_SCRATCH_BYTES];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the
+// address is looked up once per device with that device current, and that pointer goes to the
+// kernels.
+static const int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices];
+static std::mutex g_static_scratch_lock;
+
+static int static_scratch_address(void** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return NRL_E_NO_DEVICE;
+    std::lock_guard<std::mutex> hold(g_static_scratch_lock);
+    if (!g_static_scratch_addr[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        if (!p) return NRL_E_NO_DEVICE;
+        g_static_scratch_addr[dev] = p;
+    }
+    *out = g_static_scratch_addr[dev];
+    return NRL_OK;
+}
+
+extern "C" int nrl_row_fwd_static(const nrl_row_fwd_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_row_fwd_args)) return NRL_E_BAD_ARG;
+    if (nrl_row_fwd_workspace_bytes(a->rows, a->V) > NRL_STATIC_SCRATCH_BYTES) return NRL_E_WORKSPACE;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    nrl_row_fwd_args b = *a;
+    b.workspace = (nrl_devptr)(uintptr_t)scratch;
+    b.workspace_bytes = NRL_STATIC_SCRATCH_BYTES;
+    return nrl_row_fwd(&b, stream);
 }
 
 // ---- backward ------------------------------------------------------------------------------------
