@@ -138,7 +138,7 @@ int nrl_row_fwd(const nrl_row_fwd_args* args, nrl_stream stream);
  *     that is read is written earlier in the same call), and it keeps the last call's contents.
  *     Two calls whose kernels may overlap on the GPU (different streams, no ordering) race on
  *     it: order them, or use nrl_row_fwd with separate workspaces. */
-#define NRL_STATIC_SCRATCH_BYTES (256u * 1024u)
+#define NRL_STATIC_SCRATCH_BYTES (64u * 1024u)
 int nrl_row_fwd_static(const nrl_row_fwd_args* args, nrl_stream stream);
 
 /* ---------------------------------------------------------------------------------------------

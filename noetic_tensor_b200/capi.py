@@ -16,7 +16,7 @@ FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN = 1, 2, 4
 LOSS_PG, LOSS_PPO, LOSS_K1, LOSS_K2, LOSS_K3 = range(5)
 REDUCE_NONE, REDUCE_SUM, REDUCE_TOKEN_MEAN, REDUCE_PER_SEQUENCE, REDUCE_SEQUENCE_MEAN = range(5)
 E_BAD_ARG, E_UNSUPPORTED, E_WORKSPACE, E_ROW_STATUS, E_NO_DEVICE = -1, -2, -3, -4, -5
-STATIC_SCRATCH_BYTES = 256 * 1024
+STATIC_SCRATCH_BYTES = 64 * 1024
 
 u32, u64, f32, f64, ptr = C.c_uint32, C.c_uint64, C.c_float, C.c_double, C.c_uint64
 

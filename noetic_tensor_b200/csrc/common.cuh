@@ -11,7 +11,10 @@
 
 namespace nrl {
 
-constexpr int kThreads = 512;              // threads per block of the row kernels
+#ifndef NRL_THREADS
+#define NRL_THREADS 256
+#endif
+constexpr int kThreads = NRL_THREADS;      // threads per block of the row kernels
 constexpr int kWarps = kThreads / 32;      // 16 warps: each owns a contiguous part of the row
 constexpr int kVec = 8;                    // elements per thread per step (16 B of bf16)
 constexpr int kTile = 32 * kVec;           // elements one warp covers per step
@@ -30,6 +33,7 @@ __device__ __forceinline__ uint2 ldg_stream8(const void* p) {
     asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // streaming (evict-first) 16-byte store for gradients that are written once and not re-read here
 __device__ __forceinline__ void stg_stream16(void* p, float a, float b, float c, float d) {
     asm volatile("st.global.cs.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -44,6 +48,42 @@ __device__ __forceinline__ float fmax_nan(float a, float b) {
     float r;
     asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
     return r;
+}
+
+// three-input NaN-propagating max (one instruction on sm_100)
+__device__ __forceinline__ float fmax3_nan(float a, float b, float c) {
+    float r;
+    asm("max.NaN.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// ---- packed pairs of f32 (sm_100 f32x2 arithmetic: one issue slot for two lanes of work) -------
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
 }
 
 // 2^x, hardware approximation (relative error about 2^-22)

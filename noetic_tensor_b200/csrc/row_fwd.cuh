@@ -113,40 +113,59 @@ struct VecLoader {
 // fold one vector into a thread's partial
 template <bool REF>
 __device__ __forceinline__ void accumulate(Partial& a, const float z[8], const float zr[8]) {
-    float vmax = z[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) vmax = fmax_nan(vmax, z[i]);
+    // The arithmetic runs on packed pairs (f32x2): one issue slot per two elements for the
+    // subtract, scale, sum and multiply-add steps; maxima use the three-input max.
+    const f32x2 l2e = pack2(kLog2e, kLog2e);
+    float vmax = fmax3_nan(fmax3_nan(fmax3_nan(z[0], z[1], z[2]), z[3], z[4]), fmax3_nan(z[5], z[6], z[7]), z[0]);
     if (vmax != NRL_NEG_INF) {  // something allowed here (or a NaN)
         if (!(vmax <= a.m)) partial_rebase(a.m, a.S, a.W, a.D, fmax_nan(a.m, vmax));
-        float s8 = 0.f, w8 = 0.f, d8 = 0.f;
+        const f32x2 m2 = pack2(a.m, a.m);
+        f32x2 s2 = pack2(0.f, 0.f), w2 = s2, d2 = s2;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float zc = fmaxf(z[i], -FLT_MAX);  // −inf → finite, so 0·(−inf) never appears
-            float t = zc - a.m;
-            float e = ex2_approx(t * kLog2e);
-            s8 += e;
-            w8 = fmaf(e, t, w8);
+        for (int i = 0; i < 8; i += 2) {
+            // −inf → finite, so 0·(−inf) never appears
+            f32x2 zc = pack2(fmaxf(z[i], -FLT_MAX), fmaxf(z[i + 1], -FLT_MAX));
+            f32x2 t = sub2(zc, m2);
+            float a0, a1;
+            unpack2(mul2(t, l2e), a0, a1);
+            float e0 = ex2_approx(a0), e1 = ex2_approx(a1);
+            f32x2 e = pack2(e0, e1);
+            s2 = add2(s2, e);
+            w2 = fma2(e, t, w2);
             if (REF) {
-                float d = zc - zr[i];
-                if (e > 0.f) d8 = fmaf(e, d, d8);  // a zero-probability token contributes 0
+                float d0, d1;
+                unpack2(sub2(zc, pack2(zr[i], zr[i + 1])), d0, d1);
+                // a zero-probability token contributes 0 whatever the reference holds there
+                d2 = fma2(e, pack2(e0 > 0.f ? d0 : 0.f, e1 > 0.f ? d1 : 0.f), d2);
             }
         }
-        a.S += s8;
-        a.W += w8;
-        if (REF) a.D += d8;
+        float x0, x1;
+        unpack2(s2, x0, x1);
+        a.S += x0 + x1;
+        unpack2(w2, x0, x1);
+        a.W += x0 + x1;
+        if (REF) {
+            unpack2(d2, x0, x1);
+            a.D += x0 + x1;
+        }
     }
     if (REF) {
-        float rmax = zr[0];
-#pragma unroll
-        for (int i = 1; i < 8; i++) rmax = fmax_nan(rmax, zr[i]);
+        float rmax = fmax3_nan(fmax3_nan(fmax3_nan(zr[0], zr[1], zr[2]), zr[3], zr[4]), fmax3_nan(zr[5], zr[6], zr[7]), zr[0]);
         if (rmax != NRL_NEG_INF) {
             if (!(rmax <= a.mr)) partial_rebase_ref(a.mr, a.Sr, fmax_nan(a.mr, rmax));
             // (zr − mr) first, then the scale: folding mr·log2e into one fma would shift every
             // term of the row by the rounding of that product, and ln Zr with it
-            float s8 = 0.f;
+            const f32x2 mr2 = pack2(a.mr, a.mr);
+            f32x2 s2 = pack2(0.f, 0.f);
 #pragma unroll
-            for (int i = 0; i < 8; i++) s8 += ex2_approx((zr[i] - a.mr) * kLog2e);
-            a.Sr += s8;
+            for (int i = 0; i < 8; i += 2) {
+                float a0, a1;
+                unpack2(mul2(sub2(pack2(zr[i], zr[i + 1]), mr2), l2e), a0, a1);
+                s2 = add2(s2, pack2(ex2_approx(a0), ex2_approx(a1)));
+            }
+            float x0, x1;
+            unpack2(s2, x0, x1);
+            a.Sr += x0 + x1;
         }
     }
 }
@@ -158,20 +177,118 @@ __device__ __forceinline__ void stream_block(const FwdParams& p, uint64_t row, u
     uint32_t begin, end;
     part_range(p, split * kWarps + warp, begin, end);
     Partial acc = partial_empty();
-    VecLoader<DT, REF, ALLOW, GENERAL, VEC> cur, nxt;
+    // Software pipeline: kDepth tiles of this lane's loads are in flight while one is reduced
+    // (about 64 KB per SM with two resident blocks: what HBM latency × bandwidth asks for).
+#ifdef NRL_DEPTH
+    constexpr int kDepth = NRL_DEPTH;
+#else
+    constexpr int kDepth = (REF || ALLOW || GENERAL || DT == NRL_F32) ? 3 : 4;
+#endif
+    VecLoader<DT, REF, ALLOW, GENERAL, VEC> buf[kDepth];
     uint32_t v = begin + lane * kVec;
-    bool have = v < end;
-    if (have) cur.load(p, row, v, end);
-    while (have) {
-        uint32_t vn = v + kTile;
-        bool have_n = vn < end;
-        if (have_n) nxt.load(p, row, vn, end);  // next tile in flight while this one is reduced
-        float z[8], zr[8];
-        cur.values(p, z, zr);
-        accumulate<REF>(acc, z, zr);
-        cur = nxt;
-        v = vn;
-        have = have_n;
+#pragma unroll
+    for (int d = 0; d < kDepth; d++)
+        if (v + d * kTile < end) buf[d].load(p, row, v + d * kTile, end);
+    while (v < end) {
+#pragma unroll
+        for (int d = 0; d < kDepth; d++) {
+            if (v < end) {
+                float z[8], zr[8];
+                buf[d].values(p, z, zr);
+                accumulate<REF>(acc, z, zr);
+                uint32_t vn = v + kDepth * kTile;
+                if (vn < end) buf[d].load(p, row, vn, end);
+            }
+            v += kTile;
+        }
+    }
+    acc = partial_warp_reduce(acc);
+    if (lane == 0) sp[warp] = acc;
+}
+
+// The same for rows with a byte allow-mask, when most of the vocabulary is excluded (grammar
+// masks allow a few per cent of it): an excluded logit cannot affect any output, so it is not
+// read. Each warp scans its part's mask bytes tile by tile (1 byte per element, coalesced) and
+// queues the 8-element vectors that hold at least one allowed token in a 64-entry ring in shared
+// memory; whenever 32 are queued, every lane takes one, loads its logits / reference / mask
+// bytes and folds it into its partial. Issued arithmetic therefore runs on 32 busy lanes instead
+// of the one or two per tile that have work, and HBM traffic drops to the mask plus the 32-byte
+// sectors that contain an allowed token. The batch order depends only on the mask, so results
+// stay bitwise reproducible.
+constexpr int kQueue = 256;  // ring entries per warp: 31 left over + 4 tiles × 32 lanes, rounded up
+constexpr int kAhead = 4;    // mask tiles scanned per group
+
+template <int DT, bool REF>
+__device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* queue) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t lt = (1u << lane) - 1u;
+    uint32_t begin, end;
+    part_range(p, split * kWarps + warp, begin, end);
+    uint32_t* wq = queue + warp * kQueue;
+    typedef VecLoader<DT, REF, true, false, true> Loader;
+    Partial acc = partial_empty();
+    Loader pend;
+    bool pend_ok = false, pend_any = false;
+    uint32_t head = 0, count = 0;  // warp-uniform ring state
+
+    // this lane's mask bytes of the tile at `v`: pointer arithmetic is one 64-bit add per group
+    const uint8_t* mp = p.allow + row * p.allow_stride + begin + lane * kVec;
+    uint32_t v = begin + lane * kVec;
+    uint32_t t0 = begin;  // warp-uniform tile base of the group in mk[]
+    uint32_t mk[kAhead];  // OR of a tile's eight mask bytes: all the scan needs
+    uint2 mn[kAhead];
+#pragma unroll
+    for (int j = 0; j < kAhead; j++) {
+        uint2 q = (v + j * kTile < end) ? ldg_stream8(mp + j * kTile) : make_uint2(0u, 0u);
+        mk[j] = q.x | q.y;
+    }
+    // One loop with one copy of the arithmetic (a small instruction footprint): each turn scans
+    // a group of mask tiles if any is left, then folds batches while at least 32 vectors are
+    // queued; after the last group it drains the queue and the pending batch.
+    for (;;) {
+        const bool scanning = t0 < end;
+        if (scanning) {
+            // the next group's mask bytes fly while this group is scanned, and the group eight
+            // ahead is pulled into L2 (one 128-byte line per lane 0..7) so that its loads are
+            // short when their turn comes
+            const uint8_t* np = mp + kAhead * kTile;
+            const uint32_t nv = v + kAhead * kTile;
+            if (lane < 8 && t0 + 8 * kAhead * kTile + lane * 128 < end) prefetch_l2(mp - lane * kVec + 8 * kAhead * kTile + lane * 128);
+#pragma unroll
+            for (int j = 0; j < kAhead; j++) mn[j] = (nv + j * kTile < end) ? ldg_stream8(np + j * kTile) : make_uint2(0u, 0u);
+#pragma unroll
+            for (int j = 0; j < kAhead; j++) {
+                const bool nz = mk[j] != 0u;
+                const uint32_t ball = __ballot_sync(0xffffffffu, nz);
+                if (nz) wq[(head + count + __popc(ball & lt)) & (kQueue - 1)] = v + j * kTile;
+                count += __popc(ball);
+            }
+#pragma unroll
+            for (int j = 0; j < kAhead; j++) mk[j] = mn[j].x | mn[j].y;
+            mp = np;
+            v = nv;
+            t0 += kAhead * kTile;
+            __syncwarp();
+        }
+        while (count >= 32 || (!scanning && (count > 0 || pend_any))) {
+            // lane l takes queue entry l; the previous batch is folded while these loads fly
+            const uint32_t n = count < 32 ? count : 32;
+            Loader nxt;
+            const bool ok = (uint32_t)lane < n;
+            if (ok) nxt.load(p, row, wq[(head + lane) & (kQueue - 1)], end);
+            head = (head + n) & (kQueue - 1);
+            count -= n;
+            if (pend_any && pend_ok) {
+                float z[8], zr[8];
+                pend.values(p, z, zr);
+                accumulate<REF>(acc, z, zr);
+            }
+            pend = nxt;
+            pend_ok = ok;
+            pend_any = n > 0;
+        }
+        if (!scanning) break;
+        __syncwarp();  // the batch's entries are read before the next group's pushes can reuse slots
     }
     acc = partial_warp_reduce(acc);
     if (lane == 0) sp[warp] = acc;
@@ -214,13 +331,15 @@ __device__ __forceinline__ void finalize_row(const FwdParams& p, uint64_t row, u
         if (q < nparts) {
             Partial a = get(q);
             if (a.m != NRL_NEG_INF && a.S > 0.f) {
+                // f32 expf (1 ulp) is enough for the rescale: its error enters the row's mass
+                // weighted by e^dm·|dm|, at most a few 1e-8, and it is ~10× cheaper than f64 exp
                 double dm = (double)a.m - (double)m;
-                double c = exp(dm);
+                double c = (double)expf(a.m - m);
                 S += c * (double)a.S;
                 W += c * ((double)a.W + (double)a.S * dm);
                 D += c * (double)a.D;
             }
-            if (a.mr != NRL_NEG_INF) Sr += exp((double)a.mr - (double)mr) * (double)a.Sr;
+            if (a.mr != NRL_NEG_INF) Sr += (double)expf(a.mr - mr) * (double)a.Sr;
         }
     }
     double Sin = warp_scan_incl(S, lane);
@@ -254,8 +373,7 @@ __device__ __forceinline__ void finalize_row(const FwdParams& p, uint64_t row, u
                 if (q >= nparts) break;
                 Partial a = get(q);
                 if (!(a.m != NRL_NEG_INF && a.S > 0.f)) continue;
-                double dm = (double)a.m - (double)m;
-                double mass = exp(dm) * (double)a.S;
+                double mass = (double)expf(a.m - m) * (double)a.S;
                 last = q;
                 if (c + mass > t) {
                     my_part = q;
@@ -286,11 +404,13 @@ __device__ __forceinline__ void finalize_row(const FwdParams& p, uint64_t row, u
         }
         part = first;
     }
+    // both logarithms at once: lane 1 takes the reference's, the others the policy's
+    const double lg = log(lane == 1 ? Srt : Z);
+    const double lnZ = __shfl_sync(0xffffffffu, lg, 0), lnZr = __shfl_sync(0xffffffffu, lg, 1);
     if (lane == 0) {
         RowResult r;
         r.Z = Z; r.Zr = Srt; r.W = Wt; r.D = Dt;
         r.m = m; r.mr = mr;
-        double lnZ = log(Z), lnZr = log(Srt);
         r.lnZ = (float)lnZ;
         r.lnZr = (float)lnZr;
         r.ent = (float)(lnZ - Wt / Z);

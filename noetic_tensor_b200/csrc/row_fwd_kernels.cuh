@@ -12,6 +12,7 @@ struct PickShared {
     int last_mass[kWarps];
     uint32_t first_idx[kWarps];
     int32_t token;
+    int32_t last_token;
     float z_tok, zr_tok;
 };
 
@@ -23,6 +24,137 @@ __device__ __forceinline__ void load_one(const FwdParams& p, uint64_t row, uint3
     one.values(p, zz, rr);
     z = zz[0];
     zr = REF ? rr[0] : 0.f;
+}
+
+// Sampling inside part `res.part`: the first element, in index order, at which the running mass
+// exceeds res.resid. The part is covered in rounds of kThreads·64 elements; in a round thread j
+// owns the 8 vectors [j·64, j·64+64) of the round, so (round, thread, vector, element) is index
+// order. A thread keeps the masses of its 8 vectors; a block scan of the thread totals finds the
+// owner thread, which finds its vector from the kept masses and re-reads only that one vector.
+// With a byte mask, the mask bytes are read first and logits only for vectors that allow a token.
+constexpr int kPickVec = 8;
+
+template <int DT, bool ALLOW, bool GENERAL, bool VEC>
+__device__ __forceinline__ float vector_mass(const FwdParams& p, const VecLoader<DT, false, ALLOW, GENERAL, VEC>& ld, float m, uint32_t v, uint32_t hi) {
+    float z[8], zr[8];
+    ld.values(p, z, zr);
+    double s = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        float t = fmaxf(z[i], -FLT_MAX) - m;
+        float e = ex2_approx(t * kLog2e);
+        if (v + i < hi) s += (double)e;
+    }
+    return (float)s;
+}
+
+template <int DT, bool ALLOW, bool GENERAL, bool VEC>
+__device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, const RowResult& res, PickShared* ps) {
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    typedef VecLoader<DT, false, ALLOW, GENERAL, VEC> Loader;
+    uint32_t a, b;
+    part_range(p, res.part, a, b);
+    const float m = res.m;
+    const uint8_t* mrow = ALLOW ? p.allow + row * p.allow_stride : nullptr;
+    double base = 0.0;  // mass of the rounds before this one (block-uniform)
+    if (tid == 0) ps->last_token = -1;
+    for (uint32_t r0 = a; r0 < b; r0 += kThreads * kPickVec * kVec) {
+        const uint32_t lo = r0 + (uint32_t)tid * (kPickVec * kVec);
+        float vm[kPickVec];
+        // mask bytes first: an excluded vector costs 8 bytes, not 8 logits
+        bool live[kPickVec];
+#pragma unroll
+        for (int k = 0; k < kPickVec; k++) {
+            uint32_t v = lo + k * kVec;
+            live[k] = v < b;
+            if (ALLOW && VEC && !GENERAL) {
+                RawMask mk;
+                mk.q = make_uint2(0u, 0u);
+                if (live[k]) mk.load(mrow, v);
+                live[k] = mk.any();
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < kPickVec; g += 4) {
+            Loader ld[4];
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (live[g + k]) ld[k].load(p, row, lo + (g + k) * kVec, b);
+#pragma unroll
+            for (int k = 0; k < 4; k++) vm[g + k] = live[g + k] ? vector_mass<DT, ALLOW, GENERAL, VEC>(p, ld[k], m, lo + (g + k) * kVec, b) : 0.f;
+        }
+        double s = 0.0;
+#pragma unroll
+        for (int k = 0; k < kPickVec; k++) s += (double)vm[k];
+        double incl = warp_scan_incl(s, lane);
+        __syncthreads();  // the previous round's reads of the shared slots are done
+        if (lane == 31) ps->warp_tot[warp] = incl;
+        __syncthreads();
+        double before = base, total = base;
+        for (int w = 0; w < kWarps; w++) {
+            if (w < warp) before += ps->warp_tot[w];
+            total += ps->warp_tot[w];
+        }
+        double excl = before + (incl - s);
+        bool claim = s > 0.0 && (excl + s > res.resid);
+        uint32_t cb = __ballot_sync(0xffffffffu, claim);
+        uint32_t mb = __ballot_sync(0xffffffffu, s > 0.0);
+        if (lane == 0) {
+            ps->first_claim[warp] = cb ? (warp * 32 + __ffs(cb) - 1) : -1;
+            ps->last_mass[warp] = mb ? (warp * 32 + 31 - __clz(mb)) : -1;
+        }
+        __syncthreads();
+        int owner = -1, last_owner = -1;
+        for (int w = 0; w < kWarps; w++) {
+            if (owner < 0) owner = ps->first_claim[w];
+            if (ps->last_mass[w] >= 0) last_owner = ps->last_mass[w];
+        }
+        // the thread that ends the row if rounding leaves no crossing: the last one with mass
+        const bool crossing = owner >= 0;
+        if (!crossing) owner = last_owner;
+        if (tid == owner) {
+            // find the vector from the kept masses, then walk its 8 elements
+            double c = excl;
+            int kk = -1, klast = -1;
+#pragma unroll
+            for (int k = 0; k < kPickVec; k++) {
+                if (vm[k] > 0.f) {
+                    klast = k;
+                    if (kk < 0 && crossing && c + (double)vm[k] > res.resid) kk = k;
+                    if (kk < 0) c += (double)vm[k];
+                }
+            }
+            const bool take_last = kk < 0;
+            if (take_last) kk = klast;
+            if (kk >= 0) {
+                if (take_last) c = 0.0;  // irrelevant: the last element with mass is taken
+                uint32_t v = lo + kk * kVec;
+                Loader one;
+                one.load(p, row, v, b);
+                float z[8], zr[8];
+                one.values(p, z, zr);
+                int32_t tok = -1, last = -1;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    if (v + i < b) {
+                        float t = fmaxf(z[i], -FLT_MAX) - m;
+                        float e = ex2_approx(t * kLog2e);
+                        if (e > 0.f) last = (int32_t)(v + i);
+                        c += (double)e;
+                        if (tok < 0 && !take_last && c > res.resid) tok = (int32_t)(v + i);
+                    }
+                }
+                if (crossing) ps->token = tok >= 0 ? tok : last;
+                else ps->last_token = last;
+            }
+        }
+        __syncthreads();
+        if (crossing) return;       // block-uniform: ps->token is set
+        base = total;
+    }
+    // no crossing in any round (rounding only): the last token with mass seen
+    if (tid == 0) ps->token = ps->last_token;
+    __syncthreads();
 }
 
 // All threads of the block: find the token inside part `res.part`.
@@ -70,59 +202,7 @@ __device__ __forceinline__ void pick_token(const FwdParams& p, uint64_t row, con
         return;
     }
 
-    // this thread's mass, in element order
-    double s = 0.0;
-    for (uint32_t v = lo; v < hi; v += kVec) {
-        ld.load(p, row, v, hi);
-        ld.values(p, z, zr);
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            float t = fmaxf(z[i], -FLT_MAX) - m;
-            float e = ex2_approx(t * kLog2e);
-            if (v + i < hi) s += (double)e;
-        }
-    }
-    double incl = warp_scan_incl(s, lane);
-    if (lane == 31) ps->warp_tot[warp] = incl;
-    __syncthreads();
-    double before = 0.0;
-    for (int w = 0; w < warp; w++) before += ps->warp_tot[w];
-    double excl = before + (incl - s);
-    bool claim = s > 0.0 && (excl + s > res.resid);
-    uint32_t cb = __ballot_sync(0xffffffffu, claim);
-    uint32_t mb = __ballot_sync(0xffffffffu, s > 0.0);
-    if (lane == 0) {
-        ps->first_claim[warp] = cb ? (warp * 32 + __ffs(cb) - 1) : -1;
-        ps->last_mass[warp] = mb ? (warp * 32 + 31 - __clz(mb)) : -1;
-    }
-    __syncthreads();
-    int owner = -1;
-    for (int w = 0; w < kWarps && owner < 0; w++) owner = ps->first_claim[w];
-    bool take_last = false;
-    if (owner < 0) {  // rounding only: no running sum crosses; the last thread with mass ends the row
-        take_last = true;
-        for (int w = kWarps - 1; w >= 0 && owner < 0; w--) owner = ps->last_mass[w];
-    }
-    if (tid == owner) {
-        double c = excl;
-        int32_t tok = -1, last = -1;
-        for (uint32_t v = lo; v < hi && tok < 0; v += kVec) {
-            ld.load(p, row, v, hi);
-            ld.values(p, z, zr);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (tok < 0 && v + i < hi) {
-                    float t = fmaxf(z[i], -FLT_MAX) - m;
-                    float e = ex2_approx(t * kLog2e);
-                    if (e > 0.f) last = (int32_t)(v + i);
-                    c += (double)e;
-                    if (!take_last && c > res.resid) tok = (int32_t)(v + i);
-                }
-            }
-        }
-        ps->token = tok >= 0 ? tok : last;
-    }
-    __syncthreads();
+    pick_sample<DT, ALLOW, GENERAL, VEC>(p, row, res, ps);
 }
 
 // Thread 0 writes the row's outputs.
@@ -156,14 +236,26 @@ __device__ __forceinline__ void write_row(const FwdParams& p, uint64_t row, cons
     if (p.status) p.status[row] = (uint8_t)status;
 }
 
+// Streams a block's range of a row: byte-masked rows on the vectorised fast path go through the
+// compacting scan, everything else through the plain tile loop.
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+__device__ __forceinline__ void stream_row(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp) {
+    if constexpr (ALLOW && VEC && !GENERAL) {
+        __shared__ uint32_t queue[kWarps * kQueue];
+        stream_block_compact<DT, REF>(p, row, split, sp, queue);
+    } else {
+        stream_block<DT, REF, ALLOW, GENERAL, VEC>(p, row, split, sp);
+    }
+}
+
 // ---- fused: one block per row ---------------------------------------------------------------
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
-__global__ void __launch_bounds__(kThreads, 2) row_fwd_fused(FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) row_fwd_fused(FwdParams p) {
     __shared__ Partial sp[kWarps];
     __shared__ RowResult res;
     __shared__ PickShared ps;
     const uint64_t row = blockIdx.x;
-    stream_block<DT, REF, ALLOW, GENERAL, VEC>(p, row, 0, sp);
+    stream_row<DT, REF, ALLOW, GENERAL, VEC>(p, row, 0, sp);
     __syncthreads();
     if (threadIdx.x < 32) finalize_row(p, row, kWarps, [&](uint32_t q) { return sp[q]; }, &res);
     __syncthreads();
@@ -174,11 +266,11 @@ __global__ void __launch_bounds__(kThreads, 2) row_fwd_fused(FwdParams p) {
 
 // ---- split, stage 1: a block streams one range of a row and stores its 16 partials ----------
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
-__global__ void __launch_bounds__(kThreads, 2) row_fwd_parts(FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) row_fwd_parts(FwdParams p) {
     __shared__ Partial sp[kWarps];
     const uint64_t row = blockIdx.x / p.nsplit;
     const uint32_t split = blockIdx.x % p.nsplit;
-    stream_block<DT, REF, ALLOW, GENERAL, VEC>(p, row, split, sp);
+    stream_row<DT, REF, ALLOW, GENERAL, VEC>(p, row, split, sp);
     __syncthreads();
     if (threadIdx.x < kWarps) {
         Partial a = sp[threadIdx.x];
@@ -190,7 +282,7 @@ __global__ void __launch_bounds__(kThreads, 2) row_fwd_parts(FwdParams p) {
 
 // ---- split, stage 2: merge a row's partials, pick the token, write the outputs --------------
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
-__global__ void __launch_bounds__(kThreads, 2) row_fwd_finish(FwdParams p) {
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) row_fwd_finish(FwdParams p) {
     __shared__ RowResult res;
     __shared__ PickShared ps;
     const uint64_t row = blockIdx.x;
