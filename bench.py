@@ -35,6 +35,8 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch ÷ algorithmic bytes per launch, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the current kernel).
 NCU_TRAFFIC_RATIO = None
+# Measured-peak read bandwidth of a pure streaming read kernel on this pool (for context only).
+
 
 
 def measured_peak():
@@ -164,7 +166,7 @@ def run_reference(args):
     value = sample_rows / dt
     line = {
         "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (bf16 storage)", "data": "synthetic", "impl": "reference",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "impl": "reference",
         "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)", "rows_per_step": sample_rows, "V": V},
         "cpu_baseline": {"value": value, "unit": "rows/s", "cores": threads, "kind": "port",
                          "sample": f"{sample_rows} rows of the workload per step; C++ restatement of the reference's Cpu(Fast) op sequence "
@@ -173,6 +175,126 @@ def run_reference(args):
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def _time(fn, iters=5, warm=3):
+    import torch
+
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_extras(dev, peak):
+    """Secondary measurements on row slices of the other configurations (device-timed, inputs
+    resident, each slice several GB so L2 holds none of it): not the headline, reported so that
+    every kernel on the path has a number. bytes = algorithmic bytes of forward + backward."""
+    import torch
+
+    from noetic_tensor_b200 import capi, ops, synth
+
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(77)
+    res = {}
+
+    def entry(rows, ms, nbytes, what):
+        return {"what": what, "rows": rows, "ms": ms, "rows_per_s": rows / (ms * 1e-3), "GBps": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_peak": nbytes / (ms * 1e-3) / 1e9 / peak}
+
+    # headline shape, forward + backward to d(logits)
+    rows = 8192
+    bias = synth.zipf_bias(V, 1.1, gen, dev)
+    x = synth.normal_logits(rows, V, 3.0, torch.bfloat16, gen, dev, bias=bias)
+    r = synth.perturbed(x, 0.05, gen)
+    m = synth.grammar_masks(rows, V, gen, dev)
+    u = synth.uniforms(rows, gen, dev)
+    ones = torch.ones(rows, device=dev)
+    d = torch.empty(rows, V, dtype=torch.float32, device=dev)
+
+    def fwd_bwd():
+        f = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+        ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones, g_ent=ones, out=d)
+
+    res["headline_fwd_bwd"] = entry(rows, _time(fwd_bwd), rows * V * (5 + 5 + 4), "config 3 + reference: sample+logp+KL+entropy forward, then backward to f32 d(logits)")
+    f = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+    res["headline_bwd_only"] = entry(rows, _time(lambda: ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones, g_ent=ones, out=d)), rows * V * (5 + 4),
+                                     "row backward alone (reads logits, reference, mask; writes f32 gradients)")
+    res["unmasked_fwd"] = entry(rows, _time(lambda: ops.row_forward(x, ref_logits=r, uniforms=u)), rows * V * 4, "same logits and reference without a mask: every byte is read")
+    del x, r, m, d, f
+
+    # config 4: one PPO step, V = 151936, forward + token losses + backward
+    V4, S4, B4, T4 = 151936, 1, 32, 256
+    rows = S4 * B4 * T4
+    x = synth.normal_logits(rows, V4, 2.5, torch.bfloat16, gen, dev)
+    r = synth.perturbed(x, 0.05, gen)
+    u = synth.uniforms(rows, gen, dev)
+    tok = ops.row_forward(x, uniforms=u, want_entropy=False).tokens
+    f0 = ops.row_forward(x, ref_logits=r, tokens=tok)
+    old = (f0.logp + 0.02 * torch.randn(rows, generator=gen, device=dev)).reshape(S4, B4, T4).contiguous()
+    adv = synth.group_relative_advantages(S4, B4, 8, 0.3, gen, dev)
+    d = torch.empty(rows, V4, dtype=torch.float32, device=dev)
+    up = torch.ones(S4, device=dev)
+    launches0 = capi.lib().nrl_launch_count()
+
+    def ppo_step():
+        f = ops.row_forward(x, ref_logits=r, tokens=tok)
+        lp = f.logp.reshape(S4, B4, T4)
+        per, _ = ops.token_loss(capi.LOSS_PPO, lp, other=old, weights=adv, clip_low=0.2, clip_high=0.2, clamp=20.0, want_grad=False)
+        loss = ops.reduce_tokens(per, None, capi.REDUCE_TOKEN_MEAN)
+        kl = ops.reduce_tokens(f.kl.reshape(S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN)
+        ent = ops.reduce_tokens(f.entropy.reshape(S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN)
+        g_per = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, up)
+        _, g_lp = ops.token_loss(capi.LOSS_PPO, lp, other=old, weights=adv, clip_low=0.2, clip_high=0.2, clamp=20.0, upstream=g_per)
+        g_kl = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, 0.04 * up).reshape(-1)
+        g_en = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, -0.01 * up).reshape(-1)
+        ops.row_backward(x, f, ref_logits=r, g_logp=g_lp.reshape(-1), g_kl=g_kl, g_ent=g_en, out=d)
+        return loss, kl, ent
+
+    ms = _time(ppo_step)
+    res["ppo_step_config4"] = entry(rows, ms, rows * V4 * (4 + 4 + 4), "config 4 slice [1,32,256,151936] bf16 + reference: PPO-clip 0.2 + 0.04 KL − 0.01 entropy, forward + backward to f32 d(logits)")
+    res["ppo_step_config4"]["launches_per_step"] = (capi.lib().nrl_launch_count() - launches0) // 8
+    del x, r, d, f0
+
+    # config 2: dense f32 sampling + backward of the sampled tokens' log-probs
+    V2, rows = 32000, 32768
+    x = synth.normal_logits(rows, V2, 2.0, torch.float32, gen, dev)
+    u = synth.uniforms(rows, gen, dev)
+    ones = torch.ones(rows, device=dev)
+    d = torch.empty(rows, V2, dtype=torch.float32, device=dev)
+
+    def cfg2():
+        f = ops.row_forward(x, uniforms=u)
+        ops.row_backward(x, f, g_logp=ones, out=d)
+
+    res["dense_f32_config2"] = entry(rows, _time(cfg2), rows * V2 * (4 + 4 + 4), "config 2 slice [rows,32000] f32, no mask: sample+logp+entropy forward, backward of the sum of sampled log-probs")
+    del x, d
+
+    # config 5: extreme sparse masks at V = 262144
+    V5, rows = 262144, 4096
+    x = synth.normal_logits(rows, V5, 4.0, torch.bfloat16, gen, dev)
+    m, idx = synth.sparse_masks(rows, V5, gen, dev)
+    shift = torch.zeros(rows, V5, dtype=torch.bfloat16, device=dev)
+    live = idx >= 0
+    rr = torch.arange(rows, device=dev)[:, None].expand(rows, 8)
+    x[rr[live], idx[live]] -= 30.0
+    r = synth.perturbed(x, 0.1, gen)
+    del shift
+    u = synth.uniforms(rows, gen, dev)
+    ones = torch.ones(rows, device=dev)
+    d = torch.empty(rows, V5, dtype=torch.float32, device=dev)
+
+    def cfg5():
+        f = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+        ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones, out=d)
+
+    res["sparse_config5"] = entry(rows, _time(cfg5), rows * V5 * (5 + 5 + 4), "config 5 slice [rows,262144] bf16 + reference + masks allowing 1-8 tokens: masked sample+logp+KL forward + backward")
+    return res
 
 
 def run_ours(args):
@@ -251,7 +373,12 @@ def run_ours(args):
     achieved = alg_bytes / (launch_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
                 "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_fwd_fused<bf16, ref, allow>", "algorithmic_bytes_per_launch": alg_bytes,
-                "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * alg_bytes}
+                "traffic": None if NCU_TRAFFIC_RATIO is None else NCU_TRAFFIC_RATIO * alg_bytes,
+                "note": "algorithmic bytes count every logit, reference and mask byte once (5 B per element); the kernel does not read logits the mask "
+                        "excludes, so its DRAM traffic (`traffic`, from ncu) is below the algorithmic bytes and `frac` can exceed 1"}
+    if roofline["traffic"]:
+        roofline["dram_GBps"] = roofline["traffic"] / (launch_ms * 1e-3) / 1e9
+        roofline["dram_frac"] = roofline["dram_GBps"] / peak
 
     # end to end from host memory: pinned inputs cross PCIe every step, results come back
     e2e = None
@@ -277,6 +404,12 @@ def run_ours(args):
                "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
                "note": "host-resident bf16 logits + reference + mask streamed over PCIe in 512-row chunks, double-buffered; bound by the host link, not by HBM"}
 
+    extras = None
+    if rank == 0 and not args.no_extras:
+        del logits, ref, mask, u, out, again
+        torch.cuda.empty_cache()
+        extras = run_extras(dev, peak)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         n = 24
@@ -290,11 +423,11 @@ def run_ours(args):
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 (bf16 storage)", "data": "synthetic",
-            "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)", "storage": "bf16 logits, f32 arithmetic", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
                        "rows_per_gpu_per_step": rows, "cache": "inputs (tens of GB) far larger than the 126 MB L2; no flush needed", "partition": f"rows split across {world} rank(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "bitwise_reproducible": reproducible, "refused_rows": bad,
+            "bitwise_reproducible": reproducible, "refused_rows": bad, "extras": extras,
         }
         print(json.dumps(line))
     if world > 1:
@@ -311,6 +444,7 @@ def main():
     ap.add_argument("--e2e-rows", type=int, default=2048)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
     ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

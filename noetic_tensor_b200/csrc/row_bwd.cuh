@@ -60,6 +60,22 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
 
     VecLoader<DT, REF, ALLOW, GENERAL, VEC> ld;
     for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
+        if constexpr (ALLOW && VEC && !GENERAL) {
+            // an excluded vector has zero gradient whatever its logits are: only its 8 mask bytes are read
+            RawMask mk;
+            mk.load(f.allow, row * f.allow_stride + v);
+            const bool holds_token = tok >= (int32_t)v && tok < (int32_t)(v + kVec);  // its entry gets g_lp even if excluded
+            if (!mk.any() && !holds_token) {
+                if (vec_out) {
+                    stg_stream16(out + v, 0.f, 0.f, 0.f, 0.f);
+                    stg_stream16(out + v + 4, 0.f, 0.f, 0.f, 0.f);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) out[v + i] = 0.f;
+                }
+                continue;
+            }
+        }
         ld.load(f, row, v, v_end);
         float z[8], zr[8], g[8];
         ld.values(f, z, zr);

@@ -102,70 +102,161 @@ struct VecLoader {
         if (ALLOW) {
 #pragma unroll
             for (int i = 0; i < 8; i++) {
+                // an excluded token becomes −FLT_MAX, not −inf: exp underflows to exactly 0 either
+                // way, and no 0·inf or inf − inf can appear downstream
                 bool ok = k.allowed(i);
-                z[i] = ok ? z[i] : NRL_NEG_INF;
-                if (REF) zr[i] = ok ? zr[i] : NRL_NEG_INF;
+                z[i] = ok ? z[i] : -FLT_MAX;
+                if (REF) zr[i] = ok ? zr[i] : -FLT_MAX;
             }
         }
     }
 };
 
-// fold one vector into a thread's partial
-template <bool REF>
-__device__ __forceinline__ void accumulate(Partial& a, const float z[8], const float zr[8]) {
-    // The arithmetic runs on packed pairs (f32x2): one issue slot per two elements for the
-    // subtract, scale, sum and multiply-add steps; maxima use the three-input max.
-    const f32x2 l2e = pack2(kLog2e, kLog2e);
+__device__ __forceinline__ float fmin3(float a, float b, float c) {
+    float r;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+__device__ __forceinline__ float warp_max_nan(float x) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) x = fmax_nan(x, __shfl_xor_sync(0xffffffffu, x, s));
+    return x;
+}
+
+// A lane's running partial while it streams: the sums live as packed pairs (even elements in
+// the low half, odd in the high half) so that the per-vector work is packed arithmetic only;
+// the halves are added when the lane's partial is handed to the reduction tree.
+struct Acc {
+    f32x2 S2, W2, D2, Sr2;
+    float m, mr;  // warp-wide maxima: the same in every lane of a warp
+    float G;      // this lane's mass in the current chunk of the sampling log, at maximum m
+};
+
+__device__ __forceinline__ Acc acc_empty() {
+    Acc a;
+    a.S2 = a.W2 = a.D2 = a.Sr2 = pack2(0.f, 0.f);
+    a.m = a.mr = NRL_NEG_INF;
+    a.G = 0.f;
+    return a;
+}
+
+__device__ __forceinline__ Partial acc_to_partial(const Acc& a) {
+    Partial p;
+    float x0, x1;
+    unpack2(a.S2, x0, x1);
+    p.S = x0 + x1;
+    unpack2(a.W2, x0, x1);
+    p.W = x0 + x1;
+    unpack2(a.D2, x0, x1);
+    p.D = x0 + x1;
+    unpack2(a.Sr2, x0, x1);
+    p.Sr = x0 + x1;
+    p.m = a.m;
+    p.mr = a.mr;
+    return p;
+}
+
+// move the policy sums to a larger (or NaN) maximum mn
+__device__ __forceinline__ void acc_rebase(Acc& a, float mn) {
+    if (a.m != mn) {
+        if (a.m == NRL_NEG_INF) {
+            a.S2 = a.W2 = a.D2 = pack2(0.f, 0.f);
+            a.G = 0.f;
+        } else {
+            const float dm = a.m - mn;
+            const float c = expf(dm);  // accurate: a warp's maximum grows only ~ln(n) times per row
+            const f32x2 c2 = pack2(c, c);
+            a.W2 = mul2(fma2(a.S2, pack2(dm, dm), a.W2), c2);
+            a.S2 = mul2(a.S2, c2);
+            a.D2 = mul2(a.D2, c2);
+            a.G *= c;
+        }
+        a.m = mn;
+    }
+}
+__device__ __forceinline__ void acc_rebase_ref(Acc& a, float mn) {
+    if (a.mr != mn) {
+        if (a.mr == NRL_NEG_INF) {
+            a.Sr2 = pack2(0.f, 0.f);
+        } else {
+            const float c = expf(a.mr - mn);
+            a.Sr2 = mul2(a.Sr2, pack2(c, c));
+        }
+        a.mr = mn;
+    }
+}
+
+// Fold one vector per lane into the lanes' partials. Called by all 32 lanes of a warp together
+// (a lane without work passes −FLT_MAX everywhere). Values are finite or −FLT_MAX (excluded);
+// real −inf logits are rare and are made safe in the slow block below.
+//
+// The running maxima are warp-wide: when some lane's vector exceeds the current maximum, every
+// lane moves to the warp's new maximum at once. A warp's maximum grows only ~ln(n) times over a
+// row, so one vote per vector keeps the rebase (an accurate expf), the −inf handling and the
+// first-data case off the common path; with per-lane maxima a warp would take that path at
+// almost every step. The common path is packed f32x2 arithmetic and 3-input min/max.
+template <bool REF, bool LOG>
+__device__ __forceinline__ void accumulate(Acc& a, float z[8], float zr[8]) {
     float vmax = fmax3_nan(fmax3_nan(fmax3_nan(z[0], z[1], z[2]), z[3], z[4]), fmax3_nan(z[5], z[6], z[7]), z[0]);
-    if (vmax != NRL_NEG_INF) {  // something allowed here (or a NaN)
-        if (!(vmax <= a.m)) partial_rebase(a.m, a.S, a.W, a.D, fmax_nan(a.m, vmax));
+    const float vmin = fmin3(fmin3(fmin3(z[0], z[1], z[2]), z[3], z[4]), fmin3(z[5], z[6], z[7]), z[0]);
+    float rmax = NRL_NEG_INF;
+    if (REF) rmax = fmax3_nan(fmax3_nan(fmax3_nan(zr[0], zr[1], zr[2]), zr[3], zr[4]), fmax3_nan(zr[5], zr[6], zr[7]), zr[0]);
+    const bool slow = !(vmax <= a.m) || vmin == NRL_NEG_INF || (REF && !(rmax <= a.mr));
+    if (__any_sync(0xffffffffu, slow)) {
+        if (vmin == NRL_NEG_INF) {
+            // −inf logits: make them finite (exp underflows to exactly 0 either way) and keep
+            // 0·inf and inf − inf out of the entropy and KL sums. The reference's entry is only
+            // touched where the policy's was −inf, so a token the policy can draw but the
+            // reference excludes still gives KL = +inf.
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (z[i] == NRL_NEG_INF) {
+                    z[i] = -FLT_MAX;
+                    if (REF) zr[i] = fmaxf(zr[i], -FLT_MAX);
+                }
+            }
+            vmax = fmax_nan(vmax, -FLT_MAX);
+        }
+        const float wm = warp_max_nan(vmax);
+        if (!(wm <= -FLT_MAX)) acc_rebase(a, fmax_nan(a.m, wm));
+        if (REF) {
+            const float wr = warp_max_nan(rmax);
+            if (wr != NRL_NEG_INF && !(wr <= -FLT_MAX)) acc_rebase_ref(a, fmax_nan(a.mr, wr));
+        }
+    }
+    const f32x2 l2e = pack2(kLog2e, kLog2e);
+    if (!(vmax <= -FLT_MAX)) {  // something allowed here (or a NaN)
         const f32x2 m2 = pack2(a.m, a.m);
-        f32x2 s2 = pack2(0.f, 0.f), w2 = s2, d2 = s2;
+        const f32x2 before = a.S2;
 #pragma unroll
         for (int i = 0; i < 8; i += 2) {
-            // −inf → finite, so 0·(−inf) never appears
-            f32x2 zc = pack2(fmaxf(z[i], -FLT_MAX), fmaxf(z[i + 1], -FLT_MAX));
-            f32x2 t = sub2(zc, m2);
+            const f32x2 zz = pack2(z[i], z[i + 1]);
+            const f32x2 t = sub2(zz, m2);
             float a0, a1;
             unpack2(mul2(t, l2e), a0, a1);
-            float e0 = ex2_approx(a0), e1 = ex2_approx(a1);
-            f32x2 e = pack2(e0, e1);
-            s2 = add2(s2, e);
-            w2 = fma2(e, t, w2);
-            if (REF) {
-                float d0, d1;
-                unpack2(sub2(zc, pack2(zr[i], zr[i + 1])), d0, d1);
-                // a zero-probability token contributes 0 whatever the reference holds there
-                d2 = fma2(e, pack2(e0 > 0.f ? d0 : 0.f, e1 > 0.f ? d1 : 0.f), d2);
-            }
+            const f32x2 e = pack2(ex2_approx(a0), ex2_approx(a1));
+            a.S2 = add2(a.S2, e);
+            a.W2 = fma2(e, t, a.W2);
+            if (REF) a.D2 = fma2(e, sub2(zz, pack2(zr[i], zr[i + 1])), a.D2);
         }
-        float x0, x1;
-        unpack2(s2, x0, x1);
-        a.S += x0 + x1;
-        unpack2(w2, x0, x1);
-        a.W += x0 + x1;
-        if (REF) {
-            unpack2(d2, x0, x1);
-            a.D += x0 + x1;
+        if (LOG) {  // what this vector added to the lane's mass, for the sampling log
+            float d0, d1;
+            unpack2(sub2(a.S2, before), d0, d1);
+            a.G += d0 + d1;
         }
     }
     if (REF) {
-        float rmax = fmax3_nan(fmax3_nan(fmax3_nan(zr[0], zr[1], zr[2]), zr[3], zr[4]), fmax3_nan(zr[5], zr[6], zr[7]), zr[0]);
-        if (rmax != NRL_NEG_INF) {
-            if (!(rmax <= a.mr)) partial_rebase_ref(a.mr, a.Sr, fmax_nan(a.mr, rmax));
+        if (rmax != NRL_NEG_INF && !(rmax <= -FLT_MAX)) {
             // (zr − mr) first, then the scale: folding mr·log2e into one fma would shift every
             // term of the row by the rounding of that product, and ln Zr with it
             const f32x2 mr2 = pack2(a.mr, a.mr);
-            f32x2 s2 = pack2(0.f, 0.f);
 #pragma unroll
             for (int i = 0; i < 8; i += 2) {
                 float a0, a1;
                 unpack2(mul2(sub2(pack2(zr[i], zr[i + 1]), mr2), l2e), a0, a1);
-                s2 = add2(s2, pack2(ex2_approx(a0), ex2_approx(a1)));
+                a.Sr2 = add2(a.Sr2, pack2(ex2_approx(a0), ex2_approx(a1)));
             }
-            float x0, x1;
-            unpack2(s2, x0, x1);
-            a.Sr += x0 + x1;
         }
     }
 }
@@ -176,7 +267,7 @@ __device__ __forceinline__ void stream_block(const FwdParams& p, uint64_t row, u
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     uint32_t begin, end;
     part_range(p, split * kWarps + warp, begin, end);
-    Partial acc = partial_empty();
+    Acc acc = acc_empty();
     // Software pipeline: kDepth tiles of this lane's loads are in flight while one is reduced
     // (about 64 KB per SM with two resident blocks: what HBM latency × bandwidth asks for).
 #ifdef NRL_DEPTH
@@ -189,21 +280,141 @@ __device__ __forceinline__ void stream_block(const FwdParams& p, uint64_t row, u
 #pragma unroll
     for (int d = 0; d < kDepth; d++)
         if (v + d * kTile < end) buf[d].load(p, row, v + d * kTile, end);
-    while (v < end) {
+    for (uint32_t t0 = begin; t0 < end;) {  // t0: warp-uniform tile base
 #pragma unroll
         for (int d = 0; d < kDepth; d++) {
-            if (v < end) {
+            if (t0 < end) {
                 float z[8], zr[8];
-                buf[d].values(p, z, zr);
-                accumulate<REF>(acc, z, zr);
+                if (v < end) {
+                    buf[d].values(p, z, zr);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) z[i] = zr[i] = -FLT_MAX;
+                }
+                accumulate<REF, false>(acc, z, zr);
                 uint32_t vn = v + kDepth * kTile;
                 if (vn < end) buf[d].load(p, row, vn, end);
             }
             v += kTile;
+            t0 += kTile;
         }
     }
-    acc = partial_warp_reduce(acc);
-    if (lane == 0) sp[warp] = acc;
+    const Partial part = partial_warp_reduce(acc_to_partial(acc));
+    if (lane == 0) sp[warp] = part;
+}
+
+// The unmasked fast path: each warp streams its part through a 4 KB ring in shared memory filled
+// by asynchronous 16-byte copies (cp.async). A lane only ever reads back the bytes it copied
+// itself, so its own wait_group is the only synchronisation. The ring keeps 4 KB per warp —
+// 128 KB per SM with four resident blocks — in flight without holding registers, which is what
+// lets the loads run far enough ahead of the arithmetic.
+constexpr int kRingRows = 8;  // rows of 32 lanes × 16 B per warp
+
+// The sampling log (shared memory, fused kernel only). While a warp streams its part it records,
+// per chunk of the part and per lane, the mass the lane added in that chunk (relative to the
+// warp's maximum at the chunk's end, also recorded). After the row's total is known, the chunk
+// that holds u·Z is found from these numbers and only that chunk is read again — by one warp —
+// instead of the whole part by the whole block. A chunk is a run of `tiles_per_chunk` tiles on
+// the unmasked path (entries unused) or one batch of 32 queued vectors on the masked path
+// (`entry` holds each lane's vector). A part that outgrows the log marks it overflowed and the
+// block falls back to re-reading the whole part.
+constexpr uint32_t kLogOverflow = 0xffffffffu;
+constexpr uint32_t kNoEntry = 0xffffffffu;
+
+template <int N, bool ENTRIES>
+struct SampleLog {
+    float mass[kWarps][N][32];
+    uint32_t entry[ENTRIES ? kWarps : 1][ENTRIES ? N : 1][32];
+    float cmax[kWarps][N];
+    uint32_t count[kWarps];
+    uint32_t tiles_per_chunk[kWarps];
+};
+constexpr int kLogDense = 64 / kWarps;     // chunks per part, unmasked path
+constexpr int kLogCompact = 128 / kWarps;  // batches per part, masked path
+typedef SampleLog<kLogDense, false> DenseLog;
+typedef SampleLog<kLogCompact, true> CompactLog;
+
+template <int DT, bool REF, bool LOG>
+__device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint4* ring, DenseLog* log) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int kPer = (DT == NRL_F32 ? 2 : 1);     // 16-byte pieces per lane per stream per tile
+    constexpr int kRows = kPer * (REF ? 2 : 1);       // ring rows one tile takes
+    constexpr int kSlots = kRingRows / kRows;         // tiles in flight
+    constexpr uint32_t kEsize = (DT == NRL_F32 ? 4 : 2);
+    uint32_t begin, end;
+    part_range(p, split * kWarps + warp, begin, end);
+    Acc acc = acc_empty();
+    const uint32_t base = smem_addr(ring + warp * (kRingRows * 32) + lane);  // this lane's column of the ring
+    const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kVec) * kEsize;
+    const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kVec) * kEsize : nullptr;
+    uint32_t v = begin + lane * kVec;  // the tile this lane consumes next
+    // sampling log: chunks of `gsz` tiles, at most kLogDense of them
+    const uint32_t ntiles = (end - begin + kTile - 1) / kTile;
+    const uint32_t gsz = (ntiles + kLogDense - 1) / kLogDense;
+    uint32_t left = gsz, chunk = 0;
+    auto flush = [&]() {
+        log->mass[warp][chunk][lane] = acc.G;
+        if (lane == 0) log->cmax[warp][chunk] = acc.m;
+        acc.G = 0.f;
+        chunk++;
+        left = gsz;
+    };
+    auto issue = [&](int slot, uint32_t vv, const char* xq, const char* rq) {
+        if (vv < end) {
+#pragma unroll
+            for (int k = 0; k < kPer; k++) {
+                cp_async16(base + (slot * kRows + k) * 512, xq + 16 * k);
+                if (REF) cp_async16(base + (slot * kRows + kPer + k) * 512, rq + 16 * k);
+            }
+        }
+        cp_async_commit();  // one group per tile, empty or not, so that the group count stays in step
+    };
+#pragma unroll
+    for (int s = 0; s < kSlots; s++) issue(s, v + s * kTile, xp + (size_t)s * kTile * kEsize, REF ? rp + (size_t)s * kTile * kEsize : nullptr);
+    for (uint32_t t0 = begin; t0 < end; t0 += kSlots * kTile) {  // warp-uniform
+#pragma unroll
+        for (int s = 0; s < kSlots; s++) {
+            cp_async_wait<kSlots - 1>();  // the oldest tile has landed
+            if (t0 + s * kTile < end) {  // warp-uniform: the tile exists
+                Raw<DT> x, r;
+                if constexpr (DT == NRL_F32) {
+                    x.a = lds16(base + (s * kRows) * 512);
+                    x.b = lds16(base + (s * kRows + 1) * 512);
+                    if (REF) {
+                        r.a = lds16(base + (s * kRows + 2) * 512);
+                        r.b = lds16(base + (s * kRows + 3) * 512);
+                    }
+                } else {
+                    x.q = lds16(base + (s * kRows) * 512);
+                    if (REF) r.q = lds16(base + (s * kRows + 1) * 512);
+                }
+                float z[8], zr[8];
+                x.unpack(z);
+                if (REF) r.unpack(zr);
+                if (v >= end) {  // a lane past the end of a ragged last tile: nothing copied, nothing to add
+#pragma unroll
+                    for (int i = 0; i < 8; i++) z[i] = zr[i] = -FLT_MAX;
+                }
+                accumulate<REF, LOG>(acc, z, zr);
+                if (LOG && --left == 0) flush();
+            }
+            // refill the slot just consumed with the tile kSlots ahead
+            issue(s, v + kSlots * kTile, xp + (size_t)kSlots * kTile * kEsize, REF ? rp + (size_t)kSlots * kTile * kEsize : nullptr);
+            v += kTile;
+            xp += (size_t)kTile * kEsize;
+            if (REF) rp += (size_t)kTile * kEsize;
+        }
+    }
+    cp_async_wait<0>();
+    if (LOG) {
+        if (left != gsz) flush();
+        if (lane == 0) {
+            log->count[warp] = chunk;
+            log->tiles_per_chunk[warp] = gsz;
+        }
+    }
+    const Partial part = partial_warp_reduce(acc_to_partial(acc));
+    if (lane == 0) sp[warp] = part;
 }
 
 // The same for rows with a byte allow-mask, when most of the vocabulary is excluded (grammar
@@ -218,17 +429,18 @@ __device__ __forceinline__ void stream_block(const FwdParams& p, uint64_t row, u
 constexpr int kQueue = 256;  // ring entries per warp: 31 left over + 4 tiles × 32 lanes, rounded up
 constexpr int kAhead = 4;    // mask tiles scanned per group
 
-template <int DT, bool REF>
-__device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* queue) {
+template <int DT, bool REF, bool LOG>
+__device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* queue, CompactLog* log) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t lt = (1u << lane) - 1u;
     uint32_t begin, end;
     part_range(p, split * kWarps + warp, begin, end);
     uint32_t* wq = queue + warp * kQueue;
     typedef VecLoader<DT, REF, true, false, true> Loader;
-    Partial acc = partial_empty();
+    Acc acc = acc_empty();
     Loader pend;
     bool pend_ok = false, pend_any = false;
+    uint32_t pend_v = kNoEntry, batch = 0;  // the vector this lane holds in `pend`; batches folded so far
     uint32_t head = 0, count = 0;  // warp-uniform ring state
 
     // this lane's mask bytes of the tile at `v`: pointer arithmetic is one 64-bit add per group
@@ -275,23 +487,40 @@ __device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_
             const uint32_t n = count < 32 ? count : 32;
             Loader nxt;
             const bool ok = (uint32_t)lane < n;
-            if (ok) nxt.load(p, row, wq[(head + lane) & (kQueue - 1)], end);
+            const uint32_t nv_entry = ok ? wq[(head + lane) & (kQueue - 1)] : kNoEntry;
+            if (ok) nxt.load(p, row, nv_entry, end);
             head = (head + n) & (kQueue - 1);
             count -= n;
-            if (pend_any && pend_ok) {
+            if (pend_any) {  // warp-uniform; lanes without an entry fold an empty vector
                 float z[8], zr[8];
-                pend.values(p, z, zr);
-                accumulate<REF>(acc, z, zr);
+                if (pend_ok) {
+                    pend.values(p, z, zr);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 8; i++) z[i] = zr[i] = -FLT_MAX;
+                }
+                accumulate<REF, LOG>(acc, z, zr);
+                if (LOG) {  // one log chunk per batch: the lane's vector and what it added
+                    if (batch < (uint32_t)kLogCompact) {
+                        log->mass[warp][batch][lane] = acc.G;
+                        log->entry[warp][batch][lane] = pend_v;
+                        if (lane == 0) log->cmax[warp][batch] = acc.m;
+                    }
+                    acc.G = 0.f;
+                    batch++;
+                }
             }
             pend = nxt;
+            pend_v = nv_entry;
             pend_ok = ok;
             pend_any = n > 0;
         }
         if (!scanning) break;
         __syncwarp();  // the batch's entries are read before the next group's pushes can reuse slots
     }
-    acc = partial_warp_reduce(acc);
-    if (lane == 0) sp[warp] = acc;
+    if (LOG && lane == 0) log->count[warp] = batch <= (uint32_t)kLogCompact ? batch : kLogOverflow;
+    const Partial part = partial_warp_reduce(acc_to_partial(acc));
+    if (lane == 0) sp[warp] = part;
 }
 
 struct RowResult {

@@ -2,6 +2,8 @@
 // few long rows are split over several blocks (stage 1 leaves part partials in scratch memory,
 // stage 2 merges them and picks the token).
 #pragma once
+#include <type_traits>
+
 #include "row_fwd.cuh"
 
 namespace nrl {
@@ -13,6 +15,8 @@ struct PickShared {
     uint32_t first_idx[kWarps];
     int32_t token;
     int32_t last_token;
+    uint32_t chunk_a, chunk_b;  // unmasked path: the chunk warp 0 found, re-read by the whole block
+    double chunk_resid;
     float z_tok, zr_tok;
 };
 
@@ -49,12 +53,9 @@ __device__ __forceinline__ float vector_mass(const FwdParams& p, const VecLoader
 }
 
 template <int DT, bool ALLOW, bool GENERAL, bool VEC>
-__device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, const RowResult& res, PickShared* ps) {
+__device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, uint32_t a, uint32_t b, float m, double resid, PickShared* ps) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     typedef VecLoader<DT, false, ALLOW, GENERAL, VEC> Loader;
-    uint32_t a, b;
-    part_range(p, res.part, a, b);
-    const float m = res.m;
     const uint8_t* mrow = ALLOW ? p.allow + row * p.allow_stride : nullptr;
     double base = 0.0;  // mass of the rounds before this one (block-uniform)
     if (tid == 0) ps->last_token = -1;
@@ -96,7 +97,7 @@ __device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, co
             total += ps->warp_tot[w];
         }
         double excl = before + (incl - s);
-        bool claim = s > 0.0 && (excl + s > res.resid);
+        bool claim = s > 0.0 && (excl + s > resid);
         uint32_t cb = __ballot_sync(0xffffffffu, claim);
         uint32_t mb = __ballot_sync(0xffffffffu, s > 0.0);
         if (lane == 0) {
@@ -120,7 +121,7 @@ __device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, co
             for (int k = 0; k < kPickVec; k++) {
                 if (vm[k] > 0.f) {
                     klast = k;
-                    if (kk < 0 && crossing && c + (double)vm[k] > res.resid) kk = k;
+                    if (kk < 0 && crossing && c + (double)vm[k] > resid) kk = k;
                     if (kk < 0) c += (double)vm[k];
                 }
             }
@@ -141,7 +142,7 @@ __device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, co
                         float e = ex2_approx(t * kLog2e);
                         if (e > 0.f) last = (int32_t)(v + i);
                         c += (double)e;
-                        if (tok < 0 && !take_last && c > res.resid) tok = (int32_t)(v + i);
+                        if (tok < 0 && !take_last && c > resid) tok = (int32_t)(v + i);
                     }
                 }
                 if (crossing) ps->token = tok >= 0 ? tok : last;
@@ -155,6 +156,113 @@ __device__ __forceinline__ void pick_sample(const FwdParams& p, uint64_t row, co
     // no crossing in any round (rounding only): the last token with mass seen
     if (tid == 0) ps->token = ps->last_token;
     __syncthreads();
+}
+
+// Sampling from the log the streaming pass left (fused kernel): warp 0 alone finds the chunk of
+// part `res.part` that holds res.resid from the logged chunk masses, reads that one chunk again
+// (up to tiles_per_chunk vectors per lane on the unmasked path, one queued vector per lane on
+// the masked path) and walks to the token. Index order inside a chunk is (tile, lane, element).
+// Returns false (block-uniform, nothing written) if the part outgrew the log.
+template <int DT, bool ALLOW, class Log>
+__device__ __forceinline__ bool pick_logged(const FwdParams& p, uint64_t row, const RowResult& res, const Log* log, PickShared* ps) {
+    typedef VecLoader<DT, false, ALLOW, false, true> Loader;
+    const uint32_t w = res.part;
+    const uint32_t n = log->count[w];
+    if (n == kLogOverflow) return false;
+    if (threadIdx.x >= 32) return true;
+    const int lane = threadIdx.x;
+    const float m = res.m;
+    uint32_t begin, end;
+    part_range(p, w, begin, end);
+    // the chunk: running prefix of chunk masses at the row maximum, lower chunks first
+    double prefix = 0.0, r2 = 0.0;
+    int cstar = -1, clast = -1;
+    for (uint32_t c = 0; c < n; c++) {
+        const float cm = log->cmax[w][c];
+        double x = cm == NRL_NEG_INF ? 0.0 : (double)log->mass[w][c][lane] * (double)expf(cm - m);
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) x += __shfl_xor_sync(0xffffffffu, x, s);
+        if (x > 0.0) clast = (int)c;
+        if (cstar < 0 && prefix + x > res.resid) {
+            cstar = (int)c;
+            r2 = res.resid - prefix;
+        }
+        if (cstar < 0) prefix += x;
+    }
+    const bool take_last = cstar < 0;  // rounding only: the last token with mass of the last chunk with mass
+    if (take_last) cstar = clast;
+    if (cstar < 0) {  // the part holds no mass at all: no token
+        if (lane == 0) {
+            ps->token = -1;
+            ps->chunk_a = ps->chunk_b = 0;
+            ps->chunk_resid = 0.0;
+        }
+        return true;
+    }
+    if constexpr (!ALLOW) {
+        // unmasked path: hand the chunk's element range to the whole block (one vector per thread
+        // when a chunk is 8 tiles), which scans it like a small part
+        if (lane == 0) {
+            const uint32_t tiles = log->tiles_per_chunk[w];
+            const uint32_t ca = begin + (uint32_t)cstar * tiles * kTile;
+            const uint32_t cb = ca + tiles * kTile;
+            ps->chunk_a = ca < end ? ca : end;
+            ps->chunk_b = cb < end ? cb : end;
+            ps->chunk_resid = take_last ? 1e300 : r2;
+        }
+        return true;
+    } else {
+    // masked path: the chunk is one batch, lane l holds its queued vector
+    double run = 0.0;
+    int32_t token = -1, last = -1;
+    {
+        Loader ld;
+        const uint32_t vv = log->entry[w][cstar][lane];
+        if (vv != kNoEntry) ld.load(p, row, vv, end);
+        float e[8];
+        double s = 0.0;
+        if (vv != kNoEntry) {
+            float z[8], zr[8];
+            ld.values(p, z, zr);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                e[i] = ex2_approx((fmaxf(z[i], -FLT_MAX) - m) * kLog2e);
+                s += (double)e[i];
+                if (e[i] > 0.f) last = (int32_t)(vv + i);
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) e[i] = 0.f;
+        }
+        const double incl = warp_scan_incl(s, lane);
+        const bool mine = !take_last && s > 0.0 && run + incl > r2;
+        const uint32_t ball = __ballot_sync(0xffffffffu, mine);
+        if (ball) {
+            const int owner = __ffs(ball) - 1;
+            int32_t tok = -1;
+            if (lane == owner) {
+                double c = run + (incl - s);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    c += (double)e[i];
+                    if (tok < 0 && e[i] > 0.f && c > r2) tok = (int32_t)(vv + i);
+                }
+                if (tok < 0) tok = last;  // rounding inside the vector
+            }
+            token = __shfl_sync(0xffffffffu, tok, owner);
+        }
+    }
+    if (token < 0) {  // no crossing (rounding): the last token with mass in the batch
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            int32_t o = __shfl_xor_sync(0xffffffffu, last, s);
+            last = o > last ? o : last;
+        }
+        token = last;
+    }
+    if (lane == 0) ps->token = token;
+    return true;
+    }
 }
 
 // All threads of the block: find the token inside part `res.part`.
@@ -202,7 +310,7 @@ __device__ __forceinline__ void pick_token(const FwdParams& p, uint64_t row, con
         return;
     }
 
-    pick_sample<DT, ALLOW, GENERAL, VEC>(p, row, res, ps);
+    pick_sample<DT, ALLOW, GENERAL, VEC>(p, row, a, b, res.m, res.resid, ps);
 }
 
 // Thread 0 writes the row's outputs.
@@ -219,8 +327,9 @@ __device__ __forceinline__ void write_row(const FwdParams& p, uint64_t row, cons
         } else {
             float z, zr;
             load_one<DT, REF, ALLOW, GENERAL>(p, row, (uint32_t)tok, z, zr);
-            lp = (z - res.m) - res.lnZ;
-            if (REF) rlp = (zr - res.mr) - res.lnZr;
+            // an excluded token (−inf logit, or masked out: −FLT_MAX inside the kernels) has log-prob −inf
+            lp = z <= -FLT_MAX ? NRL_NEG_INF : (z - res.m) - res.lnZ;
+            if (REF) rlp = zr <= -FLT_MAX ? NRL_NEG_INF : (zr - res.mr) - res.lnZr;
         }
     }
     bool bad = (status & 3u) != 0;
@@ -237,12 +346,29 @@ __device__ __forceinline__ void write_row(const FwdParams& p, uint64_t row, cons
 }
 
 // Streams a block's range of a row: byte-masked rows on the vectorised fast path go through the
-// compacting scan, everything else through the plain tile loop.
+// compacting scan, unmasked ones through the asynchronous ring, everything else through the plain
+// tile loop. With LOG the fast paths also leave the sampling log for pick_logged.
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
-__device__ __forceinline__ void stream_row(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp) {
-    if constexpr (ALLOW && VEC && !GENERAL) {
-        __shared__ uint32_t queue[kWarps * kQueue];
-        stream_block_compact<DT, REF>(p, row, split, sp, queue);
+struct FastPath {
+    static constexpr bool compact = ALLOW && VEC && !GENERAL;
+    static constexpr bool ring = !ALLOW && VEC && !GENERAL;
+    typedef typename std::conditional<compact, CompactLog, DenseLog>::type Log;
+};
+
+// the staging area a fast path needs in shared memory: the vector queue or the copy ring
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+struct Stage {
+    typedef FastPath<DT, REF, ALLOW, GENERAL, VEC> F;
+    static constexpr int words = F::compact ? kWarps * kQueue : (F::ring ? kWarps * kRingRows * 32 * 4 : 4);
+};
+
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC, bool LOG>
+__device__ __forceinline__ void stream_row(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* stage, typename FastPath<DT, REF, ALLOW, GENERAL, VEC>::Log* log) {
+    typedef FastPath<DT, REF, ALLOW, GENERAL, VEC> F;
+    if constexpr (F::compact) {
+        stream_block_compact<DT, REF, LOG>(p, row, split, sp, stage, log);
+    } else if constexpr (F::ring) {
+        stream_block_async<DT, REF, LOG>(p, row, split, sp, reinterpret_cast<uint4*>(stage), log);
     } else {
         stream_block<DT, REF, ALLOW, GENERAL, VEC>(p, row, split, sp);
     }
@@ -251,16 +377,43 @@ __device__ __forceinline__ void stream_row(const FwdParams& p, uint64_t row, uin
 // ---- fused: one block per row ---------------------------------------------------------------
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 __global__ void __launch_bounds__(kThreads, 1024 / kThreads) row_fwd_fused(FwdParams p) {
+    typedef FastPath<DT, REF, ALLOW, GENERAL, VEC> F;
+    // The log pays off on the masked path (one queued vector per lane to re-read). On the unmasked
+    // path the whole-part scan by the full block measured faster, so that path does not log.
+    constexpr bool kLogged = F::compact;
     __shared__ Partial sp[kWarps];
     __shared__ RowResult res;
     __shared__ PickShared ps;
+    __shared__ typename std::conditional<kLogged, typename F::Log, int>::type slog;
+    __shared__ __align__(16) uint32_t stage[Stage<DT, REF, ALLOW, GENERAL, VEC>::words];
     const uint64_t row = blockIdx.x;
-    stream_row<DT, REF, ALLOW, GENERAL, VEC>(p, row, 0, sp);
+    const bool sampling = (p.flags & NRL_FWD_SAMPLE) != 0;
+    if constexpr (kLogged) {
+        if (sampling) stream_row<DT, REF, ALLOW, GENERAL, VEC, true>(p, row, 0, sp, stage, &slog);
+        else stream_row<DT, REF, ALLOW, GENERAL, VEC, false>(p, row, 0, sp, stage, &slog);
+    } else {
+        stream_row<DT, REF, ALLOW, GENERAL, VEC, false>(p, row, 0, sp, stage, nullptr);
+    }
     __syncthreads();
     if (threadIdx.x < 32) finalize_row(p, row, kWarps, [&](uint32_t q) { return sp[q]; }, &res);
     __syncthreads();
     const bool pick = !res.status && (p.flags & (NRL_FWD_SAMPLE | NRL_FWD_GREEDY));
-    if (pick) pick_token<DT, REF, ALLOW, GENERAL, VEC>(p, row, res, &ps);
+    if (pick) {
+        bool done = false;
+        if constexpr (kLogged) {
+            if (sampling) {
+                done = pick_logged<DT, ALLOW>(p, row, res, &slog, &ps);
+                if constexpr (F::ring) {
+                    if (done) {
+                        __syncthreads();
+                        pick_sample<DT, ALLOW, GENERAL, VEC>(p, row, ps.chunk_a, ps.chunk_b, res.m, ps.chunk_resid, &ps);
+                    }
+                }
+            }
+        }
+        if (!done) pick_token<DT, REF, ALLOW, GENERAL, VEC>(p, row, res, &ps);
+        __syncthreads();
+    }
     if (threadIdx.x == 0) write_row<DT, REF, ALLOW, GENERAL>(p, row, res, pick ? ps.token : -1);
 }
 
@@ -270,7 +423,8 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) row_fwd_parts(FwdPa
     __shared__ Partial sp[kWarps];
     const uint64_t row = blockIdx.x / p.nsplit;
     const uint32_t split = blockIdx.x % p.nsplit;
-    stream_row<DT, REF, ALLOW, GENERAL, VEC>(p, row, split, sp);
+    __shared__ __align__(16) uint32_t stage[Stage<DT, REF, ALLOW, GENERAL, VEC>::words];
+    stream_row<DT, REF, ALLOW, GENERAL, VEC, false>(p, row, split, sp, stage, nullptr);
     __syncthreads();
     if (threadIdx.x < kWarps) {
         Partial a = sp[threadIdx.x];
