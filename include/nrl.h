@@ -174,6 +174,9 @@ typedef struct nrl_row_bwd_args {
     nrl_devptr g_kl;     /* f32 [rows] or 0 */
     nrl_devptr g_ent;    /* f32 [rows] or 0 */
     nrl_devptr d_logits; /* out f32 [rows, V] */
+    uint32_t accumulate; /* 1: add into d_logits instead of overwriting it (the tape's `new + old`,
+                            src/tensor/autodiff.rs:198-201, without a separate pass) */
+    uint32_t reserved0;
 } nrl_row_bwd_args;
 
 int nrl_row_bwd(const nrl_row_bwd_args* args, nrl_stream stream);
@@ -205,7 +208,7 @@ typedef struct nrl_token_loss_args {
     double dual;          /* PPO: dual-clip constant c > 1, used when has_dual */
     double clamp;         /* PPO: log-ratio clamp; K*: δ clamp; used when has_clamp */
     uint32_t has_clamp;
-    uint32_t reserved0;
+    uint32_t accumulate;  /* 1: add into dloss_dlogp instead of overwriting it (a logp tensor that feeds two losses) */
     nrl_devptr loss;      /* out f32 [S,B,T], 0 at unscored positions; or 0 */
     nrl_devptr upstream;  /* f32 [S,B,T] gradient of the per-token loss (from nrl_reduce_tokens_bwd), or 0 for ones */
     nrl_devptr dloss_dlogp; /* out f32 [S,B,T] = upstream · d loss / d logp; or 0 */

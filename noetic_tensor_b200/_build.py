@@ -56,6 +56,30 @@ def build(force=False, verbose=False):
     return LIB
 
 
+HOST_HEADER = os.path.join(HERE, "host", "noetic_rl.hpp")
+
+
+def build_host_program(source, out):
+    """Compiles a C++ program that uses host/noetic_rl.hpp (the C++ mirror of `nn::rl`) and links
+    it against libnrl.so and the CUDA runtime. g++ only: the header holds no device code."""
+    build()
+    deps = [source, HOST_HEADER, INCLUDE, LIB]
+    if os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
+        return out
+    os.makedirs(os.path.dirname(out), exist_ok=True)
+    cuda = os.path.dirname(os.path.dirname(nvcc_path()))
+    cmd = [
+        "g++", "-std=c++17", "-O1", "-Wall", "-Wextra", "-I", os.path.join(cuda, "include"), source, "-o", out,
+        "-L", HERE, "-l:libnrl.so", "-L", os.path.join(cuda, "lib64"), "-lcudart",
+        "-Wl,-rpath,$ORIGIN/" + os.path.relpath(HERE, os.path.dirname(out)), "-Wl,-rpath," + os.path.join(cuda, "lib64"),
+    ]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("g++ failed building " + os.path.basename(out))
+    return out
+
+
 if __name__ == "__main__":
     build(force=True, verbose="-v" in sys.argv)
     print(LIB)

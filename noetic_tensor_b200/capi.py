@@ -34,7 +34,7 @@ class RowBwdArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("dtype", u32), ("V", u32), ("temperature", f32), ("rows", u64),
         ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
-        ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr),
+        ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr), ("accumulate", u32), ("reserved0", u32),
     ]
 
 
@@ -42,7 +42,7 @@ class TokenLossArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("kind", u32), ("S", u64), ("B", u64), ("T", u64),
         ("logp", ptr), ("other", ptr), ("weights", ptr), ("weights_per_sequence", u32), ("has_dual", u32), ("mask", ptr),
-        ("clip_low", f64), ("clip_high", f64), ("dual", f64), ("clamp", f64), ("has_clamp", u32), ("reserved0", u32),
+        ("clip_low", f64), ("clip_high", f64), ("dual", f64), ("clamp", f64), ("has_clamp", u32), ("accumulate", u32),
         ("loss", ptr), ("upstream", ptr), ("dloss_dlogp", ptr),
     ]
 

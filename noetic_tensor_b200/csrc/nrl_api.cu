@@ -250,6 +250,7 @@ extern "C" int nrl_row_bwd(const nrl_row_bwd_args* a, nrl_stream stream) {
     p.g_kl = (const float*)a->g_kl;
     p.g_ent = (const float*)a->g_ent;
     p.d_logits = (float*)a->d_logits;
+    p.accumulate = a->accumulate ? 1u : 0u;
     // blocks per row: about 16K elements each, so short rows are one block and long rows spread out
     uint32_t chunks = (a->V + 16383) / 16384;
     if (chunks < 1) chunks = 1;
@@ -291,6 +292,7 @@ static int fill_tok(TokParams& p, const nrl_token_loss_args* a) {
     p.w_per_seq = a->weights_per_sequence;
     p.has_dual = a->has_dual;
     p.has_clamp = a->has_clamp;
+    p.accumulate = a->accumulate ? 1u : 0u;
     p.ratio_lo = (float)(1.0 - a->clip_low);
     p.ratio_hi = (float)(1.0 + a->clip_high);
     p.neg_dual = (float)(-a->dual);

@@ -17,6 +17,7 @@ struct BwdParams {
     const float* g_ent;
     float* d_logits;
     uint32_t chunks_per_row;  // blocks per row
+    uint32_t accumulate;      // add into d_logits
 };
 
 constexpr int kBwdThreads = 256;
@@ -40,6 +41,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     const bool vec_out = VEC && ((reinterpret_cast<uintptr_t>(p.d_logits) & 15u) == 0);
 
     if (glp == 0.f && gkl == 0.f && gen == 0.f) {
+        if (p.accumulate) return;  // adding exact zeros
         // an unscored position: exact zeros, the inputs are not read
         for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
             if (vec_out) {
@@ -66,6 +68,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             mk.load(f.allow, row * f.allow_stride + v);
             const bool holds_token = tok >= (int32_t)v && tok < (int32_t)(v + kVec);  // its entry gets g_lp even if excluded
             if (!mk.any() && !holds_token) {
+                if (p.accumulate) continue;
                 if (vec_out) {
                     stg_stream16(out + v, 0.f, 0.f, 0.f, 0.f);
                     stg_stream16(out + v + 4, 0.f, 0.f, 0.f, 0.f);
@@ -91,6 +94,11 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             if ((int32_t)(v + i) == tok) d += glp;
             if (GENERAL && f.tau != 1.0f) d = __fdiv_rn(d, f.tau);
             g[i] = d;
+        }
+        if (p.accumulate) {
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (v + i < v_end) g[i] += out[v + i];
         }
         if (vec_out) {
             stg_stream16(out + v, g[0], g[1], g[2], g[3]);

@@ -19,6 +19,7 @@ struct TokParams {
     uint32_t w_per_seq;
     uint32_t has_dual;
     uint32_t has_clamp;
+    uint32_t accumulate;  // dloss += instead of =
     float ratio_lo, ratio_hi;  // (f32)(1 − low), (f32)(1 + high)
     float neg_dual;            // (f32)(−c)
     float clamp;
@@ -93,7 +94,10 @@ __global__ void token_loss_kernel(TokParams p) {
     }
     if (!scored) { per = 0.f; dl = 0.f; }  // zero_masked: a select, so garbage never leaks
     if (p.loss) p.loss[i] = per;
-    if (p.dloss) p.dloss[i] = (p.upstream && scored) ? p.upstream[i] * dl : dl;
+    if (p.dloss) {
+        float d = (p.upstream && scored) ? p.upstream[i] * dl : dl;
+        p.dloss[i] = p.accumulate ? p.dloss[i] + d : d;
+    }
 }
 
 // block-wide sum of (a, b) in a fixed tree; result valid on thread 0

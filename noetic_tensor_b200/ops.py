@@ -110,7 +110,7 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
     return out
 
 
-def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None):
+def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None, accumulate=False):
     """d(logits) [rows, V] f32 from the forward's saved statistics and per-row upstream gradients."""
     dev = logits.device
     rows, V = logits.shape
@@ -130,6 +130,7 @@ def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, tem
     else:
         _need(out, torch.float32, (rows, V), "d_logits", dev)
     a.d_logits = _p(out)
+    a.accumulate = 1 if accumulate else 0
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_row_bwd(C.byref(a), _stream(dev)), "nrl_row_bwd")
     return out
@@ -164,8 +165,9 @@ def _tok_args(kind, logp, other, weights, mask, clip_low=0.0, clip_high=0.0, dua
     return a
 
 
-def token_loss(kind, logp, *, other=None, weights=None, mask=None, clip_low=0.0, clip_high=0.0, dual=None, clamp=None, want_grad=True, upstream=None):
-    """Per-token loss [S,B,T] (0 at unscored positions) and upstream · its derivative w.r.t. logp."""
+def token_loss(kind, logp, *, other=None, weights=None, mask=None, clip_low=0.0, clip_high=0.0, dual=None, clamp=None, want_grad=True, upstream=None, accumulate_into=None):
+    """Per-token loss [S,B,T] (0 at unscored positions) and upstream · its derivative w.r.t. logp
+    (added into `accumulate_into` when that is given: a logp tensor that feeds two losses)."""
     dev = logp.device
     a = _tok_args(kind, logp, other, weights, mask, clip_low, clip_high, dual, clamp)
     if upstream is not None:
@@ -173,6 +175,9 @@ def token_loss(kind, logp, *, other=None, weights=None, mask=None, clip_low=0.0,
         a.upstream = _p(upstream)
     loss = torch.empty_like(logp)
     dl = torch.empty_like(logp) if want_grad else None
+    if accumulate_into is not None:
+        _need(accumulate_into, torch.float32, logp.shape, "accumulate_into", dev)
+        dl, a.accumulate = accumulate_into, 1
     a.loss, a.dloss_dlogp = _p(loss), _p(dl)
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_token_loss(C.byref(a), _stream(dev)), "nrl_token_loss")

@@ -36,7 +36,7 @@ def test_identity_calls_need_no_gpu():
 def test_struct_layouts():
     # sizes follow from the header's field lists (8-byte alignment, no packing)
     assert C.sizeof(capi.RowFwdArgs) == 4 * 4 + 8 + 4 + 4 + 16 * 8
-    assert C.sizeof(capi.RowBwdArgs) == 4 * 4 + 8 + 14 * 8
+    assert C.sizeof(capi.RowBwdArgs) == 4 * 4 + 8 + 14 * 8 + 8
     assert C.sizeof(capi.TokenLossArgs) == 8 + 3 * 8 + 3 * 8 + 8 + 8 + 4 * 8 + 8 + 3 * 8
 
 

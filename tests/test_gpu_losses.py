@@ -141,6 +141,11 @@ def test_policy_gradient_reductions_by_hand():
     assert red(capi.REDUCE_SEQUENCE_MEAN) == [-4.25]
     per2, _ = ops.token_loss(capi.LOSS_PG, lp, weights=w)
     assert ops.reduce_tokens(per2, None, capi.REDUCE_SUM).cpu().tolist() == [6.0 - 30.0]
+    # a log-prob tensor that feeds two losses: the second derivative is added into the first
+    ref = t32([-1.5, -2, -2, -4, -4, -7], (1, 2, 3))
+    _, dk = ops.token_loss(capi.LOSS_K1, lp, other=ref, mask=m)
+    _, both = ops.token_loss(capi.LOSS_K1, lp, other=ref, mask=m, accumulate_into=dl.clone())
+    assert torch.equal(both, dl + dk) and both.cpu().ravel().tolist() == [0.0, 0.0, 0.0, 0.0, 3.0, 0.0]
 
 
 def test_clipped_policy_loss_overflow_guards():

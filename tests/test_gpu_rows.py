@@ -241,3 +241,41 @@ def test_sampler_distribution_and_reproducibility(oracle):
     fr = np.bincount(f.tokens.cpu().numpy(), minlength=v) / draws
     assert fr[3] == 0
     assert np.all(np.abs(fr - p) <= 4.5 * np.sqrt(p * (1 - p) / draws) + 1e-12)
+
+
+@pytest.mark.parametrize("V,dtype,masked", [(1000, torch.float32, False), (4104, torch.bfloat16, True), (37, torch.bfloat16, False), (128256, torch.bfloat16, True)])
+def test_backward_accumulate_adds_into_d_logits(V, dtype, masked):
+    """Three separate backward calls adding into one d(logits) (what a tape does with three nodes
+    on the same logits) equal the single combined call to rounding, keep unscored rows and
+    excluded entries exactly as they were, and `accumulate` on a pre-filled buffer adds to it."""
+    from noetic_tensor_b200 import ops
+
+    g = np.random.default_rng(V)
+    rows = 24
+    x, _ = stored(g.normal(0, 2, (rows, V)), dtype)
+    r, _ = stored(g.normal(0, 2, (rows, V)), dtype)
+    m = None
+    if masked:
+        mm = (g.uniform(0, 1, (rows, V // 8)) < 0.5).repeat(8, axis=1)  # whole excluded vectors, as a grammar mask has
+        mm = np.concatenate([mm, np.ones((rows, V - mm.shape[1]), bool)], axis=1) & (g.uniform(0, 1, (rows, V)) < 0.9)
+        mm[:, 0] = True
+        m = to_dev(mm.astype(np.uint8), None)
+    f = ops.row_forward(x, ref_logits=r, allow=m, uniforms=to_dev(g.uniform(0, 1, rows).astype(np.float32), None))
+    score = to_dev((np.arange(rows) % 4 != 1).astype(np.float32), None)
+    glp, gkl, gen = score * 0.7, score * 0.04, score * -0.01
+    whole = ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=glp, g_kl=gkl, g_ent=gen)
+    d = ops.row_backward(x, f, allow=m, g_logp=glp)
+    base = d.clone()
+    assert ops.row_backward(x, f, ref_logits=r, allow=m, g_kl=gkl, out=d, accumulate=True) is d
+    ops.row_backward(x, f, allow=m, g_ent=gen, out=d, accumulate=True)
+    err = (d - whole).abs()
+    assert (err <= 1e-6 + 1e-5 * whole.abs()).all(), err.max().item()
+    assert not torch.equal(d, base)
+    assert (d[score == 0] == 0).all()
+    if m is not None:
+        assert (d[m == 0] == 0).all()
+    # adding onto a buffer that holds something else: rows with zero upstream keep it bit for bit
+    pre = torch.full_like(whole, 0.25)
+    ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=glp, g_kl=gkl, g_ent=gen, out=pre, accumulate=True)
+    assert torch.equal(pre[score == 0], torch.full_like(pre[score == 0], 0.25))
+    assert ((pre - 0.25 - whole).abs() <= 1e-6 + 1e-5 * whole.abs()).all()
