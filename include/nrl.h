@@ -177,6 +177,12 @@ typedef struct nrl_row_bwd_args {
     uint32_t accumulate; /* 1: add into d_logits instead of overwriting it (the tape's `new + old`,
                             src/tensor/autodiff.rs:198-201, without a separate pass) */
     uint32_t reserved0;
+    nrl_devptr g_uniform;    /* f32 [rows] or 0: upstream gradient of −mean_v log π_v (the label-smoothing
+                                term of cross_entropy_with, src/nn/loss.rs:70-72); adds g·(π_j − 1/V).
+                                Not with masks or a temperature (NRL_E_UNSUPPORTED) */
+    nrl_devptr d_ref_logits; /* out f32 [rows, V] or 0: gradient w.r.t. ref_logits of the KL term,
+                                g_kl·(ρ_j − π_j) (kl_div's prediction side, src/nn/loss.rs:175-183).
+                                With it, d_logits may be 0 (a detached teacher) */
 } nrl_row_bwd_args;
 
 int nrl_row_bwd(const nrl_row_bwd_args* args, nrl_stream stream);
@@ -231,6 +237,41 @@ enum { NRL_REDUCE_NONE = 0, NRL_REDUCE_SUM = 1, NRL_REDUCE_TOKEN_MEAN = 2, NRL_R
 
 int nrl_reduce_tokens(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
 int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr mask, nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * The cross-entropy family of nn::loss over the same row kernels (src/nn/loss.rs:10-79):
+ *   nll                    :10-16   −log_softmax(logits)[target]           = −logp of nrl_row_fwd(TOKENS_IN)
+ *   cross_entropy          :19-22   per-seed mean of nll
+ *   masked_cross_entropy   :27-34   Σ(nll·mask) / max(Σmask, 1)
+ *   cross_entropy_with     :48-79   + ignore_index (host: target → class 0, keep → 0) and label
+ *                                   smoothing ε: (1 − ε)·nll + ε·(−mean_v log π_v)
+ * replacing log_softmax → dense one-hot [S, N, V] product → lane sum. The mask enters as a product
+ * (as the reference's `nll * mask`), so a non-finite loss at an unscored position gives NaN there too.
+ *
+ * nrl_row_sum: out[r] = Σ_v logits[r, v] in f32, fixed order (needed only for ε > 0:
+ * −mean_v log π_v = m + ln Z − Σ_v z_v / V).
+ * nrl_ce_tokens: the O(rows) part. Forward: loss[i] = ((1 − ε)·(−logp[i]) + ε·u[i])·keep[i].
+ * Backward (when `upstream` is given): g_logp[i] = −(1 − ε)·keep[i]·upstream[i] and
+ * g_uniform[i] = ε·keep[i]·upstream[i], the per-row gradients nrl_row_bwd takes.
+ * Per-seed means are nrl_reduce_tokens(NRL_REDUCE_TOKEN_MEAN, S, 1, N, loss, keep, out). */
+int nrl_row_sum(uint32_t dtype, uint64_t rows, uint32_t V, nrl_devptr logits, nrl_devptr out, nrl_stream stream);
+
+typedef struct nrl_ce_args {
+    uint32_t struct_size;
+    uint32_t V;
+    uint64_t n;            /* S·B·T positions */
+    double smoothing;      /* ε in [0, 1] */
+    nrl_devptr logp;       /* f32 [n]: log-prob of the target (nrl_row_fwd, NRL_FWD_TOKENS_IN) */
+    nrl_devptr rowstats;   /* f32 [n, 4] of the same call; read when ε > 0 */
+    nrl_devptr logit_sum;  /* f32 [n] from nrl_row_sum; read when ε > 0 */
+    nrl_devptr keep;       /* f32 [n] mask × not-ignored, or 0 for all ones */
+    nrl_devptr loss;       /* out f32 [n], or 0 */
+    nrl_devptr upstream;   /* f32 [n] gradient of loss (from nrl_reduce_tokens_bwd), or 0 for no backward */
+    nrl_devptr g_logp;     /* out f32 [n] (with upstream) */
+    nrl_devptr g_uniform;  /* out f32 [n] (with upstream and ε > 0), else 0 */
+} nrl_ce_args;
+
+int nrl_ce_tokens(const nrl_ce_args* args, nrl_stream stream);
 
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
 int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);

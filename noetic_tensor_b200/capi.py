@@ -35,6 +35,7 @@ class RowBwdArgs(C.Structure):
         ("struct_size", u32), ("dtype", u32), ("V", u32), ("temperature", f32), ("rows", u64),
         ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
         ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr), ("accumulate", u32), ("reserved0", u32),
+        ("g_uniform", ptr), ("d_ref_logits", ptr),
     ]
 
 
@@ -44,6 +45,13 @@ class TokenLossArgs(C.Structure):
         ("logp", ptr), ("other", ptr), ("weights", ptr), ("weights_per_sequence", u32), ("has_dual", u32), ("mask", ptr),
         ("clip_low", f64), ("clip_high", f64), ("dual", f64), ("clamp", f64), ("has_clamp", u32), ("accumulate", u32),
         ("loss", ptr), ("upstream", ptr), ("dloss_dlogp", ptr),
+    ]
+
+
+class CeArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("V", u32), ("n", u64), ("smoothing", f64),
+        ("logp", ptr), ("rowstats", ptr), ("logit_sum", ptr), ("keep", ptr), ("loss", ptr), ("upstream", ptr), ("g_logp", ptr), ("g_uniform", ptr),
     ]
 
 
@@ -62,6 +70,8 @@ SYMBOLS = {
     "nrl_reduce_tokens": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_reduce_tokens_bwd": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_mask_rows": (C.c_int, [u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_row_sum": (C.c_int, [u32, u64, u32, ptr, ptr, C.c_void_p]),
+    "nrl_ce_tokens": (C.c_int, [C.POINTER(CeArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
 }
 

@@ -9,6 +9,7 @@
 #include "row_bwd.cuh"
 #include "row_fwd_kernels.cuh"
 #include "token_ops.cuh"
+#include "ce_ops.cuh"
 
 #define NRL_STR2(x) #x
 #define NRL_STR(x) NRL_STR2(x)
@@ -238,7 +239,9 @@ extern "C" int nrl_row_bwd(const nrl_row_bwd_args* a, nrl_stream stream) {
     memset(&p, 0, sizeof p);
     int rc = fill_fwd_params(p.in, a->dtype, a->V, a->rows, a->temperature, a->logits, a->ref_logits, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
     if (rc) return rc;
-    if (!a->d_logits || !a->rowstats || (a->rowstats & 15u) || (a->d_logits & 3u)) return NRL_E_BAD_ARG;
+    if ((!a->d_logits && !a->d_ref_logits) || !a->rowstats || (a->rowstats & 15u) || (a->d_logits & 3u) || (a->d_ref_logits & 3u)) return NRL_E_BAD_ARG;
+    if (a->d_ref_logits && (!a->ref_logits || !a->g_kl)) return NRL_E_BAD_ARG;
+    if (a->g_uniform && (a->allow_mask || a->add_mask || a->temperature != 1.0f)) return NRL_E_UNSUPPORTED;
     if (a->g_logp && !a->tokens) return NRL_E_BAD_ARG;
     if (a->g_kl && (!a->ref_logits || !a->kl)) return NRL_E_BAD_ARG;
     if (a->g_ent && !a->entropy) return NRL_E_BAD_ARG;
@@ -249,7 +252,9 @@ extern "C" int nrl_row_bwd(const nrl_row_bwd_args* a, nrl_stream stream) {
     p.g_logp = (const float*)a->g_logp;
     p.g_kl = (const float*)a->g_kl;
     p.g_ent = (const float*)a->g_ent;
+    p.g_uni = (const float*)a->g_uniform;
     p.d_logits = (float*)a->d_logits;
+    p.d_ref = (float*)a->d_ref_logits;
     p.accumulate = a->accumulate ? 1u : 0u;
     // blocks per row: about 16K elements each, so short rows are one block and long rows spread out
     uint32_t chunks = (a->V + 16383) / 16384;
@@ -338,6 +343,46 @@ extern "C" int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B,
 extern "C" int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream) {
     if (n == 0 || !x || !out) return NRL_E_BAD_ARG;
     mask_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, (const float*)x, (const float*)mask, (float*)out);
+    return after_launch();
+}
+
+// ---- cross-entropy family -------------------------------------------------------------------------
+
+extern "C" int nrl_row_sum(uint32_t dtype, uint64_t rows, uint32_t V, nrl_devptr logits, nrl_devptr out, nrl_stream stream) {
+    if (rows == 0 || V == 0 || !logits || !out) return NRL_E_BAD_ARG;
+    if (dtype != NRL_F32 && dtype != NRL_BF16) return NRL_E_UNSUPPORTED;
+    if ((logits & (dtype == NRL_F32 ? 3u : 1u)) || (out & 3u)) return NRL_E_BAD_ARG;
+    if (rows > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    const bool vec = V % kVec == 0 && (logits & 15u) == 0;
+    if (dtype == NRL_F32) row_sum_kernel<NRL_F32><<<(unsigned)rows, kSumThreads, 0, (cudaStream_t)stream>>>((const void*)logits, V, vec, (float*)out);
+    else row_sum_kernel<NRL_BF16><<<(unsigned)rows, kSumThreads, 0, (cudaStream_t)stream>>>((const void*)logits, V, vec, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_ce_tokens(const nrl_ce_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_ce_args)) return NRL_E_BAD_ARG;
+    if (a->n == 0 || a->V == 0 || !a->logp) return NRL_E_BAD_ARG;
+    if (!(a->smoothing >= 0.0 && a->smoothing <= 1.0)) return NRL_E_BAD_ARG;  // "label smoothing outside [0, 1]"
+    if (!a->loss && !a->upstream) return NRL_E_BAD_ARG;
+    if (a->upstream && !a->g_logp) return NRL_E_BAD_ARG;
+    if (a->smoothing > 0.0 && (!a->rowstats || (a->rowstats & 15u) || !a->logit_sum || (a->upstream && !a->g_uniform))) return NRL_E_BAD_ARG;
+    CeParams p;
+    memset(&p, 0, sizeof p);
+    p.logp = (const float*)a->logp;
+    p.rowstats = (const float*)a->rowstats;
+    p.logit_sum = (const float*)a->logit_sum;
+    p.keep = (const float*)a->keep;
+    p.upstream = (const float*)a->upstream;
+    p.loss = (float*)a->loss;
+    p.g_logp = (float*)a->g_logp;
+    p.g_uniform = a->smoothing > 0.0 ? (float*)a->g_uniform : nullptr;
+    p.n = a->n;
+    p.eps = (float)a->smoothing;
+    p.one_minus_eps = (float)(1.0 - a->smoothing);
+    p.inv_v = 1.0f / (float)a->V;
+    uint64_t blocks = (p.n + 255) / 256;
+    if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    ce_tokens_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
     return after_launch();
 }
 

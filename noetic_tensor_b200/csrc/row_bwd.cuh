@@ -15,10 +15,24 @@ struct BwdParams {
     const float* g_logp;
     const float* g_kl;
     const float* g_ent;
-    float* d_logits;
+    const float* g_uni;  // upstream of −mean_v log π_v (label smoothing), or null
+    float* d_logits;     // may be null when d_ref is given
+    float* d_ref;        // gradient w.r.t. the reference logits of the KL term, or null
     uint32_t chunks_per_row;  // blocks per row
-    uint32_t accumulate;      // add into d_logits
+    uint32_t accumulate;      // add into the outputs
 };
+
+// 8 consecutive f32 of a gradient row: two 16-byte streaming stores, or element stores on a ragged tail
+__device__ __forceinline__ void store_grad8(float* out, uint32_t v, uint32_t v_end, const float g[8], bool vec_out) {
+    if (vec_out) {
+        stg_stream16(out + v, g[0], g[1], g[2], g[3]);
+        stg_stream16(out + v + 4, g[4], g[5], g[6], g[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+            if (v + i < v_end) out[v + i] = g[i];
+    }
+}
 
 constexpr int kBwdThreads = 256;
 
@@ -33,23 +47,23 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     const uint32_t vec_per = (nvec + p.chunks_per_row - 1) / p.chunks_per_row;
     const uint32_t v_begin = min(chunk * vec_per, nvec) * kVec;
     const uint32_t v_end = min(min((chunk + 1) * vec_per, nvec) * kVec, V);
-    float* out = p.d_logits + row * V;
+    float* out = p.d_logits ? p.d_logits + row * V : nullptr;
+    float* out_ref = (REF && p.d_ref) ? p.d_ref + row * V : nullptr;
 
     const float glp = p.g_logp ? p.g_logp[row] : 0.f;
     const float gkl = (REF && p.g_kl) ? p.g_kl[row] : 0.f;
     const float gen = p.g_ent ? p.g_ent[row] : 0.f;
-    const bool vec_out = VEC && ((reinterpret_cast<uintptr_t>(p.d_logits) & 15u) == 0);
+    const float gun = p.g_uni ? p.g_uni[row] : 0.f;
+    const float gun_v = gun != 0.f ? __fdiv_rn(gun, (float)V) : 0.f;
+    const bool vec_out = VEC && (((reinterpret_cast<uintptr_t>(p.d_logits) | reinterpret_cast<uintptr_t>(p.d_ref)) & 15u) == 0);
 
-    if (glp == 0.f && gkl == 0.f && gen == 0.f) {
+    if (glp == 0.f && gkl == 0.f && gen == 0.f && gun == 0.f) {
         if (p.accumulate) return;  // adding exact zeros
         // an unscored position: exact zeros, the inputs are not read
+        const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
-            if (vec_out) {
-                stg_stream16(out + v, 0.f, 0.f, 0.f, 0.f);
-                stg_stream16(out + v + 4, 0.f, 0.f, 0.f, 0.f);
-            } else {
-                for (uint32_t i = 0; i < kVec && v + i < v_end; i++) out[v + i] = 0.f;
-            }
+            if (out) store_grad8(out, v, v_end, zero, vec_out);
+            if (out_ref) store_grad8(out_ref, v, v_end, zero, vec_out);
         }
         return;
     }
@@ -69,18 +83,14 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             const bool holds_token = tok >= (int32_t)v && tok < (int32_t)(v + kVec);  // its entry gets g_lp even if excluded
             if (!mk.any() && !holds_token) {
                 if (p.accumulate) continue;
-                if (vec_out) {
-                    stg_stream16(out + v, 0.f, 0.f, 0.f, 0.f);
-                    stg_stream16(out + v + 4, 0.f, 0.f, 0.f, 0.f);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 8; i++) out[v + i] = 0.f;
-                }
+                const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                if (out) store_grad8(out, v, v_end, zero, vec_out);
+                if (out_ref) store_grad8(out_ref, v, v_end, zero, vec_out);
                 continue;
             }
         }
         ld.load(f, row, v, v_end);
-        float z[8], zr[8], g[8];
+        float z[8], zr[8], g[8], gr[8];
         ld.values(f, z, zr);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -88,25 +98,38 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             float lp = (zc - m) - lnZ;
             float pi = ex2_approx(lp * kLog2e);
             float c = -glp;                                   // d logp / dz_j = 1[j = tok] − π_j
-            if (REF) c = fmaf(gkl, (lp - ((zr[i] - mr) - lnZr)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+            float lr = 0.f;
+            if (REF) {
+                lr = (zr[i] - mr) - lnZr;
+                c = fmaf(gkl, (lp - lr) - klv, c);            // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+            }
             c = fmaf(-gen, lp + hv, c);                       // d H / dz_j = −π_j (log π_j + H)
-            float d = pi > 0.f ? pi * c : 0.f;                // a zero-probability token gets exactly 0
+            c += gun;                                         // d(−mean_v log π_v) / dz_j = π_j − 1/V
+            float d = (pi > 0.f ? pi * c : 0.f) - gun_v;      // a zero-probability token gets exactly 0
             if ((int32_t)(v + i) == tok) d += glp;
             if (GENERAL && f.tau != 1.0f) d = __fdiv_rn(d, f.tau);
             g[i] = d;
+            if (REF) {                                        // d KL / dzr_j = ρ_j − π_j
+                float dr = gkl * (ex2_approx(lr * kLog2e) - pi);
+                if (GENERAL && f.tau != 1.0f) dr = __fdiv_rn(dr, f.tau);
+                gr[i] = dr;
+            }
         }
-        if (p.accumulate) {
+        if (out) {
+            if (p.accumulate) {
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-                if (v + i < v_end) g[i] += out[v + i];
+                for (int i = 0; i < 8; i++)
+                    if (v + i < v_end) g[i] += out[v + i];
+            }
+            store_grad8(out, v, v_end, g, vec_out);
         }
-        if (vec_out) {
-            stg_stream16(out + v, g[0], g[1], g[2], g[3]);
-            stg_stream16(out + v + 4, g[4], g[5], g[6], g[7]);
-        } else {
+        if (REF && out_ref) {
+            if (p.accumulate) {
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-                if (v + i < v_end) out[v + i] = g[i];
+                for (int i = 0; i < 8; i++)
+                    if (v + i < v_end) gr[i] += out_ref[v + i];
+            }
+            store_grad8(out_ref, v, v_end, gr, vec_out);
         }
     }
 }

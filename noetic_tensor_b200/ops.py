@@ -110,8 +110,12 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
     return out
 
 
-def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None, accumulate=False):
-    """d(logits) [rows, V] f32 from the forward's saved statistics and per-row upstream gradients."""
+def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None, accumulate=False,
+                 g_uniform=None, d_ref=None, want_d_logits=True):
+    """d(logits) [rows, V] f32 from the forward's saved statistics and per-row upstream gradients.
+    `g_uniform`: upstream of −mean_v log π_v (label smoothing). `d_ref=True` (or a tensor) also
+    returns the KL term's gradient w.r.t. ref_logits, g_kl·(ρ − π): the result is then the pair
+    (d_logits or None when `want_d_logits` is False, d_ref_logits)."""
     dev = logits.device
     rows, V = logits.shape
     a = capi.RowBwdArgs()
@@ -120,20 +124,30 @@ def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, tem
     a.logits, a.ref_logits = _p(logits), _p(ref_logits)
     allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
     a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
-    for name, g in (("g_logp", g_logp), ("g_kl", g_kl), ("g_ent", g_ent)):
+    for name, g in (("g_logp", g_logp), ("g_kl", g_kl), ("g_ent", g_ent), ("g_uniform", g_uniform)):
         if g is not None:
             _need(g, torch.float32, (rows,), name, dev)
     a.tokens, a.rowstats, a.kl, a.entropy = _p(fwd.tokens), _p(fwd.rowstats), _p(fwd.kl), _p(fwd.entropy)
     a.g_logp, a.g_kl, a.g_ent = _p(g_logp), _p(g_kl), _p(g_ent)
-    if out is None:
+    a.g_uniform = _p(g_uniform)
+    if not want_d_logits:
+        out = None
+    elif out is None:
         out = torch.empty(rows, V, dtype=torch.float32, device=dev)
     else:
         _need(out, torch.float32, (rows, V), "d_logits", dev)
     a.d_logits = _p(out)
+    if d_ref is True:
+        d_ref = torch.empty(rows, V, dtype=torch.float32, device=dev)
+    elif d_ref is not None and d_ref is not False:
+        _need(d_ref, torch.float32, (rows, V), "d_ref_logits", dev)
+    else:
+        d_ref = None
+    a.d_ref_logits = _p(d_ref)
     a.accumulate = 1 if accumulate else 0
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_row_bwd(C.byref(a), _stream(dev)), "nrl_row_bwd")
-    return out
+    return out if d_ref is None else (out, d_ref)
 
 
 def _tok_args(kind, logp, other, weights, mask, clip_low=0.0, clip_high=0.0, dual=None, clamp=None):
@@ -227,3 +241,39 @@ def check_status(status):
     if rc == capi.E_ROW_STATUS:
         raise RuntimeError(f"sample_categorical: position {bad.value} has no allowed token (every logit −∞ or a NaN)")
     capi.check(rc, "nrl_check_status")
+
+
+def row_sum(logits):
+    """Σ_v logits[r, v] per row in f32 (nrl_row_sum)."""
+    dev = logits.device
+    rows, V = logits.shape
+    if not logits.is_contiguous():
+        raise ValueError("logits must be contiguous")
+    out = torch.empty(rows, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_row_sum(_dt(logits), rows, V, _p(logits), _p(out), _stream(dev)), "nrl_row_sum")
+    return out
+
+
+def ce_tokens(V, logp, *, smoothing=0.0, rowstats=None, logit_sum=None, keep=None, upstream=None, want_loss=True):
+    """The O(rows) part of the cross-entropy family (nrl_ce_tokens): returns (loss, g_logp,
+    g_uniform), each [n] f32 or None."""
+    dev = logp.device
+    n = logp.numel()
+    a = capi.CeArgs()
+    a.struct_size = C.sizeof(a)
+    a.V, a.n, a.smoothing = V, n, float(smoothing)
+    _need(logp, torch.float32, logp.shape, "logp", dev)
+    a.logp, a.rowstats, a.logit_sum, a.keep = _p(logp), _p(rowstats), _p(logit_sum), _p(keep)
+    if keep is not None:
+        _need(keep, torch.float32, logp.shape, "keep", dev)
+    loss = torch.empty_like(logp) if want_loss else None
+    g_logp = g_uni = None
+    if upstream is not None:
+        _need(upstream, torch.float32, logp.shape, "upstream", dev)
+        g_logp = torch.empty_like(logp)
+        g_uni = torch.empty_like(logp) if smoothing > 0.0 else None
+    a.loss, a.upstream, a.g_logp, a.g_uniform = _p(loss), _p(upstream), _p(g_logp), _p(g_uni)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_ce_tokens(C.byref(a), _stream(dev)), "nrl_ce_tokens")
+    return loss, g_logp, g_uni

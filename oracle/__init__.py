@@ -25,11 +25,13 @@ LOG_RATIO_CLAMP = 20.0  # src/nn/rl.rs:146
 KL_DELTA_CLAMP = 20.0  # src/nn/rl.rs:150
 
 OP_TOKEN_LOG_PROBS, OP_PG, OP_PPO, OP_CLIP_FRACTION, OP_KL, OP_REFERENCE_KL, OP_KL_ESTIMATE, OP_ENTROPY = range(8)
+# nn::loss (src/nn/loss.rs): `tokens` are the targets; KL_DIV takes pred = logits, target = ref_logits
+OP_NLL, OP_CE, OP_MASKED_CE, OP_CE_WITH, OP_KL_DIV = range(8, 13)
 
 
 def build(force=False):
     """Compile liboracle.so with the Makefile beside this file."""
-    srcs = [os.path.join(_HERE, f) for f in ("oracle_api.cpp", "oracle.h", "engine.hpp", "rl.hpp", "streams.hpp", "Makefile")]
+    srcs = [os.path.join(_HERE, f) for f in ("oracle_api.cpp", "oracle.h", "engine.hpp", "rl.hpp", "loss.hpp", "streams.hpp", "Makefile")]
     if not force and os.path.exists(_LIB_PATH) and all(os.path.getmtime(_LIB_PATH) >= os.path.getmtime(s) for s in srcs):
         return _LIB_PATH
     subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True, capture_output=True)
@@ -47,6 +49,7 @@ class _Case(C.Structure):
         ("clip_low", C.c_double), ("clip_high", C.c_double), ("dual", C.c_double), ("log_ratio_clamp", C.c_double), ("delta_clamp", C.c_double),
         ("has_dual", C.c_int32), ("has_log_ratio_clamp", C.c_int32), ("has_delta_clamp", C.c_int32), ("vocab_mask_full", C.c_int32),
         ("upstream", C.c_void_p), ("out_value", C.c_void_p), ("out_capacity", C.c_int64), ("out_len", C.c_void_p), ("out_grad", C.c_void_p),
+        ("has_ignore_index", C.c_int32), ("reserved0", C.c_int32), ("ignore_index", C.c_int64), ("smoothing", C.c_double), ("out_grad_ref", C.c_void_p),
     ]
 
 
@@ -107,8 +110,9 @@ def _ptr(a):
 
 
 def rl_eval(op, shape, *, dtype=F32, logits=None, ref_logits=None, tokens=None, logp=None, old_logp=None, ref_logp=None, weights=None,
-            mask=None, vocab_mask=None, temperature=1.0, clip=None, estimator=K1, delta_clamp=None, reduction=NONE, upstream=None):
-    """Value (float64 array) and, with `upstream`, the gradient of sum(value*upstream) w.r.t. the leaf."""
+            mask=None, vocab_mask=None, temperature=1.0, clip=None, estimator=K1, delta_clamp=None, reduction=NONE, upstream=None, ignore_index=None, smoothing=0.0, grad_ref=False):
+    """Value (float64 array) and, with `upstream`, the gradient of sum(value*upstream) w.r.t. the leaf
+    (and, with `grad_ref`, w.r.t. ref_logits as a third result)."""
     S, B, T, V = shape
     n = S * B * T
     keep = []
@@ -159,6 +163,9 @@ def rl_eval(op, shape, *, dtype=F32, logits=None, ref_logits=None, tokens=None, 
         c.has_log_ratio_clamp, c.log_ratio_clamp = (1, clip.log_ratio_clamp) if clip.log_ratio_clamp is not None else (0, 0.0)
     c.estimator = estimator
     c.has_delta_clamp, c.delta_clamp = (1, delta_clamp) if delta_clamp is not None else (0, 0.0)
+    if ignore_index is not None:
+        c.has_ignore_index, c.ignore_index = 1, int(ignore_index)
+    c.smoothing = float(smoothing)
     cap = max(n, 1)
     out = np.zeros(cap, dtype=np.float64)
     out_len = C.c_int64(0)
@@ -170,10 +177,15 @@ def rl_eval(op, shape, *, dtype=F32, logits=None, ref_logits=None, tokens=None, 
         c.upstream = _ptr(up)
         grad = np.zeros(n if logp is not None else n * V, dtype=np.float64)
         c.out_grad = _ptr(grad)
+        if grad_ref:
+            gref = np.zeros(n * V, dtype=np.float64)
+            c.out_grad_ref = _ptr(gref)
     rc = lib().orc_rl_eval(C.byref(c))
     if rc != 0:
         raise RuntimeError(lib().orc_last_error().decode())
     value = out[: out_len.value].copy()
+    if upstream is not None and grad_ref:
+        return value, grad, gref
     return (value, grad) if upstream is not None else value
 
 

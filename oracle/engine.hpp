@@ -609,6 +609,35 @@ struct Engine {
         });
     }
 
+    // src/tensor/float.rs:683-706: the lane sum divided by the lane's length; backward
+    // ones · g.sum_dim(dim) / n.
+    static Tensor mean_dim(const Tensor& a, size_t dim) {
+        if (dim >= a.sh.size()) fail("mean_dim: dim out of range");
+        auto r = be_sum_dim(a.v(), a.sh, dim);
+        const T n = (T)a.sh[dim];
+        for (T& x : r.first) x = x / n;
+        Shape shape = a.sh;
+        return record(std::move(r.first), r.second, {&a}, [shape, dim](const Tensor&) {
+            return [shape, dim](const Tensor& g, const std::vector<bool>&) {
+                Tensor ones = Tensor::full(shape, 1.0);
+                Tensor gs = sum_dim(g, dim);
+                return Grads{div_scalar(mul(ones, gs), (double)shape[dim])};
+            };
+        });
+    }
+
+    // IntTensor::one_hot_float (src/tensor/int.rs:214-222): an untracked 0/1 tensor with one more axis.
+    static Tensor one_hot(const Int& idx, size_t n) {
+        std::vector<T> d(idx.v.size() * n, (T)0);
+        for (size_t i = 0; i < idx.v.size(); i++) {
+            if (idx.v[i] < 0 || (size_t)idx.v[i] >= n) fail("one_hot: index outside 0..n");
+            d[i * n + (size_t)idx.v[i]] = (T)1;
+        }
+        Shape sh = idx.sh;
+        sh.push_back(n);
+        return Tensor(std::move(d), sh);
+    }
+
     static Tensor max_dim(const Tensor& a, size_t dim) {
         auto am = argmax_dim(a.v(), a.sh, dim);
         std::vector<T> vals = k_gather(a.v(), a.sh, dim, am.first, am.second);

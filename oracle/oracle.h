@@ -22,7 +22,12 @@ enum {
     ORC_OP_KL = 4,              /* categorical_kl             src/nn/rl.rs:327-338 */
     ORC_OP_REFERENCE_KL = 5,    /* reference_kl               src/nn/rl.rs:347-351 */
     ORC_OP_KL_ESTIMATE = 6,     /* kl_estimate                src/nn/rl.rs:380-400 */
-    ORC_OP_ENTROPY = 7          /* categorical_entropy        src/nn/rl.rs:405-414 */
+    ORC_OP_ENTROPY = 7,         /* categorical_entropy        src/nn/rl.rs:405-414 */
+    ORC_OP_NLL = 8,             /* nn::loss::nll              src/nn/loss.rs:10-16   -> [S, B·T] */
+    ORC_OP_CE = 9,              /* cross_entropy              src/nn/loss.rs:19-22   -> [S] */
+    ORC_OP_MASKED_CE = 10,      /* masked_cross_entropy       src/nn/loss.rs:27-34   -> [S] */
+    ORC_OP_CE_WITH = 11,        /* cross_entropy_with         src/nn/loss.rs:48-79   -> [S] */
+    ORC_OP_KL_DIV = 12          /* kl_div(pred = logits, target = ref_logits) src/nn/loss.rs:175-183 -> [S] */
 };
 
 /* One evaluation of an rl function and, with `upstream`, of the gradient of
@@ -56,6 +61,12 @@ typedef struct orc_rl_case {
     int64_t out_capacity;
     int64_t* out_len;
     double* out_grad; /* leaf-shaped, or NULL */
+    /* the cross-entropy family (ops 8-12); `tokens` are the targets */
+    int32_t has_ignore_index;
+    int32_t reserved0;
+    int64_t ignore_index;
+    double smoothing;
+    double* out_grad_ref; /* ORC_OP_KL_DIV: gradient w.r.t. ref_logits (the target side), or NULL */
 } orc_rl_case;
 
 const char* orc_last_error(void);

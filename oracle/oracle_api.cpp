@@ -4,6 +4,7 @@
 // ctypes by tests/ and by the benchmark's CPU-baseline / reference legs. The shipped library
 // never links or calls this file.
 #include "oracle.h"
+#include "loss.hpp"
 #include "rl.hpp"
 #include "streams.hpp"
 
@@ -66,7 +67,7 @@ static int eval(const orc_rl_case* c) {
         logp = small(c->logp, tok_sh);
         if (c->upstream) logp = logp.require_grad();
         leaf = logp;
-    } else if (needs_logits && c->tokens) {
+    } else if (needs_logits && c->tokens && c->op < ORC_OP_NLL) {
         logp = R::token_log_probs(tempered(logits), tokens);
     }
     std::optional<Tensor> mask, old_logp, ref_logp, weights, ref_logits;
@@ -75,6 +76,7 @@ static int eval(const orc_rl_case* c) {
     if (c->ref_logp) ref_logp = small(c->ref_logp, tok_sh);
     if (c->weights) weights = c->weights_rank == 2 ? small(c->weights, Shape{S, B}) : small(c->weights, tok_sh);
     if (c->ref_logits) ref_logits = Tensor(load<T>(c->ref_logits, c->ref_dtype, n * V), lsh);
+    if (ref_logits && c->out_grad_ref && c->upstream) ref_logits = ref_logits->require_grad();
     const Tensor* mp = mask ? &*mask : nullptr;
     TokenReduction red = (TokenReduction)c->reduction;
     Clip clip{c->clip_low, c->clip_high, c->has_dual != 0, c->dual, c->has_log_ratio_clamp != 0, c->log_ratio_clamp};
@@ -94,6 +96,18 @@ static int eval(const orc_rl_case* c) {
         case ORC_OP_REFERENCE_KL: out = R::reference_kl(logits, *ref_logits, c->temperature, vmask ? &*vmask : nullptr, mp, red); break;
         case ORC_OP_KL_ESTIMATE: out = R::kl_estimate(logp, *ref_logp, (KlEstimator)c->estimator, c->has_delta_clamp != 0, c->delta_clamp, mp, red); break;
         case ORC_OP_ENTROPY: out = R::categorical_entropy(tempered(logits), mp, red); break;
+        case ORC_OP_NLL: out = Loss<T>::nll(logits, tokens); break;
+        case ORC_OP_CE: out = Loss<T>::cross_entropy(logits, tokens); break;
+        case ORC_OP_MASKED_CE: out = Loss<T>::masked_cross_entropy(logits, tokens, *mask); break;
+        case ORC_OP_CE_WITH: {
+            CeOptions o;
+            o.has_ignore_index = c->has_ignore_index != 0;
+            o.ignore_index = c->ignore_index;
+            o.smoothing = c->smoothing;
+            out = Loss<T>::cross_entropy_with(logits, tokens, mp, o);
+            break;
+        }
+        case ORC_OP_KL_DIV: out = Loss<T>::kl_div(logits, *ref_logits); break;
         default: fail("unknown op");
     }
     if ((int64_t)out.n() > c->out_capacity) fail("output buffer too small");
@@ -110,6 +124,10 @@ static int eval(const orc_rl_case* c) {
             for (size_t i = 0; i < ln; i++) c->out_grad[i] = 0.0;
         } else {
             for (size_t i = 0; i < ln; i++) c->out_grad[i] = (double)gl->v()[i];
+        }
+        if (c->out_grad_ref && ref_logits) {
+            const Tensor* gr = g.get(*ref_logits);
+            for (size_t i = 0; i < ref_logits->n(); i++) c->out_grad_ref[i] = gr ? (double)gr->v()[i] : 0.0;
         }
     }
     return 0;

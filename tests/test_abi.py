@@ -36,8 +36,9 @@ def test_identity_calls_need_no_gpu():
 def test_struct_layouts():
     # sizes follow from the header's field lists (8-byte alignment, no packing)
     assert C.sizeof(capi.RowFwdArgs) == 4 * 4 + 8 + 4 + 4 + 16 * 8
-    assert C.sizeof(capi.RowBwdArgs) == 4 * 4 + 8 + 14 * 8 + 8
+    assert C.sizeof(capi.RowBwdArgs) == 4 * 4 + 8 + 14 * 8 + 8 + 2 * 8
     assert C.sizeof(capi.TokenLossArgs) == 8 + 3 * 8 + 3 * 8 + 8 + 8 + 4 * 8 + 8 + 3 * 8
+    assert C.sizeof(capi.CeArgs) == 8 + 8 + 8 + 8 * 8
 
 
 def test_argument_checks_run_before_any_cuda_call():
@@ -56,3 +57,16 @@ def test_argument_checks_run_before_any_cuda_call():
     assert l.nrl_row_fwd_workspace_bytes(262144, 128256) == 0
     assert l.nrl_row_fwd_workspace_bytes(32, 128256) > 0
     assert l.nrl_row_fwd_workspace_bytes(32, 16) == 0
+    # the cross-entropy entries
+    assert l.nrl_row_sum(capi.F32, 0, 16, 256, 256, None) == capi.E_BAD_ARG
+    assert l.nrl_row_sum(9, 4, 16, 256, 256, None) == capi.E_UNSUPPORTED
+    c = capi.CeArgs()
+    c.struct_size, c.V, c.n, c.logp, c.loss, c.smoothing = C.sizeof(c), 16, 4, 256, 256, 1.5
+    assert l.nrl_ce_tokens(C.byref(c), None) == capi.E_BAD_ARG  # label smoothing outside [0, 1]
+    c.smoothing = 0.1
+    assert l.nrl_ce_tokens(C.byref(c), None) == capi.E_BAD_ARG  # smoothing needs rowstats and the logit sums
+    b = capi.RowBwdArgs()
+    b.struct_size, b.rows, b.V, b.logits, b.temperature, b.dtype, b.rowstats = C.sizeof(b), 4, 16, 256, 1.0, capi.F32, 256
+    assert l.nrl_row_bwd(C.byref(b), None) == capi.E_BAD_ARG  # no output
+    b.d_logits, b.g_uniform, b.allow_mask, b.allow_row_stride = 256, 256, 256, 16
+    assert l.nrl_row_bwd(C.byref(b), None) == capi.E_UNSUPPORTED  # label smoothing under a vocabulary mask
