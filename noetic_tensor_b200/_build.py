@@ -63,7 +63,7 @@ def build_host_program(source, out):
     """Compiles a C++ program that uses host/noetic_rl.hpp (the C++ mirror of `nn::rl`) and links
     it against libnrl.so and the CUDA runtime. g++ only: the header holds no device code."""
     build()
-    deps = [source, HOST_HEADER, INCLUDE, LIB]
+    deps = [source, HOST_HEADER, os.path.join(HERE, "host", "noetic_loss.hpp"), INCLUDE, LIB]
     if os.path.exists(out) and all(os.path.getmtime(d) <= os.path.getmtime(out) for d in deps):
         return out
     os.makedirs(os.path.dirname(out), exist_ok=True)

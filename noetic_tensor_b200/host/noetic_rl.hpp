@@ -295,7 +295,7 @@ struct Saved {  // what one forward leaves for its backward (O(rows), not the [r
     Tensor z, ref, tokens, rowstats, kl, entropy;
     bool has_ref = false;
 };
-inline void row_bwd(const Saved& s, const Tensor* g_lp, const Tensor* g_kl, const Tensor* g_en, Tensor& d, bool accumulate) {
+inline void row_bwd(const Saved& s, const Tensor* g_lp, const Tensor* g_kl, const Tensor* g_en, Tensor* d, bool accumulate, const Tensor* g_un = nullptr, Tensor* d_ref = nullptr) {
     nrl_row_fwd_args f;
     fill_inputs(f, s.z, s.has_ref ? &s.ref : nullptr);
     nrl_row_bwd_args b;
@@ -311,20 +311,44 @@ inline void row_bwd(const Saved& s, const Tensor* g_lp, const Tensor* g_kl, cons
     b.g_logp = g_lp ? g_lp->dev() : 0;
     b.g_kl = g_kl ? g_kl->dev() : 0;
     b.g_ent = g_en ? g_en->dev() : 0;
-    b.d_logits = d.dev();
+    b.g_uniform = g_un ? g_un->dev() : 0;
+    b.d_logits = d ? d->dev() : 0;
+    b.d_ref_logits = d_ref ? d_ref->dev() : 0;
     b.accumulate = accumulate ? 1 : 0;
     nrl(nrl_row_bwd(&b, stream()), "row_bwd");
 }
 // add this node's d(logits) into the gradient map (the tape's `new + old`)
-inline void push_logits_grad(const Saved& s, const Tensor& logits_leaf, const Tensor* g_lp, const Tensor* g_kl, const Tensor* g_en, std::map<uint64_t, Tensor>& grads) {
+inline void push_logits_grad(const Saved& s, const Tensor& logits_leaf, const Tensor* g_lp, const Tensor* g_kl, const Tensor* g_en, std::map<uint64_t, Tensor>& grads, const Tensor* g_un = nullptr) {
     auto it = grads.find(logits_leaf.node_->id);
     if (it == grads.end()) {
         Tensor d = Tensor::empty(logits_leaf.shape(), DType::F32, logits_leaf.device());
-        row_bwd(s, g_lp, g_kl, g_en, d, false);
+        row_bwd(s, g_lp, g_kl, g_en, &d, false, g_un);
         grads[logits_leaf.node_->id] = d;
     } else {
-        row_bwd(s, g_lp, g_kl, g_en, it->second, true);
+        row_bwd(s, g_lp, g_kl, g_en, &it->second, true, g_un);
     }
+}
+// the KL term's gradients to both sides: `policy` is the side the forward streamed as logits,
+// `reference` the side it streamed as ref_logits; either may be untracked
+inline void push_kl_grads(const Saved& s, const Tensor& policy, const Tensor& reference, const Tensor& g_kl, std::map<uint64_t, Tensor>& grads) {
+    auto slot = [&](const Tensor& leaf, bool& fresh) -> Tensor {
+        auto it = grads.find(leaf.node_->id);
+        fresh = it == grads.end();
+        return fresh ? Tensor::empty(leaf.shape(), DType::F32, leaf.device()) : it->second;
+    };
+    // one launch per side that already holds a gradient differently from the other; one for both otherwise
+    bool fp = true, fr = true;
+    Tensor dp, dr;
+    if (policy.tracked()) dp = slot(policy, fp);
+    if (reference.tracked()) dr = slot(reference, fr);
+    if (policy.tracked() && reference.tracked() && fp != fr) {
+        row_bwd(s, nullptr, &g_kl, nullptr, &dp, !fp);
+        row_bwd(s, nullptr, &g_kl, nullptr, nullptr, !fr, nullptr, &dr);
+    } else {
+        row_bwd(s, nullptr, &g_kl, nullptr, policy.tracked() ? &dp : nullptr, policy.tracked() ? !fp : !fr, nullptr, reference.tracked() ? &dr : nullptr);
+    }
+    if (policy.tracked()) grads[policy.node_->id] = dp;
+    if (reference.tracked()) grads[reference.node_->id] = dr;
 }
 inline Tensor zeros_like_rows(uint64_t n, Device dev, DType dt = DType::F32) { return Tensor::empty(Shape{(size_t)n}, dt, dev); }
 inline Tensor reduce(const Tensor& per, const Tensor* mask, TokenReduction r) {

@@ -6,7 +6,7 @@
 #include <cstdio>
 #include <random>
 
-#include "../../noetic_tensor_b200/host/noetic_rl.hpp"
+#include "../../noetic_tensor_b200/host/noetic_loss.hpp"
 
 using namespace noetic;
 namespace rl = noetic::nn::rl;
@@ -463,6 +463,108 @@ static void test_ppo_step() {
     std::printf("  PPO step backward: %llu kernel launches for 3 loss terms over %zu rows\n", (unsigned long long)launches, c.n());
 }
 
+// ---- nn::loss cross-entropy family (src/nn/tests/naive.rs:152-170, components.rs:534-588) -------
+static void test_loss_family() {
+    namespace ls = noetic::nn::loss;
+    for (int bf = 0; bf < 2; bf++) {
+        Case c = make_case(940 + bf, -3.0, 3.0, bf, bf ? 1000 : 5);
+        const size_t N = c.B * c.T;
+        std::vector<int64_t> tg = c.tokens, tg_ign = c.tokens;
+        tg_ign[1] = -100;
+        tg_ign[7] = -100;
+        std::vector<std::vector<double>> ys;
+        for (size_t i = 0; i < c.n(); i++) ys.push_back(log_softmax_row(&c.logits[i * c.V], c.V));
+        auto host = [&](const std::vector<int64_t>& t, bool masked, bool ignore, double eps, std::vector<double>* grad) {
+            std::vector<double> out(c.S);
+            if (grad) grad->assign(c.n() * c.V, 0.0);
+            for (size_t s = 0; s < c.S; s++) {
+                double sum = 0, cnt = 0;
+                for (size_t i = s * N; i < (s + 1) * N; i++) {
+                    double keep = masked ? c.mask[i] : 1.0;
+                    if (ignore && t[i] == -100) keep = 0.0;
+                    cnt += keep;
+                }
+                for (size_t i = s * N; i < (s + 1) * N; i++) {
+                    double keep = masked ? c.mask[i] : 1.0;
+                    int64_t ti = t[i];
+                    if (ignore && ti == -100) { keep = 0.0; ti = 0; }
+                    double mean = 0;
+                    for (size_t v = 0; v < c.V; v++) mean += ys[i][v];
+                    mean /= (double)c.V;
+                    sum += keep * ((1 - eps) * -ys[i][ti] + eps * -mean);
+                    if (grad)
+                        for (size_t v = 0; v < c.V; v++)
+                            (*grad)[i * c.V + v] = keep / std::max(cnt, 1.0) * (std::exp(ys[i][v]) - (1 - eps) * ((int64_t)v == ti ? 1.0 : 0.0) - eps / (double)c.V);
+                }
+                out[s] = sum / std::max(cnt, 1.0);
+            }
+            return out;
+        };
+        DType dt = bf ? DType::BF16 : DType::F32;
+        Tensor mask = Tensor::from_f32(c.mask, c.sh(), dev);
+        IntTensor t0 = IntTensor::from_data(tg, c.sh()), t1 = IntTensor::from_data(tg_ign, c.sh());
+        std::vector<double> gw;
+        {
+            Tensor z = Tensor::from_f32(c.logits, c.lsh(), dev, dt).require_grad();
+            Tensor l = ls::cross_entropy(z, t0);
+            close_all(l.to_vec(), host(tg, false, false, 0.0, &gw), 2e-6, "cross_entropy");
+            close_all(backward(l).grad(z)->to_vec(), gw, 2e-6, "d cross_entropy");
+            std::vector<double> nl;
+            for (size_t i = 0; i < c.n(); i++) nl.push_back(-ys[i][tg[i]]);
+            Tensor per = ls::nll(z, t0);
+            CHECK((per.shape() == Shape{c.S, N}), "nll shape");
+            close_all(per.to_vec(), nl, 2e-6, "nll");
+        }
+        {
+            Tensor z = Tensor::from_f32(c.logits, c.lsh(), dev, dt).require_grad();
+            Tensor l = ls::masked_cross_entropy(z, t0, mask);
+            close_all(l.to_vec(), host(tg, true, false, 0.0, &gw), 2e-6, "masked_cross_entropy");
+            auto d = backward(l).grad(z)->to_vec();
+            close_all(d, gw, 2e-6, "d masked_cross_entropy");
+            for (size_t i = 0; i < c.n(); i++)
+                if (c.mask[i] == 0.f)
+                    for (size_t v = 0; v < c.V; v++) CHECK(d[i * c.V + v] == 0.f, "unscored position has a gradient");
+            // default options are the plain losses, to the bit
+            auto a = ls::cross_entropy_with(z, t0, &mask, ls::CeOptions()).to_vec(), b = l.to_vec();
+            CHECK(std::memcmp(a.data(), b.data(), a.size() * 4) == 0, "default options differ from masked_cross_entropy");
+        }
+        {
+            Tensor z = Tensor::from_f32(c.logits, c.lsh(), dev, dt).require_grad();
+            Tensor l = ls::cross_entropy_with(z, t1, &mask, ls::CeOptions::ignore(-100).with_smoothing(0.1));
+            close_all(l.to_vec(), host(tg_ign, true, true, 0.1, &gw), 2e-6, "cross_entropy_with");
+            close_all(backward(l).grad(z)->to_vec(), gw, 2e-6, "d cross_entropy_with");
+            CHECK(throws([&] { ls::cross_entropy(z, t1); }, "one_hot: -100 is outside"), "-100 without ignore_index");
+            CHECK(throws([&] { ls::cross_entropy_with(z, t0, nullptr, ls::CeOptions().with_smoothing(1.5)); }, "label smoothing"), "smoothing 1.5");
+        }
+        // kl_div: value, KL(a, a) = 0, and both gradients
+        {
+            Case r = make_case(950 + bf, -2.0, 2.0, bf, c.V);
+            Tensor q = Tensor::from_f32(c.logits, c.lsh(), dev, dt).require_grad(), p = Tensor::from_f32(r.logits, c.lsh(), dev, dt).require_grad();
+            Tensor k = ls::kl_div(q, p);
+            std::vector<double> want(c.S, 0.0), gq(c.n() * c.V), gp(c.n() * c.V);
+            for (size_t i = 0; i < c.n(); i++) {
+                auto lp = log_softmax_row(&r.logits[i * c.V], c.V);
+                double per = 0;
+                for (size_t v = 0; v < c.V; v++) per += std::exp(lp[v]) * (lp[v] - ys[i][v]);
+                want[i / N] += per / (double)N;
+                for (size_t v = 0; v < c.V; v++) {
+                    gq[i * c.V + v] = (std::exp(ys[i][v]) - std::exp(lp[v])) / (double)N;
+                    gp[i * c.V + v] = std::exp(lp[v]) * (lp[v] - ys[i][v] - per) / (double)N;
+                }
+            }
+            close_all(k.to_vec(), want, 2e-6, "kl_div");
+            Gradients g = backward(k);
+            close_all(g.grad(q)->to_vec(), gq, 2e-6, "d kl_div / d pred");
+            close_all(g.grad(p)->to_vec(), gp, 2e-6, "d kl_div / d target");
+            for (float x : ls::kl_div(q, q.detach()).to_vec()) CHECK(std::fabs(x) < 1e-6, "KL(a, a) = %g", x);
+            // a fixed teacher: only the prediction gets a gradient
+            Tensor k2 = ls::kl_div(q, p.detach());
+            Gradients g2 = backward(k2);
+            close_all(g2.grad(q)->to_vec(), gq, 2e-6, "d kl_div / d pred, detached target");
+        }
+    }
+}
+
 int main() {
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
@@ -475,6 +577,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"group_advantages", test_group_advantages}, {"ppo step", test_ppo_step},
+        {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {
         try {
