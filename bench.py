@@ -294,6 +294,22 @@ def run_extras(dev, peak):
         ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones, out=d)
 
     res["sparse_config5"] = entry(rows, _time(cfg5), rows * V5 * (5 + 5 + 4), "config 5 slice [rows,262144] bf16 + reference + masks allowing 1-8 tokens: masked sample+logp+KL forward + backward")
+    del x, r, m, d
+
+    # the pre-training loss on the same kernels: masked cross-entropy at V = 128256, forward + backward
+    from noetic_tensor_b200 import loss as nloss
+
+    S6, B6, T6 = 2, 4, 1024
+    rows = S6 * B6 * T6
+    x = synth.normal_logits(rows, V, 3.0, torch.bfloat16, gen, dev).reshape(S6, B6, T6, V)
+    tg = torch.randint(0, V, (S6, B6, T6), generator=gen, device=dev)
+    mk = (torch.rand(S6, B6, T6, generator=gen, device=dev) < 0.9).float()
+
+    def ce_step():
+        l = nloss.masked_cross_entropy(x, tg, mk)
+        return l.backward()
+
+    res["masked_cross_entropy_fwd_bwd"] = entry(rows, _time(ce_step), rows * V * (2 + 2 + 4), "nn::loss masked_cross_entropy [2,4,1024,128256] bf16: forward (one read) + backward to f32 d(logits)")
     return res
 
 
