@@ -7,7 +7,7 @@
 #include <mutex>
 
 #include "row_bwd.cuh"
-#include "row_fwd_kernels.cuh"
+#include "row_fwd_group.cuh"
 #include "token_ops.cuh"
 #include "ce_ops.cuh"
 
@@ -69,9 +69,25 @@ extern "C" uint64_t nrl_row_fwd_workspace_bytes(uint64_t rows, uint32_t V) {
     return ns == 1 ? 0 : rows * ns * kWarps * kPartFloats * sizeof(float);
 }
 
+// NRL_GROUPED=0 in the environment turns the grouped kernel off (for comparisons; read per call so
+// that a test can switch between the two kernels).
+static bool grouped_enabled() {
+    const char* e = getenv("NRL_GROUPED");
+    return !(e && e[0] == '0');
+}
+
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 static int launch_fwd(const FwdParams& p, cudaStream_t st) {
     if (p.nsplit == 1) {
+        if constexpr (ALLOW && VEC && !GENERAL) {
+            // many byte-masked rows: a block takes a group of rows and overlaps each row's tail with
+            // the next rows' streaming
+            const uint32_t part_vectors = (p.tiles_per_block + kWarps - 1) / kWarps * (kTile / kVec);
+            if (grouped_enabled() && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * kGroupRows && part_vectors < 0xffffu) {
+                row_fwd_grouped<DT, REF><<<(unsigned)((p.rows + kGroupRows - 1) / kGroupRows), kThreads, 0, st>>>(p);
+                return after_launch();
+            }
+        }
         row_fwd_fused<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)p.rows, kThreads, 0, st>>>(p);
         return after_launch();
     }

@@ -330,7 +330,11 @@ struct SampleLog {
     uint32_t tiles_per_chunk[kWarps];
 };
 constexpr int kLogDense = 64 / kWarps;     // chunks per part, unmasked path
+#ifdef NRL_LOG_COMPACT
+constexpr int kLogCompact = NRL_LOG_COMPACT;
+#else
 constexpr int kLogCompact = 128 / kWarps;  // batches per part, masked path
+#endif
 typedef SampleLog<kLogDense, false> DenseLog;
 typedef SampleLog<kLogCompact, true> CompactLog;
 
@@ -428,14 +432,23 @@ __device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t 
 // stay bitwise reproducible.
 constexpr int kQueue = 256;  // ring entries per warp: 31 left over + 4 tiles × 32 lanes, rounded up
 constexpr int kAhead = 4;    // mask tiles scanned per group
+#ifndef NRL_AHEAD_REF
+#define NRL_AHEAD_REF 4
+#endif
+constexpr int kAheadRef = NRL_AHEAD_REF;  // the same with a reference stream (more registers held per vector)
 
-template <int DT, bool REF, bool LOG>
-__device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* queue, CompactLog* log) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// Streams part `part_index` of a row with one warp. `wq` is the calling warp's kQueue-entry ring;
+// `sink(batch, acc, pend_v)` is called by all 32 lanes once per folded batch when LOG (acc.G is
+// the lane's mass in that batch at maximum acc.m, pend_v the vector the lane folded or kNoEntry)
+// and must leave acc.G alone. Returns the part's partial (valid in lane 0) and, in `batches`, the
+// number of batches folded.
+template <int DT, bool REF, bool LOG, class Sink>
+__device__ __forceinline__ Partial stream_part_compact(const FwdParams& p, uint64_t row, uint32_t part_index, uint32_t* wq, Sink&& sink, uint32_t& batches) {
+    constexpr int kA = REF ? kAheadRef : kAhead;  // mask tiles scanned per group
+    const int lane = threadIdx.x & 31;
     const uint32_t lt = (1u << lane) - 1u;
     uint32_t begin, end;
-    part_range(p, split * kWarps + warp, begin, end);
-    uint32_t* wq = queue + warp * kQueue;
+    part_range(p, part_index, begin, end);
     typedef VecLoader<DT, REF, true, false, true> Loader;
     Acc acc = acc_empty();
     Loader pend;
@@ -447,10 +460,10 @@ __device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_
     const uint8_t* mp = p.allow + row * p.allow_stride + begin + lane * kVec;
     uint32_t v = begin + lane * kVec;
     uint32_t t0 = begin;  // warp-uniform tile base of the group in mk[]
-    uint32_t mk[kAhead];  // OR of a tile's eight mask bytes: all the scan needs
-    uint2 mn[kAhead];
+    uint32_t mk[kA];  // OR of a tile's eight mask bytes: all the scan needs
+    uint2 mn[kA];
 #pragma unroll
-    for (int j = 0; j < kAhead; j++) {
+    for (int j = 0; j < kA; j++) {
         uint2 q = (v + j * kTile < end) ? ldg_stream8(mp + j * kTile) : make_uint2(0u, 0u);
         mk[j] = q.x | q.y;
     }
@@ -463,23 +476,23 @@ __device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_
             // the next group's mask bytes fly while this group is scanned, and the group eight
             // ahead is pulled into L2 (one 128-byte line per lane 0..7) so that its loads are
             // short when their turn comes
-            const uint8_t* np = mp + kAhead * kTile;
-            const uint32_t nv = v + kAhead * kTile;
-            if (lane < 8 && t0 + 8 * kAhead * kTile + lane * 128 < end) prefetch_l2(mp - lane * kVec + 8 * kAhead * kTile + lane * 128);
+            const uint8_t* np = mp + kA * kTile;
+            const uint32_t nv = v + kA * kTile;
+            if (lane < 8 && t0 + 8 * kA * kTile + lane * 128 < end) prefetch_l2(mp - lane * kVec + 8 * kA * kTile + lane * 128);
 #pragma unroll
-            for (int j = 0; j < kAhead; j++) mn[j] = (nv + j * kTile < end) ? ldg_stream8(np + j * kTile) : make_uint2(0u, 0u);
+            for (int j = 0; j < kA; j++) mn[j] = (nv + j * kTile < end) ? ldg_stream8(np + j * kTile) : make_uint2(0u, 0u);
 #pragma unroll
-            for (int j = 0; j < kAhead; j++) {
+            for (int j = 0; j < kA; j++) {
                 const bool nz = mk[j] != 0u;
                 const uint32_t ball = __ballot_sync(0xffffffffu, nz);
                 if (nz) wq[(head + count + __popc(ball & lt)) & (kQueue - 1)] = v + j * kTile;
                 count += __popc(ball);
             }
 #pragma unroll
-            for (int j = 0; j < kAhead; j++) mk[j] = mn[j].x | mn[j].y;
+            for (int j = 0; j < kA; j++) mk[j] = mn[j].x | mn[j].y;
             mp = np;
             v = nv;
-            t0 += kAhead * kTile;
+            t0 += kA * kTile;
             __syncwarp();
         }
         while (count >= 32 || (!scanning && (count > 0 || pend_any))) {
@@ -501,11 +514,7 @@ __device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_
                 }
                 accumulate<REF, LOG>(acc, z, zr);
                 if (LOG) {  // one log chunk per batch: the lane's vector and what it added
-                    if (batch < (uint32_t)kLogCompact) {
-                        log->mass[warp][batch][lane] = acc.G;
-                        log->entry[warp][batch][lane] = pend_v;
-                        if (lane == 0) log->cmax[warp][batch] = acc.m;
-                    }
+                    sink(batch, acc, pend_v);
                     acc.G = 0.f;
                     batch++;
                 }
@@ -518,8 +527,23 @@ __device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_
         if (!scanning) break;
         __syncwarp();  // the batch's entries are read before the next group's pushes can reuse slots
     }
-    if (LOG && lane == 0) log->count[warp] = batch <= (uint32_t)kLogCompact ? batch : kLogOverflow;
-    const Partial part = partial_warp_reduce(acc_to_partial(acc));
+    batches = batch;
+    return partial_warp_reduce(acc_to_partial(acc));
+}
+
+// One block streams its range of a row: warp w takes part split·kWarps + w and logs per lane.
+template <int DT, bool REF, bool LOG>
+__device__ __forceinline__ void stream_block_compact(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint32_t* queue, CompactLog* log) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t batches = 0;
+    const Partial part = stream_part_compact<DT, REF, LOG>(p, row, split * kWarps + warp, queue + warp * kQueue, [&](uint32_t batch, const Acc& acc, uint32_t pend_v) {
+        if (batch < (uint32_t)kLogCompact) {
+            log->mass[warp][batch][lane] = acc.G;
+            log->entry[warp][batch][lane] = pend_v;
+            if (lane == 0) log->cmax[warp][batch] = acc.m;
+        }
+    }, batches);
+    if (LOG && lane == 0) log->count[warp] = batches <= (uint32_t)kLogCompact ? batches : kLogOverflow;
     if (lane == 0) sp[warp] = part;
 }
 

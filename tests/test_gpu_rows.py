@@ -279,3 +279,52 @@ def test_backward_accumulate_adds_into_d_logits(V, dtype, masked):
     ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=glp, g_kl=gkl, g_ent=gen, out=pre, accumulate=True)
     assert torch.equal(pre[score == 0], torch.full_like(pre[score == 0], 0.25))
     assert ((pre - 0.25 - whole).abs() <= 1e-6 + 1e-5 * whole.abs()).all()
+
+
+@pytest.mark.parametrize("rows,V,keep,ref", [(2400, 4104, 0.05, True), (2400, 32000, 0.75, True), (1500, 128256, 0.02, True), (1300, 128256, 0.6, False), (4096, 1000, 0.3, True)])
+def test_grouped_masked_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref):
+    """Many byte-masked rows take the grouped kernel (a block owns a few rows, its warps take
+    (row, part) tickets, a row's tail overlaps the next rows' streaming). Its per-row statistics
+    must equal the one-block-per-row kernel's bit for bit (same parts, same merge order); sampled
+    tokens may differ only on CDF boundary rows; the densest masks overflow the per-part log and
+    take the scan fallback."""
+    import os
+
+    from noetic_tensor_b200 import ops
+
+    g = torch.Generator(device=dev())
+    g.manual_seed(rows + V)
+    x = (torch.randn(rows, V, generator=g, device=dev()) * 2.5).to(torch.bfloat16)
+    r = (x.float() + 0.1 * torch.randn(rows, V, generator=g, device=dev())).to(torch.bfloat16) if ref else None
+    m = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
+    m[:, V // 2] = 1
+    m[7] = 0  # a row with no allowed token
+    u = torch.rand(rows, generator=g, device=dev())
+    runs = {}
+    for mode in ("1", "0"):
+        os.environ["NRL_GROUPED"] = mode
+        try:
+            runs[mode] = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+            again = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+            given = ops.row_forward(x, ref_logits=r, allow=m, tokens=runs[mode].tokens.clamp_min(0))
+        finally:
+            os.environ.pop("NRL_GROUPED", None)
+        assert torch.equal(again.tokens, runs[mode].tokens) and torch.equal(again.logp.view(torch.int32), runs[mode].logp.view(torch.int32))
+        ok = runs[mode].status == 0
+        assert torch.equal(given.logp.view(torch.int32)[ok], runs[mode].logp.view(torch.int32)[ok]), "log-prob of the given token differs from the sampled one's"
+    a, b = runs["1"], runs["0"]
+    assert a.status.cpu().tolist() == b.status.cpu().tolist() and a.status[7] == 1 and a.tokens[7] == -1
+    for name in ("rowstats", "entropy") + (("kl",) if ref else ()):
+        assert torch.equal(getattr(a, name).view(torch.int32), getattr(b, name).view(torch.int32)), name
+    differ = (a.tokens != b.tokens).nonzero().flatten()
+    idx = torch.unique(torch.cat([differ, torch.arange(0, rows, max(1, rows // 48), device=dev())]))
+    idx = idx[idx != 7]
+    xi = x[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    o = oracle.sample_inverse_cdf(xi, 1.0, u[idx].cpu().numpy(), allow=m[idx].cpu().numpy())
+    for f in (a, b):
+        tok = f.tokens[idx].cpu().numpy().astype(np.int64)
+        bad = (tok != o["tokens"]) & (o["boundary"] == 0)
+        assert not bad.any(), f"{bad.sum()} tokens differ from the oracle off the CDF boundaries"
+        same = tok == o["tokens"]
+        assert_close(f.logp[idx].cpu().numpy()[same], o["logp"][same], "logp")
+    assert len(differ) <= max(2, rows // 500), f"{len(differ)} rows differ between the two kernels"
