@@ -79,12 +79,18 @@ static bool grouped_enabled() {
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 static int launch_fwd(const FwdParams& p, cudaStream_t st) {
     if (p.nsplit == 1) {
-        if constexpr (ALLOW && VEC && !GENERAL) {
-            // many byte-masked rows: a block takes a group of rows and overlaps each row's tail with
-            // the next rows' streaming
-            const uint32_t part_vectors = (p.tiles_per_block + kWarps - 1) / kWarps * (kTile / kVec);
-            if (grouped_enabled() && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * kGroupRows && part_vectors < 0xffffu) {
-                row_fwd_grouped<DT, REF><<<(unsigned)((p.rows + kGroupRows - 1) / kGroupRows), kThreads, 0, st>>>(p);
+        if constexpr (VEC && !GENERAL) {
+            // many rows on a fast path: a block takes a group of rows and overlaps each row's tail
+            // with the next rows' streaming
+            FwdParams q = p;  // a row in kGroupSplit ranges of kWarps parts each
+            q.nsplit = kGroupSplit;
+            q.tiles_per_block = (p.tiles_per_block + q.nsplit - 1) / q.nsplit;
+            const uint32_t part_vectors = (q.tiles_per_block + q.parts_per_block - 1) / q.parts_per_block * (kTile / kVec);
+            // (unmasked bf16 rows that sample measured faster in the one-block-per-row kernel, whose whole
+            // block scans the token's part)
+            const bool faster = ALLOW || DT == NRL_F32 || !(p.flags & NRL_FWD_SAMPLE);
+            if (grouped_enabled() && faster && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * kGroupRows && part_vectors < 0xffffu && q.tiles_per_block >= 16) {
+                row_fwd_grouped<DT, REF, ALLOW><<<(unsigned)((p.rows + kGroupRows - 1) / kGroupRows), kThreads, 0, st>>>(q);
                 return after_launch();
             }
         }
@@ -150,6 +156,7 @@ static int fill_fwd_params(FwdParams& p, uint32_t dtype, uint32_t V, uint64_t ro
     p.tau = tau;
     p.nsplit = 1;
     p.tiles_per_block = (V + kTile - 1) / kTile;
+    p.parts_per_block = kWarps;
     return NRL_OK;
 }
 
@@ -240,7 +247,9 @@ extern "C" int nrl_row_fwd_static(const nrl_row_fwd_args* a, nrl_stream stream) 
 
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 static int launch_bwd(const BwdParams& p, cudaStream_t st) {
-    row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC><<<(unsigned)(p.in.rows * p.chunks_per_row), kBwdThreads, 0, st>>>(p);
+    const unsigned grid = (unsigned)(p.in.rows * p.chunks_per_row);
+    if (p.accumulate || p.g_uni || p.d_ref || !p.d_logits) row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC, true><<<grid, kBwdThreads, 0, st>>>(p);
+    else row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC, false><<<grid, kBwdThreads, 0, st>>>(p);
     return after_launch();
 }
 

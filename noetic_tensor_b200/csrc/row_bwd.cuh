@@ -36,7 +36,9 @@ __device__ __forceinline__ void store_grad8(float* out, uint32_t v, uint32_t v_e
 
 constexpr int kBwdThreads = 256;
 
-template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
+// EXTRA: the call uses `accumulate`, the label-smoothing upstream or the reference-side gradient;
+// without it the kernel is compiled with none of their code.
+template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC, bool EXTRA>
 __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     const FwdParams& f = p.in;
     const uint64_t row = blockIdx.x / p.chunks_per_row;
@@ -47,18 +49,19 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     const uint32_t vec_per = (nvec + p.chunks_per_row - 1) / p.chunks_per_row;
     const uint32_t v_begin = min(chunk * vec_per, nvec) * kVec;
     const uint32_t v_end = min(min((chunk + 1) * vec_per, nvec) * kVec, V);
-    float* out = p.d_logits ? p.d_logits + row * V : nullptr;
-    float* out_ref = (REF && p.d_ref) ? p.d_ref + row * V : nullptr;
+    float* out = (!EXTRA || p.d_logits) ? p.d_logits + row * V : nullptr;
+    float* out_ref = (EXTRA && REF && p.d_ref) ? p.d_ref + row * V : nullptr;
+    const bool accumulate = EXTRA && p.accumulate != 0u;
 
     const float glp = p.g_logp ? p.g_logp[row] : 0.f;
     const float gkl = (REF && p.g_kl) ? p.g_kl[row] : 0.f;
     const float gen = p.g_ent ? p.g_ent[row] : 0.f;
-    const float gun = p.g_uni ? p.g_uni[row] : 0.f;
+    const float gun = (EXTRA && p.g_uni) ? p.g_uni[row] : 0.f;
     const float gun_v = gun != 0.f ? __fdiv_rn(gun, (float)V) : 0.f;
     const bool vec_out = VEC && (((reinterpret_cast<uintptr_t>(p.d_logits) | reinterpret_cast<uintptr_t>(p.d_ref)) & 15u) == 0);
 
     if (glp == 0.f && gkl == 0.f && gen == 0.f && gun == 0.f) {
-        if (p.accumulate) return;  // adding exact zeros
+        if (accumulate) return;  // adding exact zeros
         // an unscored position: exact zeros, the inputs are not read
         const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (uint32_t v = v_begin + threadIdx.x * kVec; v < v_end; v += kBwdThreads * kVec) {
@@ -82,7 +85,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
             mk.load(f.allow, row * f.allow_stride + v);
             const bool holds_token = tok >= (int32_t)v && tok < (int32_t)(v + kVec);  // its entry gets g_lp even if excluded
             if (!mk.any() && !holds_token) {
-                if (p.accumulate) continue;
+                if (accumulate) continue;
                 const float zero[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 if (out) store_grad8(out, v, v_end, zero, vec_out);
                 if (out_ref) store_grad8(out_ref, v, v_end, zero, vec_out);
@@ -104,27 +107,28 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
                 c = fmaf(gkl, (lp - lr) - klv, c);            // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
             }
             c = fmaf(-gen, lp + hv, c);                       // d H / dz_j = −π_j (log π_j + H)
-            c += gun;                                         // d(−mean_v log π_v) / dz_j = π_j − 1/V
-            float d = (pi > 0.f ? pi * c : 0.f) - gun_v;      // a zero-probability token gets exactly 0
+            if (EXTRA) c += gun;                              // d(−mean_v log π_v) / dz_j = π_j − 1/V
+            float d = pi > 0.f ? pi * c : 0.f;                // a zero-probability token gets exactly 0
+            if (EXTRA) d -= gun_v;
             if ((int32_t)(v + i) == tok) d += glp;
             if (GENERAL && f.tau != 1.0f) d = __fdiv_rn(d, f.tau);
             g[i] = d;
-            if (REF) {                                        // d KL / dzr_j = ρ_j − π_j
+            if (EXTRA && REF && out_ref) {                    // d KL / dzr_j = ρ_j − π_j (block-uniform branch)
                 float dr = gkl * (ex2_approx(lr * kLog2e) - pi);
                 if (GENERAL && f.tau != 1.0f) dr = __fdiv_rn(dr, f.tau);
                 gr[i] = dr;
             }
         }
         if (out) {
-            if (p.accumulate) {
+            if (accumulate) {
 #pragma unroll
                 for (int i = 0; i < 8; i++)
                     if (v + i < v_end) g[i] += out[v + i];
             }
             store_grad8(out, v, v_end, g, vec_out);
         }
-        if (REF && out_ref) {
-            if (p.accumulate) {
+        if (EXTRA && REF && out_ref) {
+            if (accumulate) {
 #pragma unroll
                 for (int i = 0; i < 8; i++)
                     if (v + i < v_end) gr[i] += out_ref[v + i];

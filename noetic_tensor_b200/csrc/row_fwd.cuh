@@ -37,14 +37,15 @@ struct FwdParams {
     uint32_t V;
     uint32_t nsplit;
     uint32_t tiles_per_block;  // tiles of 256 elements per block
+    uint32_t parts_per_block;  // parts a block's range is cut into (kWarps, except in the grouped kernel)
     uint32_t flags;
     float tau;
 };
 
 // elements [begin, end) of part q (block split q / 16, warp q % 16)
 __device__ __forceinline__ void part_range(const FwdParams& p, uint32_t q, uint32_t& begin, uint32_t& end) {
-    uint32_t split = q / kWarps, w = q % kWarps;
-    uint32_t tpw = (p.tiles_per_block + kWarps - 1) / kWarps;
+    uint32_t split = q / p.parts_per_block, w = q % p.parts_per_block;
+    uint32_t tpw = (p.tiles_per_block + p.parts_per_block - 1) / p.parts_per_block;
     uint64_t t0 = (uint64_t)split * p.tiles_per_block + (uint64_t)w * tpw;
     uint64_t t1 = t0 + tpw;
     uint64_t tb = (uint64_t)(split + 1) * p.tiles_per_block;
@@ -338,17 +339,21 @@ constexpr int kLogCompact = 128 / kWarps;  // batches per part, masked path
 typedef SampleLog<kLogDense, false> DenseLog;
 typedef SampleLog<kLogCompact, true> CompactLog;
 
-template <int DT, bool REF, bool LOG>
-__device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint4* ring, DenseLog* log) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// Streams part `part_index` of an unmasked row with one warp through `wring`, the calling warp's
+// ring of kRingRows × 32 16-byte slots. With LOG, `sink(chunk, acc)` is called by all 32 lanes at
+// the end of every chunk of `tiles_per_chunk` tiles (acc.G is the lane's mass in the chunk at
+// maximum acc.m). Returns the part's partial (valid in lane 0).
+template <int DT, bool REF, bool LOG, class Sink>
+__device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_t row, uint32_t part_index, uint4* wring, Sink&& sink, uint32_t& chunks, uint32_t& tiles_per_chunk) {
+    const int lane = threadIdx.x & 31;
     constexpr int kPer = (DT == NRL_F32 ? 2 : 1);     // 16-byte pieces per lane per stream per tile
     constexpr int kRows = kPer * (REF ? 2 : 1);       // ring rows one tile takes
     constexpr int kSlots = kRingRows / kRows;         // tiles in flight
     constexpr uint32_t kEsize = (DT == NRL_F32 ? 4 : 2);
     uint32_t begin, end;
-    part_range(p, split * kWarps + warp, begin, end);
+    part_range(p, part_index, begin, end);
     Acc acc = acc_empty();
-    const uint32_t base = smem_addr(ring + warp * (kRingRows * 32) + lane);  // this lane's column of the ring
+    const uint32_t base = smem_addr(wring + lane);  // this lane's column of the ring
     const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kVec) * kEsize;
     const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kVec) * kEsize : nullptr;
     uint32_t v = begin + lane * kVec;  // the tile this lane consumes next
@@ -357,8 +362,7 @@ __device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t 
     const uint32_t gsz = (ntiles + kLogDense - 1) / kLogDense;
     uint32_t left = gsz, chunk = 0;
     auto flush = [&]() {
-        log->mass[warp][chunk][lane] = acc.G;
-        if (lane == 0) log->cmax[warp][chunk] = acc.m;
+        sink(chunk, acc);
         acc.G = 0.f;
         chunk++;
         left = gsz;
@@ -410,14 +414,25 @@ __device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t 
         }
     }
     cp_async_wait<0>();
-    if (LOG) {
-        if (left != gsz) flush();
-        if (lane == 0) {
-            log->count[warp] = chunk;
-            log->tiles_per_chunk[warp] = gsz;
-        }
+    if (LOG && left != gsz) flush();
+    chunks = chunk;
+    tiles_per_chunk = gsz;
+    return partial_warp_reduce(acc_to_partial(acc));
+}
+
+// One block streams its range of an unmasked row: warp w takes part split·kWarps + w and logs per lane.
+template <int DT, bool REF, bool LOG>
+__device__ __forceinline__ void stream_block_async(const FwdParams& p, uint64_t row, uint32_t split, Partial* sp, uint4* ring, DenseLog* log) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t chunks = 0, per = 0;
+    const Partial part = stream_part_async<DT, REF, LOG>(p, row, split * kWarps + warp, ring + warp * (kRingRows * 32), [&](uint32_t chunk, const Acc& acc) {
+        log->mass[warp][chunk][lane] = acc.G;
+        if (lane == 0) log->cmax[warp][chunk] = acc.m;
+    }, chunks, per);
+    if (LOG && lane == 0) {
+        log->count[warp] = chunks;
+        log->tiles_per_chunk[warp] = per;
     }
-    const Partial part = partial_warp_reduce(acc_to_partial(acc));
     if (lane == 0) sp[warp] = part;
 }
 

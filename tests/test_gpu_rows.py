@@ -281,11 +281,15 @@ def test_backward_accumulate_adds_into_d_logits(V, dtype, masked):
     assert ((pre - 0.25 - whole).abs() <= 1e-6 + 1e-5 * whole.abs()).all()
 
 
-@pytest.mark.parametrize("rows,V,keep,ref", [(2400, 4104, 0.05, True), (2400, 32000, 0.75, True), (1500, 128256, 0.02, True), (1300, 128256, 0.6, False), (4096, 1000, 0.3, True)])
-def test_grouped_masked_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref):
+@pytest.mark.parametrize("rows,V,keep,ref,dtype", [
+    (2400, 4104, 0.05, True, torch.bfloat16), (2400, 32000, 0.75, True, torch.bfloat16), (1500, 128256, 0.02, True, torch.bfloat16),
+    (1300, 128256, 0.6, False, torch.bfloat16), (4096, 1000, 0.3, True, torch.bfloat16), (1300, 32000, 0.2, True, torch.float32),
+    (2400, 32000, None, True, torch.bfloat16), (1300, 128256, None, False, torch.bfloat16), (1300, 32000, None, False, torch.float32),
+    (4096, 1000, None, True, torch.float32), (1200, 151936, None, True, torch.bfloat16)])
+def test_grouped_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref, dtype):
     """Many byte-masked rows take the grouped kernel (a block owns a few rows, its warps take
     (row, part) tickets, a row's tail overlaps the next rows' streaming). Its per-row statistics
-    must equal the one-block-per-row kernel's bit for bit (same parts, same merge order); sampled
+    must equal the one-block-per-row kernel's within the tolerance (it splits rows finer); sampled
     tokens may differ only on CDF boundary rows; the densest masks overflow the per-part log and
     take the scan fallback."""
     import os
@@ -294,11 +298,15 @@ def test_grouped_masked_forward_equals_the_per_row_kernel(oracle, rows, V, keep,
 
     g = torch.Generator(device=dev())
     g.manual_seed(rows + V)
-    x = (torch.randn(rows, V, generator=g, device=dev()) * 2.5).to(torch.bfloat16)
-    r = (x.float() + 0.1 * torch.randn(rows, V, generator=g, device=dev())).to(torch.bfloat16) if ref else None
-    m = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
-    m[:, V // 2] = 1
-    m[7] = 0  # a row with no allowed token
+    x = (torch.randn(rows, V, generator=g, device=dev()) * 2.5).to(dtype)
+    r = (x.float() + 0.1 * torch.randn(rows, V, generator=g, device=dev())).to(dtype) if ref else None
+    m = None
+    if keep is not None:
+        m = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
+        m[:, V // 2] = 1
+        m[7] = 0  # a row with no allowed token
+    else:
+        x[7] = float("-inf")  # the same without a mask
     u = torch.rand(rows, generator=g, device=dev())
     runs = {}
     for mode in ("1", "0"):
@@ -314,17 +322,23 @@ def test_grouped_masked_forward_equals_the_per_row_kernel(oracle, rows, V, keep,
         assert torch.equal(given.logp.view(torch.int32)[ok], runs[mode].logp.view(torch.int32)[ok]), "log-prob of the given token differs from the sampled one's"
     a, b = runs["1"], runs["0"]
     assert a.status.cpu().tolist() == b.status.cpu().tolist() and a.status[7] == 1 and a.tokens[7] == -1
-    for name in ("rowstats", "entropy") + (("kl",) if ref else ()):
-        assert torch.equal(getattr(a, name).view(torch.int32), getattr(b, name).view(torch.int32)), name
+    okr = (a.status == 0).cpu().numpy()
+    for name in ("rowstats", "entropy", "logp") + (("kl",) if ref else ()):
+        ga, gb = getattr(a, name).cpu().numpy()[okr], getattr(b, name).cpu().numpy()[okr]
+        if name == "logp":
+            same_tok = (a.tokens == b.tokens).cpu().numpy()[okr]
+            ga, gb = ga[same_tok], gb[same_tok]
+        assert_close(ga, gb, name)  # the two kernels split a row into parts differently: equal to rounding
     differ = (a.tokens != b.tokens).nonzero().flatten()
     idx = torch.unique(torch.cat([differ, torch.arange(0, rows, max(1, rows // 48), device=dev())]))
     idx = idx[idx != 7]
-    xi = x[idx].view(torch.int16).cpu().numpy().view(np.uint16)
-    o = oracle.sample_inverse_cdf(xi, 1.0, u[idx].cpu().numpy(), allow=m[idx].cpu().numpy())
+    xi = x[idx].view(torch.int16).cpu().numpy().view(np.uint16) if dtype == torch.bfloat16 else x[idx].cpu().numpy()
+    o = oracle.sample_inverse_cdf(xi, 1.0, u[idx].cpu().numpy(), allow=None if m is None else m[idx].cpu().numpy())
     for f in (a, b):
         tok = f.tokens[idx].cpu().numpy().astype(np.int64)
         bad = (tok != o["tokens"]) & (o["boundary"] == 0)
         assert not bad.any(), f"{bad.sum()} tokens differ from the oracle off the CDF boundaries"
         same = tok == o["tokens"]
         assert_close(f.logp[idx].cpu().numpy()[same], o["logp"][same], "logp")
-    assert len(differ) <= max(2, rows // 500), f"{len(differ)} rows differ between the two kernels"
+    # (every differing row was checked above to be one of the oracle's boundary rows)
+    assert len(differ) <= max(4, rows // 50), f"{len(differ)} rows differ between the two kernels"
