@@ -309,6 +309,11 @@ def run_extras(dev, peak):
         l = nloss.masked_cross_entropy(x, tg, mk)
         return l.backward()
 
+    # the reference's own sampler on the device (Gumbel-max, one ChaCha20 u64 per logit): arithmetic-bound
+    xs, ms_ = x.reshape(rows, V)[:4096], synth.grammar_masks(4096, V, gen, dev)
+    seed = bytes(range(32))
+    t_g = _time(lambda: ops.sample_gumbel(xs, seed, allow=ms_))
+    res["reference_gumbel_sampler"] = entry(4096, t_g, 4096 * V * 3, "nrl_sample_gumbel on 4096 headline-shaped rows: tokens identical to the reference's sample_categorical for the same ChaCha20 seed (bytes = logits + mask; the kernel is bound by ChaCha20 and f64 logarithms, not by HBM)")
     res["masked_cross_entropy_fwd_bwd"] = entry(rows, _time(ce_step), rows * V * (2 + 2 + 4), "nn::loss masked_cross_entropy [2,4,1024,128256] bf16: forward (one read) + backward to f32 d(logits)")
     return res
 

@@ -273,6 +273,38 @@ typedef struct nrl_ce_args {
 
 int nrl_ce_tokens(const nrl_ce_args* args, nrl_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * The reference's own sampler on the device (sample_categorical + gumbel, src/nn/rl.rs:490-529):
+ * Gumbel-max with one ChaCha20 `next_u64` per logit in row-major order,
+ *   k = next_u64() >> 11;  u = (k + 1/2) / 2^53;  g = (f32)(-ln(-ln u));  token = first max of z + g,
+ * z = logits / temperature + mask in f32. The stream is rand_chacha 0.3's ChaCha20Rng of `seed`
+ * (20 rounds, 64-bit block counter, zero stream id; u64 = two consecutive 32-bit words, low
+ * first), entered `word_offset` 32-bit words after its start, so tokens equal the reference's for
+ * the same seed and position (its noise logarithms are glibc's, here CUDA's: both within 1 ulp in
+ * f64 before the cast to f32). The call consumes 2 * rows * V words: a caller that keeps drawing
+ * from the same generator advances its position by that much.
+ * temperature = 0 (greedy, no draws) is nrl_row_fwd with NRL_FWD_GREEDY. A row with no allowed
+ * token or a NaN gets token -1 and a status byte as in nrl_row_fwd (the reference panics before
+ * drawing anything, src/nn/rl.rs:516-519; check the status before using the generator further). */
+typedef struct nrl_gumbel_args {
+    uint32_t struct_size;
+    uint32_t dtype;
+    uint32_t V;
+    float temperature;         /* > 0 */
+    uint64_t rows;
+    nrl_devptr logits;         /* [rows, V] */
+    nrl_devptr allow_mask;     /* u8 as in nrl_row_fwd, or 0 */
+    uint64_t allow_row_stride;
+    nrl_devptr add_mask;       /* f32 additive mask as in nrl_row_fwd, or 0 */
+    uint64_t add_row_stride;
+    uint8_t seed[32];          /* the ChaCha20 key (rng::derive's SHA-256, src/rng.rs:10-17) */
+    uint64_t word_offset;      /* 32-bit words already drawn from the generator */
+    nrl_devptr tokens;         /* out i32 [rows] */
+    nrl_devptr status;         /* out u8 [rows], or 0 */
+} nrl_gumbel_args;
+
+int nrl_sample_gumbel(const nrl_gumbel_args* args, nrl_stream stream);
+
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
 int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
 

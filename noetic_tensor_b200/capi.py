@@ -55,6 +55,14 @@ class CeArgs(C.Structure):
     ]
 
 
+class GumbelArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("dtype", u32), ("V", u32), ("temperature", f32), ("rows", u64),
+        ("logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
+        ("seed", C.c_uint8 * 32), ("word_offset", u64), ("tokens", ptr), ("status", ptr),
+    ]
+
+
 # every symbol include/nrl.h declares, with its signature
 SYMBOLS = {
     "nrl_version": (C.c_int, []),
@@ -72,6 +80,7 @@ SYMBOLS = {
     "nrl_mask_rows": (C.c_int, [u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_row_sum": (C.c_int, [u32, u64, u32, ptr, ptr, C.c_void_p]),
     "nrl_ce_tokens": (C.c_int, [C.POINTER(CeArgs), C.c_void_p]),
+    "nrl_sample_gumbel": (C.c_int, [C.POINTER(GumbelArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
 }
 

@@ -10,6 +10,7 @@
 #include "row_fwd_group.cuh"
 #include "token_ops.cuh"
 #include "ce_ops.cuh"
+#include "gumbel.cuh"
 
 #define NRL_STR2(x) #x
 #define NRL_STR(x) NRL_STR2(x)
@@ -408,6 +409,35 @@ extern "C" int nrl_ce_tokens(const nrl_ce_args* a, nrl_stream stream) {
     uint64_t blocks = (p.n + 255) / 256;
     if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
     ce_tokens_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(p);
+    return after_launch();
+}
+
+// ---- the reference's Gumbel-max sampler ------------------------------------------------------------
+
+extern "C" int nrl_sample_gumbel(const nrl_gumbel_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_gumbel_args)) return NRL_E_BAD_ARG;
+    GumbelParams p;
+    memset(&p, 0, sizeof p);
+    int rc = fill_fwd_params(p.in, a->dtype, a->V, a->rows, a->temperature, a->logits, 0, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    if (rc) return rc;
+    if (!a->tokens || (a->tokens & 3u)) return NRL_E_BAD_ARG;
+    if (a->rows > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    for (int i = 0; i < 8; i++)
+        p.key[i] = (uint32_t)a->seed[4 * i] | (uint32_t)a->seed[4 * i + 1] << 8 | (uint32_t)a->seed[4 * i + 2] << 16 | (uint32_t)a->seed[4 * i + 3] << 24;
+    p.word_offset = a->word_offset;
+    p.tokens = (int32_t*)a->tokens;
+    p.status = (uint8_t*)a->status;
+    const bool vec = can_vectorise(a->V, a->logits, 0, a->allow_mask, a->allow_row_stride, a->add_mask, a->add_row_stride);
+    const unsigned grid = (unsigned)a->rows;
+    cudaStream_t st = (cudaStream_t)stream;
+#define NRL_GUMBEL(DT)                                                                                               \
+    do {                                                                                                             \
+        if (a->allow_mask) { if (vec) gumbel_argmax_kernel<DT, true, true><<<grid, kGumbelThreads, 0, st>>>(p); else gumbel_argmax_kernel<DT, true, false><<<grid, kGumbelThreads, 0, st>>>(p); } \
+        else               { if (vec) gumbel_argmax_kernel<DT, false, true><<<grid, kGumbelThreads, 0, st>>>(p); else gumbel_argmax_kernel<DT, false, false><<<grid, kGumbelThreads, 0, st>>>(p); } \
+    } while (0)
+    if (a->dtype == NRL_F32) NRL_GUMBEL(NRL_F32);
+    else NRL_GUMBEL(NRL_BF16);
+#undef NRL_GUMBEL
     return after_launch();
 }
 

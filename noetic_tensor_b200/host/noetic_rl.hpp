@@ -424,6 +424,49 @@ inline IntTensor sample_categorical(const Tensor& logits, double temperature, co
     return out;
 }
 
+// The state of a ChaCha20Rng (src/rng.rs:10-17 derives its 32-byte seed): the seed and the number
+// of 32-bit words drawn so far.
+struct ChaChaStream {
+    uint8_t seed[32];
+    uint64_t words = 0;
+};
+
+// src/nn/rl.rs:510-529 as the reference defines it: Gumbel-max with one `next_u64` of `rng` per
+// logit in row-major order, so the tokens are the reference's for the same generator state;
+// `rng` advances by what the reference's sampler draws. Temperature 0 draws nothing.
+inline IntTensor sample_categorical(const Tensor& logits, double temperature, const Tensor* mask, ChaChaStream& rng) {
+    if (!(temperature >= 0.0 && std::isfinite(temperature))) throw std::runtime_error("sample_categorical: temperature (must be >= 0)");
+    if (temperature == 0.0) return sample_categorical(logits, 0.0, mask, (const Tensor*)nullptr);
+    Tensor z = tempered_logits(logits.detach(), temperature, mask);
+    detail::Rows r = detail::rows_of(z);
+    Tensor tok = Tensor::empty(Shape{(size_t)r.rows}, DType::I32, z.device());
+    Tensor status = Tensor::empty(Shape{(size_t)r.rows}, DType::U8, z.device());
+    nrl_row_fwd_args f;
+    detail::fill_inputs(f, z, nullptr);
+    nrl_gumbel_args a;
+    std::memset(&a, 0, sizeof a);
+    a.struct_size = sizeof a;
+    a.dtype = f.dtype; a.V = f.V; a.temperature = f.temperature; a.rows = f.rows;
+    a.logits = f.logits; a.allow_mask = f.allow_mask; a.allow_row_stride = f.allow_row_stride; a.add_mask = f.add_mask; a.add_row_stride = f.add_row_stride;
+    std::memcpy(a.seed, rng.seed, 32);
+    a.word_offset = rng.words;
+    a.tokens = tok.dev();
+    a.status = status.dev();
+    nrl(nrl_sample_gumbel(&a, detail::stream()), "sample_gumbel");
+    uint64_t bad = 0;
+    uint32_t bits = 0;
+    int rc = nrl_check_status(status.dev(), r.rows, detail::stream(), &bad, &bits);
+    if (rc == NRL_E_ROW_STATUS) throw std::runtime_error("sample_categorical: position " + std::to_string(bad) + " has no allowed token (every logit −∞ or a NaN)");
+    nrl(rc, "check_status");
+    rng.words += 2ull * r.rows * r.V;
+    std::vector<int32_t> h(r.rows);
+    cu(cudaMemcpy(h.data(), tok.ptr(), h.size() * 4, cudaMemcpyDeviceToHost), "download tokens");
+    IntTensor out;
+    out.data.assign(h.begin(), h.end());
+    out.shape = detail::lead(logits);
+    return out;
+}
+
 namespace detail {
 // One forward over the rows with given tokens and/or a reference; fills `s`.
 inline void forward(const Tensor& z, const Tensor* ref, const IntTensor* tokens, Saved& s, Tensor* logp, bool want_kl, bool want_ent) {

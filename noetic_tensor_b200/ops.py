@@ -277,3 +277,29 @@ def ce_tokens(V, logp, *, smoothing=0.0, rowstats=None, logit_sum=None, keep=Non
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_ce_tokens(C.byref(a), _stream(dev)), "nrl_ce_tokens")
     return loss, g_logp, g_uni
+
+
+def sample_gumbel(logits, seed, *, word_offset=0, temperature=1.0, allow=None, add_mask=None):
+    """The reference's Gumbel-max sampler on the device (nrl_sample_gumbel): `seed` is the 32-byte
+    ChaCha20 key, `word_offset` the 32-bit words already drawn. Returns (tokens int32 [rows],
+    status uint8 [rows]); the call consumes 2·rows·V words of the stream."""
+    dev = logits.device
+    rows, V = logits.shape
+    if not logits.is_contiguous():
+        raise ValueError("logits must be contiguous")
+    if len(seed) != 32:
+        raise ValueError("seed: 32 bytes")
+    a = capi.GumbelArgs()
+    a.struct_size = C.sizeof(a)
+    a.dtype, a.V, a.rows, a.temperature = _dt(logits), V, rows, float(temperature)
+    a.logits = _p(logits)
+    allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
+    a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
+    a.seed[:] = list(seed)
+    a.word_offset = int(word_offset)
+    tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    status = torch.empty(rows, dtype=torch.uint8, device=dev)
+    a.tokens, a.status = _p(tokens), _p(status)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_sample_gumbel(C.byref(a), _stream(dev)), "nrl_sample_gumbel")
+    return tokens, status

@@ -94,6 +94,37 @@ def sample_categorical(logits, temperature=1.0, vocab_mask=None, uniforms=None):
     return f.tokens.reshape(lead), f.logp.reshape(lead)
 
 
+class ChaChaStream:
+    """The position of a `ChaCha20Rng` (src/rng.rs:10-17 derives its 32-byte seed): the seed and
+    the number of 32-bit words drawn so far. `sample_categorical_reference` advances it as the
+    reference's sampler advances its generator."""
+
+    def __init__(self, seed, words=0):
+        if len(seed) != 32:
+            raise ValueError("seed: 32 bytes")
+        self.seed, self.words = bytes(seed), int(words)
+
+
+def sample_categorical_reference(logits, temperature, vocab_mask, rng):
+    """`sample_categorical(logits, temperature, mask, rng)` with the reference's own noise
+    (src/nn/rl.rs:510-529): Gumbel-max, one `next_u64` of `rng` per logit in row-major order, so the
+    tokens are the reference's for the same generator state. Temperature 0 is the first maximum
+    and draws nothing. Refuses a position with no allowed token before drawing, as the reference
+    does. Returns tokens [...] (int32)."""
+    if temperature < 0:
+        raise ValueError(f"sample_categorical: temperature {temperature} (must be ≥ 0)")
+    z = Tempered(logits, 1.0 if temperature == 0.0 else temperature, vocab_mask)
+    lead = z.shape[:-1]
+    if temperature == 0.0:
+        f = ops.row_forward(z.flat, greedy=True, want_entropy=False, want_logp=False, **z.kw())
+        ops.check_status(f.status)
+        return f.tokens.reshape(lead)
+    tokens, status = ops.sample_gumbel(z.flat, rng.seed, word_offset=rng.words, **z.kw())
+    ops.check_status(status)
+    rng.words += 2 * z.flat.shape[0] * z.V
+    return tokens.reshape(lead)
+
+
 class _TokenLogProbs:
     """token_log_probs (src/nn/rl.rs:134-141) and its backward to the logits."""
 

@@ -415,6 +415,88 @@ static void test_sample_categorical() {
     CHECK(throws([&] { rl::sample_categorical(tz, -1.0, nullptr, &tu); }, "temperature"), "negative temperature");
 }
 
+// ---- sample_categorical with the reference's own noise (src/nn/rl.rs:490-529) -------------------
+// Host restatement for the check: ChaCha20 (RFC 8439 block function, 64-bit counter, as
+// rand_chacha's ChaCha20Rng), one u64 per logit, noise in f64, first maximum in f32.
+struct HostChaCha {
+    uint32_t key[8];
+    uint64_t counter = 0;
+    uint32_t buf[16];
+    int idx = 16;
+    static uint32_t rotl(uint32_t x, int n) { return (x << n) | (x >> (32 - n)); }
+    static void qr(uint32_t* s, int a, int b, int c, int d) {
+        s[a] += s[b]; s[d] ^= s[a]; s[d] = rotl(s[d], 16);
+        s[c] += s[d]; s[b] ^= s[c]; s[b] = rotl(s[b], 12);
+        s[a] += s[b]; s[d] ^= s[a]; s[d] = rotl(s[d], 8);
+        s[c] += s[d]; s[b] ^= s[c]; s[b] = rotl(s[b], 7);
+    }
+    explicit HostChaCha(const uint8_t seed[32]) {
+        for (int i = 0; i < 8; i++) key[i] = (uint32_t)seed[4 * i] | (uint32_t)seed[4 * i + 1] << 8 | (uint32_t)seed[4 * i + 2] << 16 | (uint32_t)seed[4 * i + 3] << 24;
+    }
+    uint32_t next_u32() {
+        if (idx >= 16) {
+            uint32_t in[16] = {0x61707865, 0x3320646e, 0x79622d32, 0x6b206574};
+            for (int i = 0; i < 8; i++) in[4 + i] = key[i];
+            in[12] = (uint32_t)counter; in[13] = (uint32_t)(counter >> 32); in[14] = in[15] = 0;
+            uint32_t s[16];
+            std::memcpy(s, in, sizeof s);
+            for (int r = 0; r < 10; r++) {
+                qr(s, 0, 4, 8, 12); qr(s, 1, 5, 9, 13); qr(s, 2, 6, 10, 14); qr(s, 3, 7, 11, 15);
+                qr(s, 0, 5, 10, 15); qr(s, 1, 6, 11, 12); qr(s, 2, 7, 8, 13); qr(s, 3, 4, 9, 14);
+            }
+            for (int i = 0; i < 16; i++) buf[i] = s[i] + in[i];
+            counter++;
+            idx = 0;
+        }
+        return buf[idx++];
+    }
+    uint64_t next_u64() {
+        uint64_t lo = next_u32(), hi = next_u32();
+        return hi << 32 | lo;
+    }
+};
+
+static void test_sample_categorical_reference() {
+    using rl::ChaChaStream;
+    const size_t rows = 24, V = 1000;
+    std::mt19937_64 g(930);
+    std::uniform_real_distribution<double> u(-3, 3);
+    std::vector<float> z(rows * V), add(V);
+    for (float& x : z) x = (float)u(g);
+    for (size_t v = 0; v < V; v++) add[v] = v % 7 == 3 ? -INFINITY : 0.f;
+    Tensor tz = Tensor::from_f32(z, Shape{1, 2, rows / 2, V}, dev), tm = Tensor::from_f32(add, Shape{1, 1, 1, V}, dev);
+    ChaChaStream rng;
+    for (int i = 0; i < 32; i++) rng.seed[i] = (uint8_t)(37 * i + 11);
+    const float tau = 0.7f;
+    IntTensor first = rl::sample_categorical(tz, tau, &tm, rng);
+    CHECK(rng.words == 2 * rows * V, "the generator advanced by %llu words", (unsigned long long)rng.words);
+    IntTensor second = rl::sample_categorical(tz, tau, &tm, rng);  // continues the same stream
+    HostChaCha h(rng.seed);
+    for (int pass = 0; pass < 2; pass++) {
+        const IntTensor& got = pass ? second : first;
+        for (size_t r = 0; r < rows; r++) {
+            float best = -INFINITY;
+            int64_t bi = -1;
+            for (size_t v = 0; v < V; v++) {
+                const uint64_t k = h.next_u64() >> 11;
+                const double uu = ((double)k + 0.5) / 9007199254740992.0;
+                const float gn = (float)(-std::log(-std::log(uu)));
+                const float y = (z[r * V + v] / tau + add[v]) + gn;
+                if (y > best) { best = y; bi = (int64_t)v; }
+            }
+            CHECK(got.data[r] == bi, "pass %d row %zu: token %lld, the reference sampler gives %lld", pass, r, (long long)got.data[r], (long long)bi);
+            CHECK(got.data[r] % 7 != 3, "an excluded token was drawn");
+        }
+    }
+    ChaChaStream again = rng;
+    again.words = 0;
+    CHECK(rl::sample_categorical(tz, tau, &tm, again).data == first.data, "the same generator state gives the same tokens");
+    // temperature 0 draws nothing
+    ChaChaStream still = rng;
+    rl::sample_categorical(tz, 0.0, &tm, still);
+    CHECK(still.words == rng.words, "greedy sampling consumed the generator");
+}
+
 // ---- group_advantages (src/nn/tests/rl.rs:550-575, 644-653) ------------------------------------
 static void test_group_advantages() {
     auto a = rl::group_advantages({1, 2, 3, 5, 5, 5}, 3, rl::GroupNorm::MeanOnly());
@@ -576,6 +658,7 @@ int main() {
         {"token_log_probs", test_token_log_probs}, {"policy_gradient_loss", test_policy_gradient},
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
+        {"sample_categorical (reference noise)", test_sample_categorical_reference},
         {"group_advantages", test_group_advantages}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
