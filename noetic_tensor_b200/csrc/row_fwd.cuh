@@ -13,6 +13,8 @@
 // u·Z is found from the parts' masses, then that one part (a few KB, an L2 hit) is re-read and
 // scanned in element order.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace nrl {
