@@ -87,11 +87,8 @@ static int launch_fwd(const FwdParams& p, cudaStream_t st) {
             q.nsplit = kGroupSplit;
             q.tiles_per_block = (p.tiles_per_block + q.nsplit - 1) / q.nsplit;
             const uint32_t part_vectors = (q.tiles_per_block + q.parts_per_block - 1) / q.parts_per_block * (kTile / kVec);
-            // (unmasked bf16 rows that sample measured faster in the one-block-per-row kernel, whose whole
-            // block scans the token's part)
-            const bool faster = ALLOW || DT == NRL_F32 || !(p.flags & NRL_FWD_SAMPLE);
-            if (grouped_enabled() && faster && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * kGroupRows && part_vectors < 0xffffu && q.tiles_per_block >= 16) {
-                row_fwd_grouped<DT, REF, ALLOW><<<(unsigned)((p.rows + kGroupRows - 1) / kGroupRows), kThreads, 0, st>>>(q);
+            if (grouped_enabled() && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * group_rows<ALLOW>() && part_vectors < 0xffffu && q.tiles_per_block >= 16) {
+                row_fwd_grouped<DT, REF, ALLOW><<<(unsigned)((p.rows + group_rows<ALLOW>() - 1) / group_rows<ALLOW>()), kThreads, 0, st>>>(q);
                 return after_launch();
             }
         }

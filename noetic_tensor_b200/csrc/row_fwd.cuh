@@ -356,9 +356,14 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     part_range(p, part_index, begin, end);
     Acc acc = acc_empty();
     const uint32_t base = smem_addr(wring + lane);  // this lane's column of the ring
-    const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kVec) * kEsize;
-    const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kVec) * kEsize : nullptr;
-    uint32_t v = begin + lane * kVec;  // the tile this lane consumes next
+    // Every warp-wide copy covers 512 contiguous bytes. With 2-byte elements a lane's piece is its
+    // 8 elements of the tile; with 4-byte elements a lane takes two pieces of 4 elements, 128
+    // elements apart (lane·4 … and 128 + lane·4 …), so that neither copy touches half sectors.
+    constexpr uint32_t kLaneElems = 16 / kEsize;  // elements per 16-byte piece
+    constexpr uint32_t kPieceGap = 128;           // F32: elements between a lane's two pieces
+    const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kLaneElems) * kEsize;
+    const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kLaneElems) * kEsize : nullptr;
+    uint32_t v = begin + lane * kLaneElems;  // this lane's first element of the tile it consumes next
     // sampling log: chunks of `gsz` tiles, at most kLogDense of them
     const uint32_t ntiles = (end - begin + kTile - 1) / kTile;
     const uint32_t gsz = (ntiles + kLogDense - 1) / kLogDense;
@@ -370,11 +375,11 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
         left = gsz;
     };
     auto issue = [&](int slot, uint32_t vv, const char* xq, const char* rq) {
-        if (vv < end) {
 #pragma unroll
-            for (int k = 0; k < kPer; k++) {
-                cp_async16(base + (slot * kRows + k) * 512, xq + 16 * k);
-                if (REF) cp_async16(base + (slot * kRows + kPer + k) * 512, rq + 16 * k);
+        for (int k = 0; k < kPer; k++) {
+            if (vv + k * kPieceGap < end) {
+                cp_async16(base + (slot * kRows + k) * 512, xq + 512 * k);
+                if (REF) cp_async16(base + (slot * kRows + kPer + k) * 512, rq + 512 * k);
             }
         }
         cp_async_commit();  // one group per tile, empty or not, so that the group count stays in step
@@ -401,9 +406,13 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
                 float z[8], zr[8];
                 x.unpack(z);
                 if (REF) r.unpack(zr);
-                if (v >= end) {  // a lane past the end of a ragged last tile: nothing copied, nothing to add
+                // a piece past the end of a ragged last tile: nothing was copied, nothing to add
 #pragma unroll
-                    for (int i = 0; i < 8; i++) z[i] = zr[i] = -FLT_MAX;
+                for (int k = 0; k < kPer; k++) {
+                    if (v + k * kPieceGap >= end) {
+#pragma unroll
+                        for (int i = k * (8 / kPer); i < (k + 1) * (8 / kPer); i++) z[i] = zr[i] = -FLT_MAX;
+                    }
                 }
                 accumulate<REF, LOG>(acc, z, zr);
                 if (LOG && --left == 0) flush();

@@ -3,16 +3,16 @@
 // In the one-block-per-row kernel a row ends with a tail — merge the part partials, find the
 // token, read its logits, write the outputs — during which one warp works through a chain of
 // dependent loads while the block's other warps wait, and before it every warp waits for the
-// row's slowest part. Here a block takes a group of kGroupRows consecutive rows. Its warps take
-// (row, part) tickets from a counter in shared memory, rows in order; a warp streams one part,
-// and the warp that delivers a row's last part runs that row's tail while the other warps are
-// already streaming the next rows' parts. Each row of the group has its own result buffer, so no
-// warp ever waits for another: there is no spin, no barrier after the first, and nothing that
-// could hang.
+// row's slowest part. Here a block takes a group of consecutive rows (group_rows). Its warps take
+// (row, part) tickets from a counter in shared memory, rows in order, and stream one part per
+// ticket into the row's own result buffer, so heavy and light parts balance over the group and
+// nothing is waited for. After one barrier at the end the rows' tails run side by side, one warp
+// per row: their latency is paid once per group instead of once per row. There is no spin and
+// nothing that could hang.
 //
 // Every result is a pure function of (row, part): which warp streams a part and when does not
-// enter any sum, and parts are merged in index order, so results are bitwise reproducible (and
-// equal to the one-block-per-row kernel's to rounding: that kernel splits a row into fewer parts).
+// enter any sum, and parts are merged in index order, so results are bitwise reproducible and
+// the row statistics equal the one-block-per-row kernel's bit for bit.
 #pragma once
 #include "row_fwd_kernels.cuh"
 
@@ -24,13 +24,23 @@ namespace nrl {
 #ifndef NRL_GROUP_SPLIT
 #define NRL_GROUP_SPLIT 1
 #endif
-constexpr int kGroupRows = NRL_GROUP_ROWS;        // rows per block
+#ifndef NRL_GROUP_ROWS_DENSE
+#define NRL_GROUP_ROWS_DENSE 4
+#endif
+// rows per block: the per-row buffers of masked rows hold the batch log and are larger
+template <bool ALLOW>
+__host__ __device__ constexpr int group_rows() {
+    return ALLOW ? NRL_GROUP_ROWS : NRL_GROUP_ROWS_DENSE;
+}
 // Parts per row = kGroupSplit · kWarps. Finer parts would balance the tickets better (the warp
 // that runs a row's tail falls behind and tends to take the next row's last ticket too), but each
 // part pays for filling and draining the load pipeline: one part per warp measured fastest.
 constexpr int kGroupSplit = NRL_GROUP_SPLIT;
 constexpr int kGroupParts = kGroupSplit * kWarps;
-constexpr int kPLog = 64 / kGroupSplit;           // logged batches per part, masked rows
+#ifndef NRL_PLOG
+#define NRL_PLOG (64 / kGroupSplit)
+#endif
+constexpr int kPLog = NRL_PLOG;                   // logged batches per part, masked rows
 
 // What the streaming pass leaves per part for the token pick.
 // Masked rows: a batch is 32 consecutive live vectors (vectors with an allowed token) of the part
@@ -242,10 +252,9 @@ __device__ __forceinline__ int32_t pick_from_chunk_log(const FwdParams& p, uint6
 template <bool ALLOW>
 struct GroupShared {
     typedef typename std::conditional<ALLOW, MaskedPartLog, DensePartLog>::type Log;
-    Partial sp[kGroupRows][kGroupParts];
-    Log log[kGroupRows][kGroupParts];
+    Partial sp[group_rows<ALLOW>()][kGroupParts];
+    Log log[group_rows<ALLOW>()][kGroupParts];
     RowResult res[kWarps];
-    uint32_t arrived[kGroupRows];  // parts delivered per row
     uint32_t next_ticket;
 };
 
@@ -272,19 +281,16 @@ __global__ void __launch_bounds__(kThreads, group_blocks<REF, ALLOW>()) row_fwd_
     // the staging area of the streaming loop: the vector queue (masked) or the copy ring (unmasked)
     __shared__ __align__(16) uint32_t stage[ALLOW ? kWarps * kQueue : kWarps * kRingRows * 32 * 4];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int b = 0; b < kGroupRows; b++) sh.arrived[b] = 0u;
-        sh.next_ticket = 0u;
-    }
+    if (threadIdx.x == 0) sh.next_ticket = 0u;
     __syncthreads();
-    const uint64_t row0 = (uint64_t)blockIdx.x * kGroupRows;
+    const uint64_t row0 = (uint64_t)blockIdx.x * group_rows<ALLOW>();
     const uint64_t left = p.rows - row0;
-    const uint32_t nrows = (uint32_t)(left < (uint64_t)kGroupRows ? left : (uint64_t)kGroupRows);
+    const uint32_t nrows = (uint32_t)(left < (uint64_t)group_rows<ALLOW>() ? left : (uint64_t)group_rows<ALLOW>());
     const bool sampling = (p.flags & NRL_FWD_SAMPLE) != 0;
     uint32_t* wstage = stage + warp * (ALLOW ? kQueue : kRingRows * 32 * 4);
 
     // one part of one row of the group, streamed by the calling warp and delivered to the row's buffer
-    auto stream_one = [&](uint32_t b, uint32_t part) -> bool {
+    auto stream_one = [&](uint32_t b, uint32_t part) {
         const uint64_t row = row0 + b;
         auto* lg = &sh.log[b][part];
         Partial mine;
@@ -324,17 +330,10 @@ __global__ void __launch_bounds__(kThreads, group_blocks<REF, ALLOW>()) row_fwd_
             }
         }
         if (lane == 0) sh.sp[b][part] = mine;
-        __syncwarp();
-        __threadfence_block();  // the part's results are visible before its arrival is
-        uint32_t before = 0;
-        if (lane == 0) before = atomicAdd(&sh.arrived[b], 1u);
-        before = __shfl_sync(0xffffffffu, before, 0);
-        return before == kGroupParts - 1;  // this warp delivered the row's last part
     };
     // a row's tail, by the calling warp, once all its parts are delivered
     auto tail_one = [&](uint32_t b) {
         const uint64_t row = row0 + b;
-        __threadfence_block();
         finalize_row(p, row, kGroupParts, [&](uint32_t q) { return sh.sp[b][q]; }, &sh.res[warp]);
         __syncwarp();
         const RowResult res = sh.res[warp];
@@ -353,9 +352,11 @@ __global__ void __launch_bounds__(kThreads, group_blocks<REF, ALLOW>()) row_fwd_
         if (lane == 0) t = atomicAdd(&sh.next_ticket, 1u);
         t = __shfl_sync(0xffffffffu, t, 0);
         if (t >= nrows * kGroupParts) break;
-        const uint32_t b = t / kGroupParts;
-        if (stream_one(b, t % kGroupParts)) tail_one(b);
+        stream_one(t / kGroupParts, t % kGroupParts);
     }
+    // every part of every row of the group is delivered: the rows' tails, one warp per row, side by side
+    __syncthreads();
+    for (uint32_t b = (uint32_t)warp; b < nrows; b += kWarps) tail_one(b);
 }
 
 }  // namespace nrl
