@@ -34,7 +34,7 @@ METRIC = "rows/s fused sample+logprob+KL+entropy, V=128256 bf16"
 FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch ÷ algorithmic bytes per launch, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the current kernel).
-NCU_TRAFFIC_RATIO = 0.633  # profiles/row_fwd_grouped_bf16_ref_allow_4096rows.md: 1.6614 GB of DRAM traffic per 2.6267 GB algorithmic
+NCU_TRAFFIC_RATIO = 0.626  # profiles/row_fwd_grouped_bf16_ref_allow_4096rows.md: 1.6437 GB of DRAM traffic per 2.6267 GB algorithmic
 # Measured-peak read bandwidth of a pure streaming read kernel on this pool (for context only).
 
 
