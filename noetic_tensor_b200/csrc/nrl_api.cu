@@ -246,7 +246,17 @@ extern "C" int nrl_row_fwd_static(const nrl_row_fwd_args* a, nrl_stream stream) 
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 static int launch_bwd(const BwdParams& p, cudaStream_t st) {
     const unsigned grid = (unsigned)(p.in.rows * p.chunks_per_row);
-    if (p.accumulate || p.g_uni || p.d_ref || !p.d_logits) row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC, true><<<grid, kBwdThreads, 0, st>>>(p);
+    const bool extra = p.accumulate || p.g_uni || p.d_ref || !p.d_logits;
+    // f32 logits, and bf16 logits alone (the cross-entropy backward): stores and loads that fill whole
+    // sectors measured faster. With a mask or a reference stream the 8-element mapping, with its
+    // fewer and wider loads, measured as fast or faster, so those stay on it.
+    if constexpr (VEC && !GENERAL && (DT == NRL_F32 || (!ALLOW && !REF))) {
+        if (!extra && aligned16((uint64_t)(uintptr_t)p.d_logits)) {
+            row_bwd_split_kernel<DT, REF, ALLOW><<<grid, kBwdThreads, 0, st>>>(p);
+            return after_launch();
+        }
+    }
+    if (extra) row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC, true><<<grid, kBwdThreads, 0, st>>>(p);
     else row_bwd_kernel<DT, REF, ALLOW, GENERAL, VEC, false><<<grid, kBwdThreads, 0, st>>>(p);
     return after_launch();
 }

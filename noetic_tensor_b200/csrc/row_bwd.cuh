@@ -138,4 +138,125 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
     }
 }
 
+// ---- the common case: vectorised inputs, no temperature / additive mask, none of the extras --------
+//
+// The gradient is f32, so a lane that owned 8 consecutive elements would write 32 bytes with
+// two 16-byte stores, and each warp-wide store would touch every 32-byte sector of a kilobyte
+// but fill only half of it. Here a warp owns a 256-element tile as two 128-element halves and a
+// lane takes 4 consecutive elements of each (element 4·lane and 128 + 4·lane of the tile): every
+// warp-wide store, and every load of f32 logits, covers 512 contiguous bytes. bf16 logits arrive
+// as 8-byte loads (256 contiguous bytes per warp), mask bytes as 4-byte loads.
+__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+
+template <int DT>
+struct Piece {  // 4 consecutive elements of one stream
+    uint4 q;    // bf16: x, y hold them; f32: all four words
+    __device__ __forceinline__ void load(const void* base, uint64_t elem) {
+        if constexpr (DT == NRL_BF16) {
+            const uint2 h = ldg_stream8((const uint16_t*)base + elem);
+            q = make_uint4(h.x, h.y, 0u, 0u);
+        } else {
+            q = ldg_stream16((const float*)base + elem);
+        }
+    }
+    __device__ __forceinline__ void unpack(float z[4]) const {
+        if constexpr (DT == NRL_BF16) {
+            z[0] = bf16_lo(q.x); z[1] = bf16_hi(q.x); z[2] = bf16_lo(q.y); z[3] = bf16_hi(q.y);
+        } else {
+            z[0] = __uint_as_float(q.x); z[1] = __uint_as_float(q.y); z[2] = __uint_as_float(q.z); z[3] = __uint_as_float(q.w);
+        }
+    }
+};
+
+template <int DT, bool REF, bool ALLOW>
+__global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_split_kernel(BwdParams p) {
+    const FwdParams& f = p.in;
+    const uint64_t row = blockIdx.x / p.chunks_per_row;
+    const uint32_t chunk = blockIdx.x % p.chunks_per_row;
+    const uint32_t V = f.V;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // this block's range of the row, in whole tiles
+    const uint32_t ntiles = (V + kTile - 1) / kTile;
+    const uint32_t tiles_per = (ntiles + p.chunks_per_row - 1) / p.chunks_per_row;
+    const uint32_t t_begin = min(chunk * tiles_per, ntiles) * kTile;
+    const uint32_t t_end = min(min((chunk + 1) * tiles_per, ntiles) * kTile, V);
+    float* out = p.d_logits + row * V;
+    constexpr uint32_t kHalf = kTile / 2, kStep = (kBwdThreads / 32) * kTile;
+
+    const float glp = p.g_logp ? p.g_logp[row] : 0.f;
+    const float gkl = (REF && p.g_kl) ? p.g_kl[row] : 0.f;
+    const float gen = p.g_ent ? p.g_ent[row] : 0.f;
+    if (glp == 0.f && gkl == 0.f && gen == 0.f) {
+        // an unscored position: exact zeros, the inputs are not read
+        for (uint32_t t = t_begin + warp * kTile; t < t_end; t += kStep) {
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const uint32_t e = t + k * kHalf + lane * 4;
+                if (e < t_end) stg_stream16(out + e, 0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        return;
+    }
+    const float4 st = reinterpret_cast<const float4*>(p.rowstats)[row];
+    const float m = st.x, lnZ = st.y, mr = st.z, lnZr = st.w;
+    const float klv = (REF && p.kl && gkl != 0.f) ? p.kl[row] : 0.f;
+    const float hv = (p.entropy && gen != 0.f) ? p.entropy[row] : 0.f;
+    const int32_t tok = (p.tokens && glp != 0.f) ? p.tokens[row] : -1;
+    const uint8_t* mrow = ALLOW ? f.allow + row * f.allow_stride : nullptr;
+
+    for (uint32_t t = t_begin + warp * kTile; t < t_end; t += kStep) {
+        uint32_t e[2], mk[2];
+        bool live[2];
+        Piece<DT> x[2], r[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            e[k] = t + k * kHalf + lane * 4;
+            mk[k] = 0xffffffffu;
+            if (ALLOW) mk[k] = e[k] < t_end ? ldg_stream4(mrow + e[k]) : 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            // an excluded piece has zero gradient whatever its logits are (only its mask bytes are
+            // read), unless it holds the token, whose entry gets g_lp even if excluded
+            const bool holds_token = tok >= (int32_t)e[k] && tok < (int32_t)(e[k] + 4);
+            live[k] = e[k] < t_end && (mk[k] != 0u || holds_token);
+            if (live[k]) {
+                x[k].load(f.logits, row * V + e[k]);
+                if (REF) r[k].load(f.ref, row * V + e[k]);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            if (e[k] >= t_end) continue;
+            float g[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live[k]) {
+                float z[4], zr[4];
+                x[k].unpack(z);
+                if (REF) r[k].unpack(zr);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const bool ok = !ALLOW || ((mk[k] >> (8 * i)) & 0xffu) != 0u;
+                    const float zc = ok ? fmaxf(z[i], -FLT_MAX) : -FLT_MAX;
+                    const float lp = (zc - m) - lnZ;
+                    const float pi = ex2_approx(lp * kLog2e);
+                    float c = -glp;                                   // d logp / dz_j = 1[j = tok] − π_j
+                    if (REF) {
+                        const float zrc = ok ? zr[i] : -FLT_MAX;
+                        c = fmaf(gkl, (lp - ((zrc - mr) - lnZr)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+                    }
+                    c = fmaf(-gen, lp + hv, c);                       // d H / dz_j = −π_j (log π_j + H)
+                    float d = pi > 0.f ? pi * c : 0.f;                // a zero-probability token gets exactly 0
+                    if ((int32_t)(e[k] + i) == tok) d += glp;
+                    g[i] = d;
+                }
+            }
+            stg_stream16(out + e[k], g[0], g[1], g[2], g[3]);
+        }
+    }
+}
+
 }  // namespace nrl
