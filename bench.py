@@ -462,9 +462,10 @@ def run_ours(args):
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
         h2d, d2h = hf.bytes_per_row()
-        e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": e2e_rows * h2d, "d2h_bytes_per_step": e2e_rows * d2h,
+        e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": int(hf.h2d_bytes), "d2h_bytes_per_step": e2e_rows * d2h,
+               "host_bytes_per_step": e2e_rows * h2d, "packed_chunks": hf.packed_chunks, "whole_chunks": hf.whole_chunks, "host_threads": hf.threads,
                "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
-               "note": "host-resident bf16 logits + reference + mask streamed over PCIe in 512-row chunks, double-buffered; bound by the host link, not by HBM"}
+               "note": "host-resident bf16 logits + reference + mask (host_bytes_per_step, pinned) through the host path in 512-row chunks, double-buffered: host threads keep the vectors the mask allows (nrl_host_pack), h2d_bytes_per_step cross PCIe, a kernel puts them in place (nrl_unpack_rows), then the same forward; the packing runs inside the timed region"}
 
     extras = None
     if rank == 0 and not args.no_extras:
@@ -504,7 +505,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
-    ap.add_argument("--e2e-rows", type=int, default=2048)
+    ap.add_argument("--e2e-rows", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--variant", default="headline", choices=["headline", "unmasked"], help="unmasked: drop the mask (for profiling the every-byte-read path); not the headline")
     ap.add_argument("--no-e2e", action="store_true")

@@ -305,6 +305,53 @@ typedef struct nrl_gumbel_args {
 
 int nrl_sample_gumbel(const nrl_gumbel_args* args, nrl_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Rows that live in HOST memory (no counterpart in the reference, whose tensors are uploaded
+ * whole, src/tensor/gpu/mod.rs:472-481): the byte-masked forward never reads a logit the mask
+ * excludes, so those need not cross PCIe.
+ * nrl_host_pack runs on `threads` host threads (no CUDA call): per row it writes one liveness bit
+ * per 8-element vector (a vector is live when any of its 8 mask bytes is non-zero) and, for the
+ * live vectors in row order, their logits, reference logits and 8 mask bytes. The output arrays
+ * are the caller's (pinned, for the copies that follow). Returns NRL_E_WORKSPACE with
+ * `live_vectors` set when `capacity` is too small: upload the rows whole instead.
+ * nrl_unpack_rows (one kernel) takes the device copies of those arrays and writes the live vectors
+ * to their places in the full [rows, V] logits / reference buffers and the full byte mask (zeros
+ * for the rest); other elements of the logits buffers keep whatever they held. The buffers are
+ * then what nrl_row_fwd / nrl_row_bwd take with that mask. V must be a multiple of 8, V <= 262144. */
+typedef struct nrl_pack_args {
+    uint32_t struct_size;
+    uint32_t dtype;
+    uint32_t V;
+    uint32_t threads;
+    uint64_t rows;
+    const void* logits;         /* host [rows, V] */
+    const void* ref_logits;     /* host [rows, V] or NULL */
+    const uint8_t* allow_mask;  /* host u8 [rows, V] */
+    uint64_t capacity;          /* live vectors the packed arrays can hold */
+    uint64_t* live_words;       /* out host u64 [rows, ceil(V / 8 / 64)]: bit j of word w = vector 64w + j is live */
+    uint32_t* row_offset;       /* out host u32 [rows + 1]: live vectors before each row */
+    void* packed_logits;        /* out host [capacity, 8] elements */
+    void* packed_ref;           /* out host [capacity, 8] elements, or NULL */
+    uint64_t* packed_mask;      /* out host [capacity]: the 8 mask bytes of each live vector */
+    uint64_t live_vectors;      /* out */
+} nrl_pack_args;
+
+int nrl_host_pack(nrl_pack_args* args);
+
+typedef struct nrl_unpack_args {
+    uint32_t struct_size;
+    uint32_t dtype;
+    uint32_t V;
+    uint32_t reserved0;
+    uint64_t rows;
+    nrl_devptr live_words, row_offset, packed_logits, packed_ref, packed_mask; /* device copies of nrl_host_pack's outputs */
+    nrl_devptr logits;      /* out [rows, V]: live vectors written */
+    nrl_devptr ref_logits;  /* out [rows, V] or 0 (with packed_ref 0) */
+    nrl_devptr allow_mask;  /* out u8 [rows, V]: written in full */
+} nrl_unpack_args;
+
+int nrl_unpack_rows(const nrl_unpack_args* args, nrl_stream stream);
+
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
 int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
 

@@ -63,6 +63,23 @@ class GumbelArgs(C.Structure):
     ]
 
 
+class PackArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("dtype", u32), ("V", u32), ("threads", u32), ("rows", u64),
+        ("logits", C.c_void_p), ("ref_logits", C.c_void_p), ("allow_mask", C.c_void_p), ("capacity", u64),
+        ("live_words", C.c_void_p), ("row_offset", C.c_void_p), ("packed_logits", C.c_void_p), ("packed_ref", C.c_void_p), ("packed_mask", C.c_void_p),
+        ("live_vectors", u64),
+    ]
+
+
+class UnpackArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("dtype", u32), ("V", u32), ("reserved0", u32), ("rows", u64),
+        ("live_words", ptr), ("row_offset", ptr), ("packed_logits", ptr), ("packed_ref", ptr), ("packed_mask", ptr),
+        ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr),
+    ]
+
+
 # every symbol include/nrl.h declares, with its signature
 SYMBOLS = {
     "nrl_version": (C.c_int, []),
@@ -81,6 +98,8 @@ SYMBOLS = {
     "nrl_row_sum": (C.c_int, [u32, u64, u32, ptr, ptr, C.c_void_p]),
     "nrl_ce_tokens": (C.c_int, [C.POINTER(CeArgs), C.c_void_p]),
     "nrl_sample_gumbel": (C.c_int, [C.POINTER(GumbelArgs), C.c_void_p]),
+    "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
+    "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
 }
 

@@ -11,6 +11,7 @@
 #include "token_ops.cuh"
 #include "ce_ops.cuh"
 #include "gumbel.cuh"
+#include "host_pack.cuh"
 
 #define NRL_STR2(x) #x
 #define NRL_STR(x) NRL_STR2(x)
@@ -445,6 +446,36 @@ extern "C" int nrl_sample_gumbel(const nrl_gumbel_args* a, nrl_stream stream) {
     if (a->dtype == NRL_F32) NRL_GUMBEL(NRL_F32);
     else NRL_GUMBEL(NRL_BF16);
 #undef NRL_GUMBEL
+    return after_launch();
+}
+
+// ---- host-resident rows --------------------------------------------------------------------------
+
+extern "C" int nrl_host_pack(nrl_pack_args* a) {
+    if (!a || a->struct_size != sizeof(nrl_pack_args)) return NRL_E_BAD_ARG;
+    if (a->rows == 0 || a->V == 0 || a->V % kVec != 0 || a->V > 262144u) return NRL_E_BAD_ARG;
+    if (!a->logits || !a->allow_mask || !a->live_words || !a->row_offset || !a->packed_logits || !a->packed_mask) return NRL_E_BAD_ARG;
+    if ((a->ref_logits != nullptr) != (a->packed_ref != nullptr)) return NRL_E_BAD_ARG;
+    if (a->dtype == NRL_BF16) return a->ref_logits ? host_pack_impl<2, true>(a) : host_pack_impl<2, false>(a);
+    if (a->dtype == NRL_F32) return a->ref_logits ? host_pack_impl<4, true>(a) : host_pack_impl<4, false>(a);
+    return NRL_E_UNSUPPORTED;
+}
+
+extern "C" int nrl_unpack_rows(const nrl_unpack_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_unpack_args)) return NRL_E_BAD_ARG;
+    if (a->rows == 0 || a->V == 0 || a->V % kVec != 0 || a->V > 262144u || a->rows > 0x7fffffffull) return NRL_E_BAD_ARG;
+    if (!a->live_words || !a->row_offset || !a->packed_logits || !a->packed_mask || !a->logits || !a->allow_mask) return NRL_E_BAD_ARG;
+    if ((a->ref_logits != 0) != (a->packed_ref != 0)) return NRL_E_BAD_ARG;
+    if ((a->logits | a->ref_logits | a->allow_mask | a->packed_logits | a->packed_ref) & 15u) return NRL_E_BAD_ARG;
+    if ((a->packed_mask | a->live_words) & 7u) return NRL_E_BAD_ARG;
+    const unsigned grid = (unsigned)a->rows;
+    cudaStream_t st = (cudaStream_t)stream;
+#define NRL_UNPACK(ES, RF) unpack_rows_kernel<ES, RF><<<grid, 256, 0, st>>>(a->V, (const uint64_t*)a->live_words, (const uint32_t*)a->row_offset, (const uint4*)a->packed_logits, \
+                                                                          (const uint4*)a->packed_ref, (const uint2*)a->packed_mask, (char*)a->logits, (char*)a->ref_logits, (uint8_t*)a->allow_mask)
+    if (a->dtype == NRL_BF16) { if (a->ref_logits) NRL_UNPACK(2, true); else NRL_UNPACK(2, false); }
+    else if (a->dtype == NRL_F32) { if (a->ref_logits) NRL_UNPACK(4, true); else NRL_UNPACK(4, false); }
+    else return NRL_E_UNSUPPORTED;
+#undef NRL_UNPACK
     return after_launch();
 }
 

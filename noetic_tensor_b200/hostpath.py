@@ -4,18 +4,31 @@ Rows are independent, so host batches are streamed through the GPU in row chunks
 is reduced on the compute stream, chunk i+1 crosses PCIe on a copy stream into the other of two
 device slots, and the per-row results of chunk i−1 go back to pinned host memory. The device
 never holds more than two chunks. All arithmetic is libnrl.so's; this file only moves bytes.
+
+With a byte mask the link carries only what the forward reads (`packed=True`, the default): host
+threads keep one liveness bit per 8-element vector and the logits, reference logits and mask
+bytes of the live vectors (nrl_host_pack), and a kernel puts them back in place on the device
+(nrl_unpack_rows). A chunk whose live vectors outgrow the staging buffers is uploaded whole.
 """
+import ctypes as C
+import os
+
 import torch
 
-from . import ops
+from . import capi, ops
 
 
 class HostForward:
-    def __init__(self, V, dtype, *, chunk_rows=512, ref=True, mask=True, device="cuda:0"):
+    def __init__(self, V, dtype, *, chunk_rows=512, ref=True, mask=True, device="cuda:0", packed=True, live_fraction=0.25, threads=None):
         self.dev = torch.device(device)
         self.V, self.dtype, self.chunk = V, dtype, chunk_rows
         self.has_ref, self.has_mask = ref, mask
+        self.packed = bool(packed and mask and V % 8 == 0 and V <= 262144)
+        self.threads = int(threads or min(os.cpu_count() or 1, 32))
+        self.words = (V // 8 + 63) // 64
+        self.capacity = max(1, int(chunk_rows * (V // 8) * live_fraction))  # live vectors a chunk's staging buffers hold
         mk = lambda dt, *shape: torch.empty(*shape, dtype=dt, device=self.dev)
+        pin = lambda dt, *shape: torch.empty(*shape, dtype=dt).pin_memory()
         self.slots = []
         for _ in range(2):
             s = dict(x=mk(dtype, chunk_rows, V), u=mk(torch.float32, chunk_rows))
@@ -23,15 +36,59 @@ class HostForward:
                 s["r"] = mk(dtype, chunk_rows, V)
             if mask:
                 s["m"] = mk(torch.uint8, chunk_rows, V)
+            if self.packed:
+                for where, make in (("h", pin), ("d", mk)):
+                    s[where + "_words"] = make(torch.int64, chunk_rows, self.words)
+                    s[where + "_off"] = make(torch.int32, chunk_rows + 1)
+                    s[where + "_px"] = make(dtype, self.capacity, 8)
+                    if ref:
+                        s[where + "_pr"] = make(dtype, self.capacity, 8)
+                    s[where + "_pm"] = make(torch.int64, self.capacity)
+                s["staged"] = torch.cuda.Event()  # the copies out of this slot's pinned staging buffers have finished
             s["ready"] = torch.cuda.Event()
             s["free"] = torch.cuda.Event()
             self.slots.append(s)
+        self.packed_chunks = self.whole_chunks = 0
         self.copy_stream = torch.cuda.Stream(self.dev)
         self.back_stream = torch.cuda.Stream(self.dev)
 
     def bytes_per_row(self):
+        """(host→device bytes of a row uploaded whole, device→host bytes of its results); what a
+        call actually sent is in `h2d_bytes` after it."""
         e = torch.empty(0, dtype=self.dtype).element_size()
         return self.V * (e * (2 if self.has_ref else 1) + (1 if self.has_mask else 0)) + 4, 4 * 4 + 1
+
+    def _pack(self, s, i, logits, ref, mask, r0, r1):
+        """Host threads compact rows [r0, r1) into the slot's pinned staging buffers. Returns the
+        number of live vectors, or None when they do not fit (the chunk is then uploaded whole)."""
+        if i >= 2:
+            s["staged"].synchronize()  # the previous copies out of these staging buffers are done
+        a = capi.PackArgs()
+        a.struct_size = C.sizeof(a)
+        a.dtype, a.V, a.threads, a.rows, a.capacity = (capi.F32 if self.dtype == torch.float32 else capi.BF16), self.V, self.threads, r1 - r0, self.capacity
+        esize = logits.element_size()
+        a.logits = logits.data_ptr() + r0 * self.V * esize
+        a.ref_logits = ref.data_ptr() + r0 * self.V * esize if self.has_ref else None
+        a.allow_mask = mask.data_ptr() + r0 * self.V
+        a.live_words, a.row_offset = s["h_words"].data_ptr(), s["h_off"].data_ptr()
+        a.packed_logits, a.packed_mask = s["h_px"].data_ptr(), s["h_pm"].data_ptr()
+        a.packed_ref = s["h_pr"].data_ptr() if self.has_ref else None
+        rc = capi.lib().nrl_host_pack(C.byref(a))
+        if rc == capi.E_WORKSPACE:
+            return None
+        capi.check(rc, "nrl_host_pack")
+        return int(a.live_vectors)
+
+    def _unpack(self, s, n):
+        a = capi.UnpackArgs()
+        a.struct_size = C.sizeof(a)
+        a.dtype, a.V, a.rows = (capi.F32 if self.dtype == torch.float32 else capi.BF16), self.V, n
+        a.live_words, a.row_offset = s["d_words"].data_ptr(), s["d_off"].data_ptr()
+        a.packed_logits, a.packed_mask = s["d_px"].data_ptr(), s["d_pm"].data_ptr()
+        a.packed_ref = s["d_pr"].data_ptr() if self.has_ref else 0
+        a.logits, a.allow_mask = s["x"].data_ptr(), s["m"].data_ptr()
+        a.ref_logits = s["r"].data_ptr() if self.has_ref else 0
+        capi.check(capi.lib().nrl_unpack_rows(C.byref(a), C.c_void_p(self.copy_stream.cuda_stream)), "nrl_unpack_rows")
 
     def run(self, logits, uniforms, ref=None, mask=None, out=None):
         """logits/ref [rows, V], mask [rows, V] u8, uniforms [rows]: pinned host tensors. Returns
@@ -42,19 +99,36 @@ class HostForward:
             out = dict(tokens=pin(torch.int32), logp=pin(torch.float32), kl=pin(torch.float32), entropy=pin(torch.float32), status=pin(torch.uint8))
         compute = torch.cuda.current_stream(self.dev)
         done = []
+        self.h2d_bytes = 0  # bytes this call sends to the device
+        esize = logits.element_size()
         for i, r0 in enumerate(range(0, rows, self.chunk)):
             r1 = min(rows, r0 + self.chunk)
             n = r1 - r0
             s = self.slots[i % 2]
+            live = self._pack(s, i, logits, ref, mask, r0, r1) if self.packed else None
             with torch.cuda.stream(self.copy_stream):
                 if i >= 2:
                     self.copy_stream.wait_event(s["free"])  # the kernel that read this slot has finished
-                s["x"][:n].copy_(logits[r0:r1], non_blocking=True)
                 s["u"][:n].copy_(uniforms[r0:r1], non_blocking=True)
-                if self.has_ref:
-                    s["r"][:n].copy_(ref[r0:r1], non_blocking=True)
-                if self.has_mask:
-                    s["m"][:n].copy_(mask[r0:r1], non_blocking=True)
+                if live is not None:
+                    s["d_words"][:n].copy_(s["h_words"][:n], non_blocking=True)
+                    s["d_off"][: n + 1].copy_(s["h_off"][: n + 1], non_blocking=True)
+                    s["d_px"][:live].copy_(s["h_px"][:live], non_blocking=True)
+                    if self.has_ref:
+                        s["d_pr"][:live].copy_(s["h_pr"][:live], non_blocking=True)
+                    s["d_pm"][:live].copy_(s["h_pm"][:live], non_blocking=True)
+                    s["staged"].record(self.copy_stream)
+                    self._unpack(s, n)
+                    self.packed_chunks += 1
+                    self.h2d_bytes += n * 4 + n * self.words * 8 + (n + 1) * 4 + live * (8 * esize * (2 if self.has_ref else 1) + 8)
+                else:
+                    s["x"][:n].copy_(logits[r0:r1], non_blocking=True)
+                    if self.has_ref:
+                        s["r"][:n].copy_(ref[r0:r1], non_blocking=True)
+                    if self.has_mask:
+                        s["m"][:n].copy_(mask[r0:r1], non_blocking=True)
+                    self.whole_chunks += 1
+                    self.h2d_bytes += n * self.bytes_per_row()[0]
                 s["ready"].record(self.copy_stream)
             compute.wait_event(s["ready"])
             f = ops.row_forward(s["x"][:n], ref_logits=s["r"][:n] if self.has_ref else None, allow=s["m"][:n] if self.has_mask else None, uniforms=s["u"][:n])
