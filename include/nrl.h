@@ -352,8 +352,56 @@ typedef struct nrl_unpack_args {
 
 int nrl_unpack_rows(const nrl_unpack_args* args, nrl_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Generic reductions along the last axis of a contiguous [rows, V] tensor, one block per row with
+ * 64-bit offsets. They replace the CUDA backend's lane kernels, which put ONE THREAD on a whole
+ * row (sum_last_f32, argmax_dim_f32: src/tensor/cuda/kernels.rs:625-670) and compose softmax,
+ * log_softmax and logsumexp from 6 generic launches each (src/tensor/activation.rs:15-42, 71-77).
+ *   NRL_LANE_SOFTMAX         out[r, :] = exp(x − max) / Σ exp(x − max)         activation.rs:15-26
+ *   NRL_LANE_LOG_SOFTMAX     out[r, :] = (x − max) − log Σ exp(x − max)         activation.rs:30-42
+ *   NRL_LANE_LOGSUMEXP       out[r] = m + log Σ exp(x − m), m = 0 where max is ±inf  activation.rs:71-77
+ *   NRL_LANE_ARGMAX          out_index[r] (i32) = first maximum, the first NaN if the row holds one;
+ *                            out (optional, f32 [rows]) = its value           kernels.rs:184-209
+ *   NRL_LANE_SUM             out[r] = Σ_v x[r, v] in the reference's operand order (eight partial
+ *                            sums, (p0+p4)+(p1+p5)+(p2+p6)+(p3+p7), then the tail): bit-equal to
+ *                            Cpu(Reference) and to sum_last_f32                kernels.rs:122-148
+ *   NRL_LANE_SOFTMAX_BWD     out = y · (g − Σ g·y)      x = the saved output y (f32), g f32 [rows, V]
+ *   NRL_LANE_LOG_SOFTMAX_BWD out = g − exp(y) · Σ g     x = the saved output y (f32), g f32 [rows, V]
+ *   NRL_LANE_LOGSUMEXP_BWD   out = g[r] · exp(x − lse[r])   x = the input, lse = the saved output, g f32 [rows]
+ * x is F32 or BF16 for the forward ops and for NRL_LANE_LOGSUMEXP_BWD, F32 for the other two
+ * backward ops. Outputs are F32. A row of −inf alone, or one holding NaN, gives NaN from softmax and
+ * log_softmax as in the reference. `out` must not alias an input. Rows take 16-byte loads when V
+ * is a multiple of 8 and x, g, out are 16-byte aligned; other shapes run an element-wise loop. */
+enum {
+    NRL_LANE_SOFTMAX = 0, NRL_LANE_LOG_SOFTMAX = 1, NRL_LANE_LOGSUMEXP = 2, NRL_LANE_ARGMAX = 3, NRL_LANE_SUM = 4,
+    NRL_LANE_SOFTMAX_BWD = 5, NRL_LANE_LOG_SOFTMAX_BWD = 6, NRL_LANE_LOGSUMEXP_BWD = 7
+};
+
+typedef struct nrl_lane_args {
+    uint32_t struct_size;
+    uint32_t op;
+    uint32_t dtype;        /* of x */
+    uint32_t V;
+    uint64_t rows;
+    nrl_devptr x;          /* [rows, V] */
+    nrl_devptr g;          /* backward ops: upstream gradient */
+    nrl_devptr lse;        /* NRL_LANE_LOGSUMEXP_BWD: f32 [rows] */
+    nrl_devptr out;        /* f32 [rows, V] or [rows]; optional for NRL_LANE_ARGMAX */
+    nrl_devptr out_index;  /* NRL_LANE_ARGMAX: i32 [rows] */
+} nrl_lane_args;
+
+int nrl_lane_op(const nrl_lane_args* args, nrl_stream stream);
+
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
 int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
+
+/* group_advantages_tensor (src/nn/rl.rs:436-469) without the host round trip: rewards f32
+ * [groups, n] on the device -> advantages f32 [groups, n], each reward minus its group's mean and,
+ * with norm_std, divided by the group's standard deviation (sample when `unbiased`, which needs
+ * n >= 2) plus eps. Computed in f64 in the host function's operand order and rounded to f32 once,
+ * so the values are the reference's bit for bit; a group whose rewards are all equal gives exact
+ * zeros. NRL_E_BAD_ARG for eps < 0 or unbiased with n < 2 (the reference's assertions). */
+int nrl_group_advantages(uint64_t groups, uint32_t n, uint32_t norm_std, double eps, uint32_t unbiased, nrl_devptr rewards, nrl_devptr out, nrl_stream stream);
 
 /* Reads `status` (u8 [rows], device) back and returns NRL_E_ROW_STATUS with the first bad row in
  * *first_bad_row if any byte is non-zero. Synchronises the stream: this is the host read the

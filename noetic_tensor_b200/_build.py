@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnrl.so")
 SOURCES = ["nrl_api.cu"]
-HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh"]
+HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh", "lane_ops.cuh"]
 INCLUDE = os.path.join(os.path.dirname(HERE), "include", "nrl.h")
 
 

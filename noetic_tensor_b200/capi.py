@@ -80,6 +80,16 @@ class UnpackArgs(C.Structure):
     ]
 
 
+class LaneArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("op", u32), ("dtype", u32), ("V", u32), ("rows", u64),
+        ("x", ptr), ("g", ptr), ("lse", ptr), ("out", ptr), ("out_index", ptr),
+    ]
+
+
+LANE_SOFTMAX, LANE_LOG_SOFTMAX, LANE_LOGSUMEXP, LANE_ARGMAX, LANE_SUM, LANE_SOFTMAX_BWD, LANE_LOG_SOFTMAX_BWD, LANE_LOGSUMEXP_BWD = range(8)
+
+
 # every symbol include/nrl.h declares, with its signature
 SYMBOLS = {
     "nrl_version": (C.c_int, []),
@@ -98,6 +108,8 @@ SYMBOLS = {
     "nrl_row_sum": (C.c_int, [u32, u64, u32, ptr, ptr, C.c_void_p]),
     "nrl_ce_tokens": (C.c_int, [C.POINTER(CeArgs), C.c_void_p]),
     "nrl_sample_gumbel": (C.c_int, [C.POINTER(GumbelArgs), C.c_void_p]),
+    "nrl_group_advantages": (C.c_int, [u64, u32, u32, C.c_double, u32, ptr, ptr, C.c_void_p]),
+    "nrl_lane_op": (C.c_int, [C.POINTER(LaneArgs), C.c_void_p]),
     "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
     "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),

@@ -1,0 +1,299 @@
+// Generic reductions along the last axis ("lanes") of a [rows, V] tensor, block-per-row with
+// 64-bit offsets: softmax, log_softmax, logsumexp and their backward rules
+// (src/tensor/activation.rs:15-42, 71-77), the first-maximum NaN-propagating argmax
+// (src/tensor/kernels.rs:184-209, src/tensor/cuda/kernels.rs:656-670) and the lane sum in the
+// reference's own operand order (src/tensor/kernels.rs:122-148, cuda/kernels.rs:602-629), which is
+// bit-equal to Cpu(Reference) for f32 input.
+//
+// The softmax family reads a row twice (the second read is an L2 hit: a block re-reads the row it
+// has just streamed) and writes it once; reductions inside a block are warp butterflies followed
+// by a merge of the warps' results in index order, so results do not depend on timing.
+#pragma once
+#include "common.cuh"
+
+namespace nrl {
+
+constexpr int kLaneThreads = 256;       // default block; long rows run 1024-thread blocks, one per SM
+constexpr int kLaneMaxThreads = 1024;
+constexpr int kLaneMaxWarps = kLaneMaxThreads / 32;
+
+// Eight consecutive elements of a row as floats; `n` of them exist. VEC: 16-byte loads (every row
+// starts on a 16-byte boundary and V is a multiple of 8).
+template <int DT, bool VEC>
+__device__ __forceinline__ int lane_load8(const void* base, uint64_t row0, uint32_t v, uint32_t V, float z[8]) {
+    Raw<DT> raw;
+    const uint32_t e0 = v * kVec;
+    int n = kVec;
+    if (VEC) {
+        raw.load(base, row0 + e0);
+    } else {
+        n = (int)(V - e0 < (uint32_t)kVec ? V - e0 : (uint32_t)kVec);
+        raw.load_scalar(base, row0 + e0, n);
+    }
+    raw.unpack(z);
+    return n;
+}
+
+template <bool VEC>
+__device__ __forceinline__ void lane_store8(float* out, uint64_t row0, uint32_t v, int n, const float y[8]) {
+    float* p = out + row0 + (uint64_t)v * kVec;
+    if (VEC) {
+        stg_stream16(p, y[0], y[1], y[2], y[3]);
+        stg_stream16(p + 4, y[4], y[5], y[6], y[7]);
+    } else {
+#pragma unroll
+        for (int i = 0; i < kVec; i++)
+            if (i < n) p[i] = y[i];
+    }
+}
+
+// ---- block reductions in a fixed order ----------------------------------------------------------
+// (max, Σ exp(· − max)) pairs
+struct MaxSum {
+    float m, S;
+};
+__device__ __forceinline__ MaxSum maxsum_merge(MaxSum a, MaxSum b) {
+    const float mn = fmax_nan(a.m, b.m);
+    if (a.m != mn) a.S = (a.m == NRL_NEG_INF) ? 0.f : a.S * expf(a.m - mn);
+    if (b.m != mn) b.S = (b.m == NRL_NEG_INF) ? 0.f : b.S * expf(b.m - mn);
+    a.m = mn;
+    a.S = __fadd_rn(a.S, b.S);
+    return a;
+}
+__device__ __forceinline__ MaxSum block_maxsum(MaxSum p, float* sh /* 2 * kLaneMaxWarps */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        MaxSum o;
+        o.m = __shfl_xor_sync(0xffffffffu, p.m, s);
+        o.S = __shfl_xor_sync(0xffffffffu, p.S, s);
+        p = (threadIdx.x & s) == 0 ? maxsum_merge(p, o) : maxsum_merge(o, p);
+    }
+    __syncthreads();  // the previous row's readers of sh are done
+    if (lane == 0) { sh[2 * warp] = p.m; sh[2 * warp + 1] = p.S; }
+    __syncthreads();
+    MaxSum r;
+    r.m = sh[0]; r.S = sh[1];
+    const int nwarps = blockDim.x >> 5;
+    for (int w = 1; w < nwarps; w++) {
+        MaxSum o;
+        o.m = sh[2 * w]; o.S = sh[2 * w + 1];
+        r = maxsum_merge(r, o);
+    }
+    return r;  // every thread computes the same bits
+}
+
+__device__ __forceinline__ float block_sum(float x, float* sh /* kLaneMaxWarps */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) x = __fadd_rn(x, __shfl_xor_sync(0xffffffffu, x, s));
+    __syncthreads();
+    if (lane == 0) sh[warp] = x;
+    __syncthreads();
+    float r = sh[0];
+    const int nwarps = blockDim.x >> 5;
+    for (int w = 1; w < nwarps; w++) r = __fadd_rn(r, sh[w]);
+    return r;
+}
+
+// first maximum, the first NaN being the maximum of a lane that holds one
+__device__ __forceinline__ bool arg_better(float e, uint32_t i, float best, uint32_t idx) {
+    const bool en = e != e, bn = best != best;
+    if (en || bn) return en && (!bn || i < idx);
+    return e > best || (e == best && i < idx);
+}
+
+// ---- softmax / log_softmax / logsumexp forward -------------------------------------------------
+// One thread's (max, Σ exp) over the vectors v = threadIdx.x, threadIdx.x + 256, … of the row.
+// Elements beyond V read as −inf. While the running maximum is still −inf the sum is NaN
+// (−inf − −inf); the first finite element resets it, so a lane of −inf alone ends as NaN, as the
+// reference's (x − max).exp() does.
+template <int DT, bool VEC>
+__device__ __forceinline__ MaxSum lane_thread_maxsum(const void* x, uint64_t row0, uint32_t V, uint32_t nvec) {
+    MaxSum p;
+    p.m = NRL_NEG_INF;
+    p.S = 0.f;
+#pragma unroll 2
+    for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float z[8];
+        lane_load8<DT, VEC>(x, row0, v, V, z);
+        const float vmax = fmax_nan(fmax3_nan(z[0], z[1], z[2]), fmax_nan(fmax3_nan(z[3], z[4], z[5]), fmax_nan(z[6], z[7])));
+        const float mn = fmax_nan(p.m, vmax);
+        if (mn != p.m) {
+            p.S = (p.m == NRL_NEG_INF) ? 0.f : p.S * expf(p.m - mn);
+            p.m = mn;
+        }
+        float e[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) e[i] = ex2_approx((z[i] - p.m) * kLog2e);
+        p.S += ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+    }
+    return p;
+}
+
+template <int DT, bool VEC, bool LOG>
+__global__ void __launch_bounds__(kLaneMaxThreads) lane_softmax_kernel(const void* __restrict__ x, float* __restrict__ out, uint64_t rows, uint32_t V) {
+    __shared__ float sh[2 * kLaneMaxWarps];
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint64_t row0 = row * V;
+        const MaxSum p = block_maxsum(lane_thread_maxsum<DT, VEC>(x, row0, V, nvec), sh);
+        const float m = p.m, lnS = logf(p.S), inv = 1.f / p.S;
+#pragma unroll 2
+        for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float z[8], y[8];
+            const int n = lane_load8<DT, VEC>(x, row0, v, V, z);
+#pragma unroll
+            for (int i = 0; i < 8; i++) y[i] = LOG ? (z[i] - m) - lnS : ex2_approx((z[i] - m) * kLog2e) * inv;
+            lane_store8<VEC>(out, row0, v, n, y);
+        }
+    }
+}
+
+// m + log Σ exp(x − m), the shift dropped where m is ±inf (a lane of −inf gives −inf, one holding
+// +inf gives +inf); NaN propagates through the maximum.
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kLaneMaxThreads) lane_logsumexp_kernel(const void* __restrict__ x, float* __restrict__ out, uint64_t rows, uint32_t V) {
+    __shared__ float sh[2 * kLaneMaxWarps];
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const MaxSum p = block_maxsum(lane_thread_maxsum<DT, VEC>(x, row * V, V, nvec), sh);
+        if (threadIdx.x == 0) {
+            const float inf = __int_as_float(0x7f800000);
+            out[row] = (p.m == inf) ? inf : (p.m == -inf ? -inf : p.m + logf(p.S));
+        }
+    }
+}
+
+// dx = g[row] · exp(x − out[row])
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kLaneMaxThreads) lane_logsumexp_bwd_kernel(const void* __restrict__ x, const float* __restrict__ lse, const float* __restrict__ g,
+                                                                          float* __restrict__ dx, uint64_t rows, uint32_t V) {
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const float o = __ldg(lse + row), gr = __ldg(g + row);
+#pragma unroll 2
+        for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float z[8], y[8];
+            const int n = lane_load8<DT, VEC>(x, row * V, v, V, z);
+#pragma unroll
+            for (int i = 0; i < 8; i++) y[i] = gr * ex2_approx((z[i] - o) * kLog2e);
+            lane_store8<VEC>(dx, row * V, v, n, y);
+        }
+    }
+}
+
+// softmax: dx = y · (g − Σ g·y);  log_softmax: dx = g − exp(y) · Σ g   (y the saved output, f32)
+template <bool VEC, bool LOG>
+__global__ void __launch_bounds__(kLaneMaxThreads) lane_softmax_bwd_kernel(const float* __restrict__ y, const float* __restrict__ g, float* __restrict__ dx,
+                                                                        uint64_t rows, uint32_t V) {
+    __shared__ float sh[kLaneMaxWarps];
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint64_t row0 = row * V;
+        float acc = 0.f;
+#pragma unroll 2
+        for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float a[8], b[8], t[8];
+            const int n = lane_load8<NRL_F32, VEC>(g, row0, v, V, a);
+            if (!LOG) lane_load8<NRL_F32, VEC>(y, row0, v, V, b);
+#pragma unroll
+            for (int i = 0; i < 8; i++) t[i] = (i < n) ? (LOG ? a[i] : a[i] * b[i]) : 0.f;
+            acc += ((t[0] + t[1]) + (t[2] + t[3])) + ((t[4] + t[5]) + (t[6] + t[7]));
+        }
+        const float s = block_sum(acc, sh);
+#pragma unroll 2
+        for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float a[8], b[8], d[8];
+            const int n = lane_load8<NRL_F32, VEC>(g, row0, v, V, a);
+            lane_load8<NRL_F32, VEC>(y, row0, v, V, b);
+#pragma unroll
+            for (int i = 0; i < 8; i++) d[i] = LOG ? a[i] - ex2_approx(b[i] * kLog2e) * s : b[i] * (a[i] - s);
+            lane_store8<VEC>(dx, row0, v, n, d);
+        }
+    }
+}
+
+// ---- argmax -------------------------------------------------------------------------------------
+template <int DT, bool VEC>
+__global__ void __launch_bounds__(kLaneMaxThreads) lane_argmax_kernel(const void* __restrict__ x, int32_t* __restrict__ out_index, float* __restrict__ out_value,
+                                                                   uint64_t rows, uint32_t V) {
+    __shared__ float shv[kLaneMaxWarps];
+    __shared__ uint32_t shi[kLaneMaxWarps];
+    const uint32_t nvec = (V + kVec - 1) / kVec;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        float best = NRL_NEG_INF;
+        uint32_t idx = 0xffffffffu;  // "nothing seen": any element of the row beats it, also a −inf one
+#pragma unroll 2
+        for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+            float z[8];
+            const int n = lane_load8<DT, VEC>(x, row * V, v, V, z);
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+                if (i < n && arg_better(z[i], v * kVec + i, best, idx)) { best = z[i]; idx = v * kVec + i; }
+        }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, s);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, s);
+            if (arg_better(ob, oi, best, idx)) { best = ob; idx = oi; }
+        }
+        __syncthreads();
+        if (lane == 0) { shv[warp] = best; shi[warp] = idx; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            best = shv[0]; idx = shi[0];
+            for (int w = 1; w < (int)(blockDim.x >> 5); w++)
+                if (arg_better(shv[w], shi[w], best, idx)) { best = shv[w]; idx = shi[w]; }
+            out_index[row] = (int32_t)idx;
+            if (out_value) out_value[row] = best;
+        }
+    }
+}
+
+// ---- the lane sum in the reference's operand order ---------------------------------------------
+// Eight partial sums p_k = x[k] + x[8 + k] + x[16 + k] + …, each built left to right, combined as
+// acc = 0; acc += p0 + p4; acc += p1 + p5; acc += p2 + p6; acc += p3 + p7; then the V mod 8 tail in
+// order. Eight lanes own a row (one partial each), so a warp streams four rows and every load
+// instruction reads four whole 32-byte sectors; the adds of one partial are dependent by
+// definition, the loads are issued 32 deep ahead of them.
+template <int DT>
+__device__ __forceinline__ float lane_elem(const void* x, uint64_t i) {
+    if (DT == NRL_BF16) return __uint_as_float((uint32_t)__ldg((const uint16_t*)x + i) << 16);
+    return __ldg((const float*)x + i);
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kLaneThreads) lane_sum_ordered_kernel(const void* __restrict__ x, float* __restrict__ out, uint64_t rows, uint32_t V) {
+    const int k = threadIdx.x & 7;
+    const uint64_t rows_per_block = blockDim.x / 8;
+    const uint32_t full = V / 8;
+    for (uint64_t base = (uint64_t)blockIdx.x * rows_per_block; base < rows; base += (uint64_t)gridDim.x * rows_per_block) {
+        const uint64_t row = base + (threadIdx.x >> 3);
+        const bool live = row < rows;  // every lane stays for the shuffles
+        const uint64_t row0 = (live ? row : 0) * V;
+        float p = 0.f;
+        uint32_t j = 0;
+        if (live) {
+            for (; j + 32 <= full; j += 32) {
+                float t[32];
+#pragma unroll
+                for (int u = 0; u < 32; u++) t[u] = lane_elem<DT>(x, row0 + (uint64_t)(j + u) * 8 + k);
+#pragma unroll
+                for (int u = 0; u < 32; u++) p = __fadd_rn(p, t[u]);
+            }
+            for (; j < full; j++) p = __fadd_rn(p, lane_elem<DT>(x, row0 + (uint64_t)j * 8 + k));
+        }
+        const float q = __fadd_rn(p, __shfl_down_sync(0xffffffffu, p, 4, 8));  // lanes 0..3 of the row: p_k + p_{k+4}
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, q, i, 8));
+        if (live && k == 0) {
+            for (uint32_t e = full * 8; e < V; e++) acc = __fadd_rn(acc, lane_elem<DT>(x, row0 + e));
+            out[row] = acc;
+        }
+    }
+}
+
+}  // namespace nrl

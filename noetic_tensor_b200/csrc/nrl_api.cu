@@ -12,6 +12,7 @@
 #include "ce_ops.cuh"
 #include "gumbel.cuh"
 #include "host_pack.cuh"
+#include "lane_ops.cuh"
 
 #define NRL_STR2(x) #x
 #define NRL_STR(x) NRL_STR2(x)
@@ -380,6 +381,13 @@ extern "C" int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devp
     return after_launch();
 }
 
+extern "C" int nrl_group_advantages(uint64_t groups, uint32_t n, uint32_t norm_std, double eps, uint32_t unbiased, nrl_devptr rewards, nrl_devptr out, nrl_stream stream) {
+    if (groups == 0 || n == 0 || !rewards || !out || ((rewards | out) & 3u)) return NRL_E_BAD_ARG;
+    if (norm_std && (!(eps >= 0.0) || (unbiased && n < 2))) return NRL_E_BAD_ARG;
+    group_advantages_kernel<<<(unsigned)((groups + 127) / 128), 128, 0, (cudaStream_t)stream>>>(groups, n, norm_std != 0, eps, unbiased != 0, (const float*)rewards, (float*)out);
+    return after_launch();
+}
+
 // ---- cross-entropy family -------------------------------------------------------------------------
 
 extern "C" int nrl_row_sum(uint32_t dtype, uint64_t rows, uint32_t V, nrl_devptr logits, nrl_devptr out, nrl_stream stream) {
@@ -446,6 +454,83 @@ extern "C" int nrl_sample_gumbel(const nrl_gumbel_args* a, nrl_stream stream) {
     if (a->dtype == NRL_F32) NRL_GUMBEL(NRL_F32);
     else NRL_GUMBEL(NRL_BF16);
 #undef NRL_GUMBEL
+    return after_launch();
+}
+
+// ---- generic lane reductions ---------------------------------------------------------------------
+
+template <int DT>
+static void launch_lane(const nrl_lane_args* a, bool vec, unsigned grid, unsigned threads, cudaStream_t st) {
+    const void* x = (const void*)a->x;
+    float* out = (float*)a->out;
+    switch (a->op) {
+        case NRL_LANE_SOFTMAX:
+            if (vec) lane_softmax_kernel<DT, true, false><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            else lane_softmax_kernel<DT, false, false><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            break;
+        case NRL_LANE_LOG_SOFTMAX:
+            if (vec) lane_softmax_kernel<DT, true, true><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            else lane_softmax_kernel<DT, false, true><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            break;
+        case NRL_LANE_LOGSUMEXP:
+            if (vec) lane_logsumexp_kernel<DT, true><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            else lane_logsumexp_kernel<DT, false><<<grid, threads, 0, st>>>(x, out, a->rows, a->V);
+            break;
+        case NRL_LANE_ARGMAX:
+            if (vec) lane_argmax_kernel<DT, true><<<grid, threads, 0, st>>>(x, (int32_t*)a->out_index, out, a->rows, a->V);
+            else lane_argmax_kernel<DT, false><<<grid, threads, 0, st>>>(x, (int32_t*)a->out_index, out, a->rows, a->V);
+            break;
+        case NRL_LANE_SUM: {
+            // eight lanes per row: few rows run small blocks so that every SM gets some
+            const unsigned bt = a->rows >= 148ull * 8 * 32 ? kLaneThreads : 64;
+            const uint64_t blocks = (a->rows + bt / 8 - 1) / (bt / 8);
+            lane_sum_ordered_kernel<DT><<<(unsigned)(blocks < 148ull * 32 ? blocks : 148ull * 32), bt, 0, st>>>(x, out, a->rows, a->V);
+            break;
+        }
+        case NRL_LANE_LOGSUMEXP_BWD:
+            if (vec) lane_logsumexp_bwd_kernel<DT, true><<<grid, threads, 0, st>>>(x, (const float*)a->lse, (const float*)a->g, out, a->rows, a->V);
+            else lane_logsumexp_bwd_kernel<DT, false><<<grid, threads, 0, st>>>(x, (const float*)a->lse, (const float*)a->g, out, a->rows, a->V);
+            break;
+        default: break;
+    }
+}
+
+extern "C" int nrl_lane_op(const nrl_lane_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_lane_args)) return NRL_E_BAD_ARG;
+    if (a->rows == 0 || a->V == 0 || !a->x || a->op > NRL_LANE_LOGSUMEXP_BWD) return NRL_E_BAD_ARG;
+    if (a->dtype != NRL_F32 && a->dtype != NRL_BF16) return NRL_E_UNSUPPORTED;
+    const bool bwd_y = a->op == NRL_LANE_SOFTMAX_BWD || a->op == NRL_LANE_LOG_SOFTMAX_BWD;
+    if (bwd_y && a->dtype != NRL_F32) return NRL_E_UNSUPPORTED;
+    if (a->op == NRL_LANE_ARGMAX ? !a->out_index : !a->out) return NRL_E_BAD_ARG;
+    if ((bwd_y || a->op == NRL_LANE_LOGSUMEXP_BWD) && !a->g) return NRL_E_BAD_ARG;
+    if (a->op == NRL_LANE_LOGSUMEXP_BWD && !a->lse) return NRL_E_BAD_ARG;
+    const uint64_t esize = a->dtype == NRL_F32 ? 4 : 2;
+    if ((a->x & (esize - 1)) || (a->out & 3u) || (a->out_index & 3u) || (a->g & 3u) || (a->lse & 3u)) return NRL_E_BAD_ARG;
+    const bool vec = a->V % kVec == 0 && aligned16(a->x) && aligned16(a->out) && (!bwd_y || aligned16(a->g));
+    // Ops that read a row twice want the second read to hit L2: when the rows that 8 blocks of 256
+    // threads per SM would hold in flight outgrow it, one block of 1024 threads per SM runs instead.
+    const bool twice = a->op == NRL_LANE_SOFTMAX || a->op == NRL_LANE_LOG_SOFTMAX || bwd_y;
+    const uint64_t row_bytes = (uint64_t)a->V * esize * (bwd_y ? 2 : 1);
+    const bool wide = twice && row_bytes * 1184ull > (96ull << 20);
+    const unsigned threads = wide ? kLaneMaxThreads : kLaneThreads;
+    const uint64_t cap = wide ? 148ull : 148ull * 8ull;
+    const unsigned grid = (unsigned)(a->rows < cap ? a->rows : cap);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (bwd_y) {
+        const float *y = (const float*)a->x, *g = (const float*)a->g;
+        float* dx = (float*)a->out;
+        if (a->op == NRL_LANE_SOFTMAX_BWD) {
+            if (vec) lane_softmax_bwd_kernel<true, false><<<grid, threads, 0, st>>>(y, g, dx, a->rows, a->V);
+            else lane_softmax_bwd_kernel<false, false><<<grid, threads, 0, st>>>(y, g, dx, a->rows, a->V);
+        } else {
+            if (vec) lane_softmax_bwd_kernel<true, true><<<grid, threads, 0, st>>>(y, g, dx, a->rows, a->V);
+            else lane_softmax_bwd_kernel<false, true><<<grid, threads, 0, st>>>(y, g, dx, a->rows, a->V);
+        }
+    } else if (a->dtype == NRL_F32) {
+        launch_lane<NRL_F32>(a, vec, grid, threads, st);
+    } else {
+        launch_lane<NRL_BF16>(a, vec, grid, threads, st);
+    }
     return after_launch();
 }
 

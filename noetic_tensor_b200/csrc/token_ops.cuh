@@ -228,4 +228,39 @@ __global__ void mask_rows_kernel(uint64_t n, const float* x, const float* mask, 
     if (i < n) out[i] = (mask && mask[i] == 0.f) ? 0.f : x[i];
 }
 
+// group_advantages (src/nn/rl.rs:436-461) on the device, in the host's own f64 operand order so
+// that the result is the reference's bit for bit: per group of n rewards min/max (all equal →
+// exact zeros), the left-to-right sum, mean, optionally the left-to-right sum of squared
+// deviations → standard deviation + eps, then (r − mean) / scale, rounded to f32 once. One thread
+// per group; products and sums are written with explicit roundings so nothing is fused.
+__global__ void group_advantages_kernel(uint64_t groups, uint32_t n, int norm_std, double eps, int unbiased, const float* rewards, float* out) {
+    const uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= groups) return;
+    const float* r = rewards + g * n;
+    float* o = out + g * n;
+    double lo = (double)__int_as_float(0x7f800000), hi = -lo, sum = 0.0;
+    for (uint32_t i = 0; i < n; i++) {
+        const double x = (double)r[i];
+        lo = fmin(lo, x);
+        hi = fmax(hi, x);
+        sum = __dadd_rn(sum, x);
+    }
+    if (lo == hi) {
+        for (uint32_t i = 0; i < n; i++) o[i] = 0.f;
+        return;
+    }
+    const double mean = __ddiv_rn(sum, (double)n);
+    double scale = 1.0;
+    if (norm_std) {
+        double ss = 0.0;
+        for (uint32_t i = 0; i < n; i++) {
+            const double d = __dsub_rn((double)r[i], mean);
+            ss = __dadd_rn(ss, __dmul_rn(d, d));
+        }
+        const double var = __ddiv_rn(ss, unbiased ? (double)(n - 1) : (double)n);
+        scale = __dadd_rn(__dsqrt_rn(var), eps);
+    }
+    for (uint32_t i = 0; i < n; i++) o[i] = (float)__ddiv_rn(__dsub_rn((double)r[i], mean), scale);
+}
+
 }  // namespace nrl

@@ -233,6 +233,18 @@ def mask_rows(x, mask):
     return out
 
 
+def group_advantages(rewards, *, norm_std=False, eps=0.0, unbiased=True):
+    """group_advantages_tensor (src/nn/rl.rs:465-469) over the last axis of f32 rewards [..., N], on the device."""
+    if rewards.dtype != torch.float32 or not rewards.is_contiguous() or rewards.device.type != "cuda":
+        raise ValueError("rewards: a contiguous float32 CUDA tensor [..., N]")
+    n = rewards.shape[-1]
+    out = torch.empty_like(rewards)
+    with torch.cuda.device(rewards.device):
+        capi.check(capi.lib().nrl_group_advantages(rewards.numel() // n, n, int(norm_std), float(eps), int(unbiased), _p(rewards), _p(out), _stream(rewards.device)),
+                   "nrl_group_advantages")
+    return out
+
+
 def check_status(status):
     """Raises the reference's error (src/nn/rl.rs:517-519) if any row was refused."""
     bad, bits = C.c_uint64(0), C.c_uint32(0)
@@ -303,3 +315,72 @@ def sample_gumbel(logits, seed, *, word_offset=0, temperature=1.0, allow=None, a
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_sample_gumbel(C.byref(a), _stream(dev)), "nrl_sample_gumbel")
     return tokens, status
+
+
+def _lane(op, x, *, g=None, lse=None, full_out=True, index=False):
+    dev = x.device
+    if dev.type != "cuda":
+        raise ValueError("lane ops run on CUDA tensors only")
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be a contiguous [rows, V] tensor")
+    rows, V = x.shape
+    a = capi.LaneArgs()
+    a.struct_size = C.sizeof(a)
+    a.op, a.dtype, a.V, a.rows = op, _dt(x), V, rows
+    a.x = _p(x)
+    if g is not None:
+        _need(g, torch.float32, (rows, V) if op != capi.LANE_LOGSUMEXP_BWD else (rows,), "g", dev)
+        a.g = _p(g)
+    if lse is not None:
+        _need(lse, torch.float32, (rows,), "lse", dev)
+        a.lse = _p(lse)
+    out = torch.empty((rows, V) if full_out else (rows,), dtype=torch.float32, device=dev)
+    a.out = _p(out)
+    idx = None
+    if index:
+        idx = torch.empty(rows, dtype=torch.int32, device=dev)
+        a.out_index = _p(idx)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_lane_op(C.byref(a), _stream(dev)), "nrl_lane_op")
+    return (idx, out) if index else out
+
+
+def softmax(x):
+    """softmax along the last axis of [rows, V] (src/tensor/activation.rs:15-26), f32 out."""
+    return _lane(capi.LANE_SOFTMAX, x)
+
+
+def log_softmax(x):
+    """log_softmax along the last axis (src/tensor/activation.rs:30-42), f32 out."""
+    return _lane(capi.LANE_LOG_SOFTMAX, x)
+
+
+def logsumexp(x):
+    """log Σ exp along the last axis with the ±inf rule (src/tensor/activation.rs:71-77), [rows]."""
+    return _lane(capi.LANE_LOGSUMEXP, x, full_out=False)
+
+
+def argmax(x):
+    """(index i32 [rows], value f32 [rows]): the first maximum, the first NaN of a row that holds one
+    (src/tensor/kernels.rs:184-209)."""
+    return _lane(capi.LANE_ARGMAX, x, full_out=False, index=True)
+
+
+def sum_last(x):
+    """Σ along the last axis in the reference's operand order (src/tensor/kernels.rs:122-148)."""
+    return _lane(capi.LANE_SUM, x, full_out=False)
+
+
+def softmax_backward(y, g):
+    """y · (g − Σ g·y) from the saved output."""
+    return _lane(capi.LANE_SOFTMAX_BWD, y, g=g)
+
+
+def log_softmax_backward(y, g):
+    """g − exp(y) · Σ g from the saved output."""
+    return _lane(capi.LANE_LOG_SOFTMAX_BWD, y, g=g)
+
+
+def logsumexp_backward(x, lse, g):
+    """g[row] · exp(x − lse[row])."""
+    return _lane(capi.LANE_LOGSUMEXP_BWD, x, g=g, lse=lse)

@@ -189,6 +189,32 @@ def rl_eval(op, shape, *, dtype=F32, logits=None, ref_logits=None, tokens=None, 
     return (value, grad) if upstream is not None else value
 
 
+LANE_SOFTMAX, LANE_LOG_SOFTMAX, LANE_LOGSUMEXP, LANE_ARGMAX, LANE_SUM = range(5)
+
+
+def lane_op(op, x, *, dtype=F32, upstream=None):
+    """softmax / log_softmax / logsumexp / argmax / sum_dim along the last axis of [rows, V] on the
+    restated engine (src/tensor/activation.rs:15-42, 71-77; src/tensor/kernels.rs:122-209).
+    Returns the value (float64; for argmax a pair (index int64, value)), and with `upstream` also
+    the gradient of sum(value * upstream) with respect to x."""
+    a, code = _storage(x)
+    rows, V = a.shape
+    full = op in (LANE_SOFTMAX, LANE_LOG_SOFTMAX)
+    value = np.zeros((rows, V) if full else rows, dtype=np.float64)
+    index = np.zeros(rows, dtype=np.int64)
+    grad = up = None
+    if upstream is not None:
+        up = _f64(upstream)
+        assert up.size == value.size
+        grad = np.zeros((rows, V), dtype=np.float64)
+    rc = lib().orc_lane_op(op, dtype, _ptr(a), code, C.c_int64(rows), C.c_int64(V), _ptr(up), _ptr(value), _ptr(index), _ptr(grad))
+    if rc != 0:
+        raise RuntimeError(lib().orc_last_error().decode())
+    if op == LANE_ARGMAX:
+        return index, value
+    return (value, grad) if upstream is not None else value
+
+
 def out_shape(shape, reduction):
     S, B, T, _ = shape
     return {NONE: (S, B, T), SUM: (S,), TOKEN_MEAN: (S,), PER_SEQUENCE: (S, B), SEQUENCE_MEAN: (S,)}[reduction]

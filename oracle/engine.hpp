@@ -727,6 +727,33 @@ struct Engine {
         });
     }
 
+    // softmax (src/tensor/activation.rs:15-26): exp(x − max) / Σ exp(x − max); backward
+    // y · (g − Σ g·y) from the saved output
+    static Tensor softmax(const Tensor& x, size_t dim) {
+        Tensor xu = x.untracked();
+        Tensor mx = max_dim(xu, dim);
+        Tensor e = exp(sub(xu, mx));
+        Tensor y = div(e, sum_dim(e, dim));
+        return attach(y.untracked(), {&x}, [dim](const Tensor& ys) {
+            return [ys, dim](const Tensor& g, const std::vector<bool>&) {
+                Tensor s = sum_dim(mul(g, ys), dim);
+                return Grads{mul(ys, sub(g, s))};
+            };
+        });
+    }
+
+    // logsumexp (src/tensor/activation.rs:71-77): m + log Σ exp(x − m) with the shift 0 where the
+    // lane's maximum is ±inf; backward g · exp(x − out)
+    static Tensor logsumexp(const Tensor& x, size_t dim) {
+        Tensor xu = x.untracked();
+        Tensor m = max_dim(xu, dim);
+        m = mask_fill(m, equal_elem(abs(m), INFINITY), 0.0).untracked();
+        Tensor out = add(log(sum_dim(exp(sub(xu, m)), dim)), m);
+        return attach(out.untracked(), {&x}, [xu](const Tensor& ys) {
+            return [ys, xu](const Tensor& g, const std::vector<bool>&) { return Grads{mul(g, exp(sub(xu, ys)))}; };
+        });
+    }
+
     // ------------------------------------------------------------------ backward
 
     struct Gradients {

@@ -81,6 +81,13 @@ void orc_row_uniforms(uint64_t root, const char* label, int64_t rows, float* out
 void orc_bf16_from_f32(const float* x, int64_t n, uint16_t* out);
 void orc_bf16_to_f32(const uint16_t* x, int64_t n, float* out);
 
+/* Lane operations of the tensor engine on a [rows, V] input (src/tensor/activation.rs:15-42, 71-77;
+ * src/tensor/kernels.rs:122-209). op: 0 softmax, 1 log_softmax, 2 logsumexp (value [rows]),
+ * 3 argmax (index in out_index, value in out_value[rows]), 4 sum_dim (value [rows]). With
+ * `upstream` (shape of the value; ops 0-2) out_grad [rows, V] is d sum(value·upstream) / dx. */
+int orc_lane_op(int op, int engine_dtype, const void* x, int x_dtype, int64_t rows, int64_t V, const double* upstream, double* out_value,
+                int64_t* out_index, double* out_grad);
+
 int orc_sample_gumbel(const void* logits, int dtype, int64_t rows, int64_t V, double temperature, const float* add_mask, int64_t add_stride,
                       const uint8_t* allow, int64_t allow_stride, uint64_t root, const char* label, int64_t* tokens, int64_t* bad_row);
 

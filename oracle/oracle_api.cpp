@@ -143,6 +143,49 @@ extern "C" int orc_rl_eval(const orc_rl_case* c) {
     }
 }
 
+template <class T>
+static void lane_op(int op, const void* x, int x_dtype, size_t rows, size_t V, const double* upstream, double* out_value, int64_t* out_index, double* out_grad) {
+    typedef Engine<T> E;
+    typedef typename E::Tensor Tensor;
+    Tensor leaf(load<T>(x, x_dtype, rows * V), Shape{rows, V});
+    if (op == 3) {
+        auto am = E::argmax(leaf, 1);
+        for (size_t r = 0; r < rows; r++) {
+            out_index[r] = am.v[r];
+            if (out_value) out_value[r] = (double)leaf.v()[r * V + (size_t)am.v[r]];
+        }
+        return;
+    }
+    if (upstream) leaf = leaf.require_grad();
+    Tensor out;
+    switch (op) {
+        case 0: out = E::softmax(leaf, 1); break;
+        case 1: out = E::log_softmax(leaf, 1); break;
+        case 2: out = E::logsumexp(leaf, 1); break;
+        case 4: out = E::sum_dim(leaf, 1); break;
+        default: fail("orc_lane_op: unknown op");
+    }
+    for (size_t i = 0; i < out.n(); i++) out_value[i] = (double)out.v()[i];
+    if (upstream) {
+        Tensor up = Tensor::from_f64s(upstream, out.sh);
+        auto g = E::backward(E::sum(E::mul(out, up)));
+        const Tensor* gl = g.get(leaf);
+        for (size_t i = 0; i < rows * V; i++) out_grad[i] = gl ? (double)gl->v()[i] : 0.0;
+    }
+}
+
+extern "C" int orc_lane_op(int op, int engine_dtype, const void* x, int x_dtype, int64_t rows, int64_t V, const double* upstream, double* out_value,
+                           int64_t* out_index, double* out_grad) {
+    try {
+        if (engine_dtype == ORC_F64) lane_op<double>(op, x, x_dtype, (size_t)rows, (size_t)V, upstream, out_value, out_index, out_grad);
+        else lane_op<float>(op, x, x_dtype, (size_t)rows, (size_t)V, upstream, out_value, out_index, out_grad);
+        return 0;
+    } catch (const std::exception& e) {
+        g_err = e.what();
+        return -1;
+    }
+}
+
 extern "C" int orc_group_advantages(const double* rewards, int64_t len, int64_t n, int norm_std, double eps, int unbiased, double* out) {
     try {
         auto v = group_advantages(rewards, (size_t)len, (size_t)n, norm_std, eps, unbiased != 0);
