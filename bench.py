@@ -475,11 +475,35 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
         e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
+        packed_rate = world * e2e_rows / float(te.item())
+        # the same rows read in place: pinned host memory is mapped into the device's address space
+        hf.run_mapped(hx, hu, ref=hr, mask=hm)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            mout = hf.run_mapped(hx, hu, ref=hr, mask=hm)
+        tm = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        mapped_rate = world * e2e_rows / float(tm.item())
+        mapped_ok = bool((mout["tokens"][:64] == out.tokens[:64].cpu()).all())
         h2d, d2h = hf.bytes_per_row()
-        e2e = {"value": world * e2e_rows / float(te.item()), "unit": "rows/s", "h2d_bytes_per_step": int(hf.h2d_bytes), "d2h_bytes_per_step": e2e_rows * d2h,
-               "host_bytes_per_step": e2e_rows * h2d, "packed_chunks": hf.packed_chunks, "whole_chunks": hf.whole_chunks, "host_threads": hf.threads,
-               "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok,
-               "note": "host-resident bf16 logits + reference + mask (host_bytes_per_step, pinned) through the host path in 512-row chunks, double-buffered: host threads keep the vectors the mask allows (nrl_host_pack), h2d_bytes_per_step cross PCIe, a kernel puts them in place (nrl_unpack_rows), then the same forward; the packing runs inside the timed region"}
+        mapped_bytes = e2e_rows * (V + 4) + hf.live_vectors * 8 * 2 * 2  # the mask whole and the uniforms + the live vectors of bf16 logits and reference
+        best_mapped = mapped_rate > packed_rate
+        e2e = {"value": max(mapped_rate, packed_rate), "unit": "rows/s", "mode": "mapped" if best_mapped else "packed",
+               "h2d_bytes_per_step": int(mapped_bytes if best_mapped else hf.h2d_bytes), "d2h_bytes_per_step": e2e_rows * d2h,
+               "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok and mapped_ok,
+               "mapped": {"value": mapped_rate, "h2d_bytes_per_step_estimate": int(mapped_bytes),
+                          "note": "nrl_row_fwd is given the pinned host logits and reference themselves (mapped into the device's address space) and fetches only the vectors the mask allows "
+                                  "over the host link; the byte mask, read whole, goes up by copies in 2048-row chunks one chunk ahead of the kernel; uniforms go up and per-row results come back by copies, all inside the timed region; "
+                                  "the byte count is an estimate (mask bytes + live vectors), the link has no counter here"},
+               "packed": {"value": packed_rate, "h2d_bytes_per_step": int(hf.h2d_bytes), "packed_chunks": hf.packed_chunks, "whole_chunks": hf.whole_chunks, "host_threads": hf.threads,
+                          "note": "512-row chunks, double-buffered: host threads keep the vectors the mask allows (nrl_host_pack), those cross PCIe by copies, a kernel puts them in place "
+                                  "(nrl_unpack_rows), then the same forward; the packing runs inside the timed region"},
+               "note": "host-resident bf16 logits + reference + U8 mask in pinned memory (host_bytes_per_step) through the C ABI, results back in pinned host memory; "
+                       "value is the faster of the two host paths, named in `mode`"}
 
     extras = None
     if rank == 0 and not args.no_extras:

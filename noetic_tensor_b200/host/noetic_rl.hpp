@@ -711,6 +711,59 @@ inline std::vector<double> group_advantages(const std::vector<double>& rewards, 
     return out;
 }
 
+// group_advantages_tensor (src/nn/rl.rs:465-469) over the last axis of device rewards [..., N],
+// without the reference's host round trip: the same f64 operand order on the device, so the values
+// are group_advantages' rounded to f32 once.
+inline Tensor group_advantages_tensor(const Tensor& rewards, GroupNorm norm) {
+    if (rewards.dtype() != DType::F32 || rewards.shape().empty()) throw std::runtime_error("group_advantages_tensor: F32 rewards of rank >= 1");
+    const size_t n = rewards.shape().back();
+    if (norm.std_norm) {
+        if (!(norm.eps >= 0.0)) throw std::runtime_error("group_advantages: ε < 0");
+        if (norm.unbiased && n < 2) throw std::runtime_error("group_advantages: the sample standard deviation needs groups of at least 2");
+    }
+    Tensor out = Tensor::empty(rewards.shape(), DType::F32, rewards.device());
+    nrl(nrl_group_advantages(numel(rewards.shape()) / n, (uint32_t)n, norm.std_norm, norm.eps, norm.unbiased, rewards.dev(), out.dev(), detail::stream()), "group_advantages_tensor");
+    return out;
+}
+
 }  // namespace rl
 }  // namespace nn
+
+// ---- lane operations of the tensor engine along the last axis (src/tensor/activation.rs:15-42,
+// 71-77; Tensor::argmax / sum_dim on the last axis), forward values; untracked ------------------
+namespace lane {
+namespace detail {
+inline Tensor run(uint32_t op, const Tensor& x, bool full, Tensor* index = nullptr) {
+    if (x.shape().empty() || (x.dtype() != DType::F32 && x.dtype() != DType::BF16)) throw std::runtime_error("lane op: F32 or BF16 tensor of rank >= 1");
+    const size_t V = x.shape().back();
+    Shape os = x.shape();
+    if (!full) os.back() = 1;
+    Tensor out = Tensor::empty(os, DType::F32, x.device());
+    nrl_lane_args a{};
+    a.struct_size = sizeof(a);
+    a.op = op;
+    a.dtype = x.dtype() == DType::F32 ? NRL_F32 : NRL_BF16;
+    a.V = (uint32_t)V;
+    a.rows = numel(x.shape()) / V;
+    a.x = x.dev();
+    a.out = out.dev();
+    if (index) {
+        *index = Tensor::empty(os, DType::I32, x.device());
+        a.out_index = index->dev();
+    }
+    nrl(nrl_lane_op(&a, 0), "lane op");
+    return out;
+}
+}  // namespace detail
+inline Tensor softmax(const Tensor& x) { return detail::run(NRL_LANE_SOFTMAX, x, true); }
+inline Tensor log_softmax(const Tensor& x) { return detail::run(NRL_LANE_LOG_SOFTMAX, x, true); }
+inline Tensor logsumexp(const Tensor& x) { return detail::run(NRL_LANE_LOGSUMEXP, x, false); }
+inline Tensor sum_last(const Tensor& x) { return detail::run(NRL_LANE_SUM, x, false); }
+// (index I32 [..., 1], value F32 [..., 1]): the first maximum, the first NaN of a lane that holds one
+inline std::pair<Tensor, Tensor> argmax(const Tensor& x) {
+    Tensor idx;
+    Tensor val = detail::run(NRL_LANE_ARGMAX, x, false, &idx);
+    return {idx, val};
+}
+}  // namespace lane
 }  // namespace noetic

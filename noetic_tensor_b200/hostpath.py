@@ -9,6 +9,10 @@ With a byte mask the link carries only what the forward reads (`packed=True`, th
 threads keep one liveness bit per 8-element vector and the logits, reference logits and mask
 bytes of the live vectors (nrl_host_pack), and a kernel puts them back in place on the device
 (nrl_unpack_rows). A chunk whose live vectors outgrow the staging buffers is uploaded whole.
+
+`run_mapped` needs no staging at all: pinned host memory is mapped into the device's address
+space, so the masked forward streams the mask from it in place and fetches only the vectors the
+mask allows, each once, over the host link; no host thread touches the rows.
 """
 import ctypes as C
 import os
@@ -90,6 +94,50 @@ class HostForward:
         a.ref_logits = s["r"].data_ptr() if self.has_ref else 0
         capi.check(capi.lib().nrl_unpack_rows(C.byref(a), C.c_void_p(self.copy_stream.cuda_stream)), "nrl_unpack_rows")
 
+    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True):
+        """The same results as `run`, the kernel reading the pinned host logits (and reference) in
+        place. With `mask_by_copy` the byte mask, which is read whole, goes up by copies in
+        `chunk_rows`-row chunks one chunk ahead of the kernel (the copy engine moves it faster than
+        loads over the link do); otherwise one launch reads everything in place."""
+        rows = logits.shape[0]
+        pin = lambda dt: torch.empty(rows, dtype=dt).pin_memory()
+        if out is None:
+            out = dict(tokens=pin(torch.int32), logp=pin(torch.float32), kl=pin(torch.float32), entropy=pin(torch.float32), status=pin(torch.uint8))
+        compute = torch.cuda.current_stream(self.dev)
+        u = uniforms.to(self.dev, non_blocking=True)
+        ref = ref if self.has_ref else None
+        mask = mask if self.has_mask else None
+        by_copy = mask_by_copy and mask is not None
+        if not by_copy:
+            chunk_rows = rows
+        elif getattr(self, "_mapped_masks", None) is None or self._mapped_masks[0].shape[0] < min(chunk_rows, rows):
+            self._mapped_masks = [torch.empty(min(chunk_rows, rows), self.V, dtype=torch.uint8, device=self.dev) for _ in range(2)]
+            self._mapped_events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(2)]
+        results = []
+        for i, r0 in enumerate(range(0, rows, chunk_rows)):
+            r1 = min(rows, r0 + chunk_rows)
+            m = mask[r0:r1] if mask is not None else None
+            if by_copy:
+                ready, free = self._mapped_events[i % 2]
+                with torch.cuda.stream(self.copy_stream):
+                    if i >= 2:
+                        self.copy_stream.wait_event(free)  # the kernel that read this buffer has finished
+                    m = self._mapped_masks[i % 2][: r1 - r0]
+                    m.copy_(mask[r0:r1], non_blocking=True)
+                    ready.record(self.copy_stream)
+                compute.wait_event(ready)
+            f = ops.row_forward(logits[r0:r1], ref_logits=None if ref is None else ref[r0:r1], allow=m, uniforms=u[r0:r1], device=self.dev)
+            if by_copy:
+                free.record(compute)
+            for name in ("tokens", "logp", "kl", "entropy", "status"):
+                t = getattr(f, name)
+                if t is not None:
+                    out[name][r0:r1].copy_(t, non_blocking=True)
+            results.append(f)
+        compute.synchronize()
+        self.copy_stream.synchronize()
+        return out
+
     def run(self, logits, uniforms, ref=None, mask=None, out=None):
         """logits/ref [rows, V], mask [rows, V] u8, uniforms [rows]: pinned host tensors. Returns
         pinned host tensors tokens (i32), logp, kl, entropy (f32) and status (u8), complete on return."""
@@ -100,6 +148,7 @@ class HostForward:
         compute = torch.cuda.current_stream(self.dev)
         done = []
         self.h2d_bytes = 0  # bytes this call sends to the device
+        self.live_vectors = 0  # 8-element vectors the mask allows, over the packed chunks of this call
         esize = logits.element_size()
         for i, r0 in enumerate(range(0, rows, self.chunk)):
             r1 = min(rows, r0 + self.chunk)
@@ -120,6 +169,7 @@ class HostForward:
                     s["staged"].record(self.copy_stream)
                     self._unpack(s, n)
                     self.packed_chunks += 1
+                    self.live_vectors += live
                     self.h2d_bytes += n * 4 + n * self.words * 8 + (n + 1) * 4 + live * (8 * esize * (2 if self.has_ref else 1) + 8)
                 else:
                     s["x"][:n].copy_(logits[r0:r1], non_blocking=True)

@@ -53,14 +53,24 @@ class RowForward:
 
 
 def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, uniforms=None, tokens=None, greedy=False,
-                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None):
+                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None, device=None):
     """Fused sample / log-prob / KL / entropy over logits [rows, V] (f32 or bf16, CUDA).
 
     Exactly one of: `uniforms` (sample by inverse CDF), `greedy=True`, `tokens` (given, int32), or
-    none (row statistics, entropy and KL only)."""
-    dev = logits.device
+    none (row statistics, entropy and KL only).
+
+    With `device` given, `logits`, `ref_logits` and the masks may be PINNED host tensors: pinned
+    memory is mapped into the device's address space, so the kernel reads them in place over the
+    host link (with a byte mask, only the mask and the vectors it allows cross it). Everything else
+    (uniforms, tokens, the outputs) lives on `device`."""
+    in_dev = logits.device
+    dev = torch.device(device) if device is not None else in_dev
     if dev.type != "cuda":
         raise ValueError("row_forward needs CUDA tensors: this library has no CPU path")
+    if in_dev.type != "cuda":
+        for t in (logits, ref_logits, allow, add_mask):
+            if t is not None and t.device != dev and not (t.device.type == "cpu" and t.is_pinned()):
+                raise ValueError("row_forward: host inputs must all be pinned (page-locked) tensors")
     if logits.dim() != 2 or not logits.is_contiguous():
         raise ValueError("logits: contiguous [rows, V]")
     rows, V = logits.shape
@@ -69,9 +79,11 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
     a.dtype, a.V, a.rows, a.temperature = _dt(logits), V, rows, float(temperature)
     a.logits = _p(logits)
     if ref_logits is not None:
-        _need(ref_logits, logits.dtype, logits.shape, "ref_logits", dev)
+        _need(ref_logits, logits.dtype, logits.shape, "ref_logits", in_dev)
         a.ref_logits = _p(ref_logits)
-    allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
+    # with host logits a mask may already be on the device (it is read whole; copying it ahead is cheaper than reading it in place)
+    allow, a.allow_row_stride, _, _ = _masks(V, rows, allow, None, dev if (allow is not None and allow.device == dev) else in_dev)
+    _, _, add_mask, a.add_row_stride = _masks(V, rows, None, add_mask, dev if (add_mask is not None and add_mask.device == dev) else in_dev)
     a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
     out = RowForward()
     f32 = dict(dtype=torch.float32, device=dev)

@@ -508,6 +508,44 @@ static void test_group_advantages() {
     CHECK((z == std::vector<double>{0, 0, 0}), "equal rewards");
     CHECK(throws([] { rl::group_advantages({1, 2, 3}, 2, rl::GroupNorm::MeanOnly()); }, "groups of n"), "ragged");
     CHECK(throws([] { rl::group_advantages({1, 2}, 1, rl::GroupNorm::Std(0.0, true)); }, "at least 2"), "n = 1 unbiased");
+    // group_advantages_tensor on the device: the host function's values rounded to f32 once
+    const std::vector<float> r32 = {1, 0, 0, 1, 0.25f, 0.5f, 4, 8, 3, 3, 3, 3};
+    const std::vector<double> r64(r32.begin(), r32.end());
+    for (auto norm : {rl::GroupNorm::MeanOnly(), rl::GroupNorm::Std(0.0, true), rl::GroupNorm::Std(1e-6, false)}) {
+        auto want = rl::group_advantages(r64, 4, norm);
+        auto got = rl::group_advantages_tensor(Tensor::from_f32(r32, {3, 4}, dev), norm).to_vec();
+        bool same = true;
+        for (size_t i = 0; i < want.size(); i++) same = same && got[i] == (float)want[i];
+        CHECK(same, "group_advantages_tensor equals the host function");
+    }
+    CHECK(throws([] { rl::group_advantages_tensor(Tensor::from_f32({1, 2}, {2, 1}, dev), rl::GroupNorm::Std(0.0, true)); }, "at least 2"), "tensor n = 1 unbiased");
+}
+
+// ---- lane operations (src/tensor/tests/standard.rs:8-24, 101-109; checks.rs:103-114) -------------
+static void test_lane_ops() {
+    const float inf = INFINITY, nan = NAN;
+    auto lse = noetic::lane::logsumexp(Tensor::from_f32({1000, 1000, -inf, 0, -inf, -inf, -inf, -inf, 1, inf, 0, 2, 0.5f, nan, 1, 3}, {4, 4}, dev)).to_vec();
+    CHECK(std::fabs(lse[0] - (1000.0f + 0.6931472f)) < 1e-3f && lse[1] == -inf && lse[2] == inf && std::isnan(lse[3]), "logsumexp at infinities");
+    auto am = noetic::lane::argmax(Tensor::from_f32({1, nan, 5, 2, nan, 3, 9, 0, 4, nan, nan, 1, 1, 7, 7, 2}, {4, 4}, dev));
+    std::vector<int32_t> idx(4);
+    noetic::cu(cudaMemcpy(idx.data(), am.first.ptr(), 16, cudaMemcpyDeviceToHost), "download");
+    CHECK((idx == std::vector<int32_t>{1, 0, 1, 1}), "argmax: the first NaN is the maximum, ties take the first");
+    auto sm = noetic::lane::softmax(Tensor::from_f32({0.5f, nan, -1, 2, -inf, -inf, -inf, -inf, 1, -inf, 3, -inf}, {3, 4}, dev)).to_vec();
+    bool nans = true;
+    for (int i = 0; i < 8; i++) nans = nans && std::isnan(sm[i]);
+    CHECK(nans && sm[9] == 0.f && std::fabs(sm[8] + sm[10] - 1.f) < 1e-6f, "softmax of NaN / all -inf / partly masked rows");
+    std::vector<float> x(3 * 37);
+    for (size_t i = 0; i < x.size(); i++) x[i] = std::sin((float)i) * 4.f;
+    auto ls = noetic::lane::log_softmax(Tensor::from_f32(x, {3, 37}, dev)).to_vec();
+    auto su = noetic::lane::sum_last(Tensor::from_f32(x, {3, 37}, dev)).to_vec();
+    for (int r = 0; r < 3; r++) {
+        double m = -1e30, z = 0, s = 0;
+        for (int j = 0; j < 37; j++) m = std::max(m, (double)x[r * 37 + j]);
+        for (int j = 0; j < 37; j++) { z += std::exp(x[r * 37 + j] - m); s += x[r * 37 + j]; }
+        bool ok = std::fabs(su[r] - s) < 1e-4;
+        for (int j = 0; j < 37; j++) ok = ok && std::fabs(ls[r * 37 + j] - (x[r * 37 + j] - m - std::log(z))) < 1e-5;
+        CHECK(ok, "log_softmax and sum_last against f64");
+    }
 }
 
 // ---- a PPO step end to end: clipped loss + β·reference_kl − c·entropy, one backward -------------
@@ -659,7 +697,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"sample_categorical (reference noise)", test_sample_categorical_reference},
-        {"group_advantages", test_group_advantages}, {"ppo step", test_ppo_step},
+        {"group_advantages", test_group_advantages}, {"lane operations", test_lane_ops}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {

@@ -124,3 +124,37 @@ def test_chunk_that_outgrows_staging_is_uploaded_whole():
     assert hf.whole_chunks == 3 and hf.packed_chunks == 0
     assert torch.equal(got["tokens"], torch.cat([f.tokens for f in parts]).cpu())
     assert torch.equal(_bits(got["logp"]), _bits(torch.cat([f.logp for f in parts]).cpu()))
+
+
+@pytest.mark.parametrize("dtype,ref,rows", [(torch.bfloat16, True, 1300), (torch.bfloat16, False, 300), (torch.float32, True, 40)])
+def test_mapped_host_rows_equal_the_resident_forward(dtype, ref, rows):
+    """The forward reading pinned host memory in place (no staging copy): the same launch shape as
+    the resident call, so every result is bit-equal."""
+    from noetic_tensor_b200 import ops, synth
+    from noetic_tensor_b200.hostpath import HostForward
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(13)
+    V = 128256 if dtype == torch.bfloat16 else 32000
+    x = synth.normal_logits(rows, V, 3.0, dtype, gen, dev)
+    r = synth.perturbed(x, 0.05, gen) if ref else None
+    m = synth.grammar_masks(rows, V, gen, dev)
+    u = synth.uniforms(rows, gen, dev)
+    want = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+    pin = lambda t: None if t is None else t.cpu().pin_memory()
+    hf = HostForward(V, dtype, chunk_rows=64, ref=ref, mask=True, device=dev, packed=False)
+    hx, hu, hr, hm = pin(x), pin(u), pin(r), pin(m)
+    for by_copy in (False, True):  # everything in place; the mask by copies (one chunk: the same launch shape)
+        got = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=rows, mask_by_copy=by_copy)
+        for name in ("tokens", "logp", "entropy") + (("kl",) if ref else ()):
+            assert torch.equal(_bits(got[name]), _bits(getattr(want, name).cpu())), (name, by_copy)
+        assert (got["status"] == 0).all()
+    # several chunks, the mask one chunk ahead: the launches of the resident forward over the same chunks
+    chunk = max(16, rows // 3)
+    got = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=chunk)
+    parts = [ops.row_forward(x[a:a + chunk], ref_logits=None if r is None else r[a:a + chunk], allow=m[a:a + chunk], uniforms=u[a:a + chunk]) for a in range(0, rows, chunk)]
+    for name in ("tokens", "logp", "entropy") + (("kl",) if ref else ()):
+        assert torch.equal(_bits(got[name]), _bits(torch.cat([getattr(f, name) for f in parts]).cpu())), name
+    with pytest.raises(ValueError, match="pinned"):
+        ops.row_forward(x.cpu(), allow=pin(m), uniforms=u, device=dev)
