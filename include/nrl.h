@@ -392,6 +392,13 @@ typedef struct nrl_lane_args {
 
 int nrl_lane_op(const nrl_lane_args* args, nrl_stream stream);
 
+/* Bit-packed vocabulary masks (no counterpart in the reference, whose masks are one byte or one
+ * f32 per token, src/tensor/gpu/mod.rs:39-40): `bits` holds u32 words, bit v of a row being bit
+ * (v mod 32) of its word v / 32, rows `bits_row_stride_words` words apart (0 = one row broadcast
+ * to all). nrl_expand_bitmask writes the U8 allow-mask [rows, V] (0 / 1) that nrl_row_fwd and
+ * nrl_row_bwd take: a host caller uploads V / 8 bytes per row instead of V. */
+int nrl_expand_bitmask(uint64_t rows, uint32_t V, nrl_devptr bits, uint64_t bits_row_stride_words, nrl_devptr allow_mask, nrl_stream stream);
+
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */
 int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
 

@@ -136,4 +136,29 @@ __global__ void __launch_bounds__(256) unpack_rows_kernel(uint32_t V, const uint
     }
 }
 
+// Bit-packed vocabulary masks: bit v of a row is bit (v mod 32) of its 32-bit word v / 32 (the
+// layout grammar engines emit). One thread expands one byte of bits into eight mask bytes.
+__global__ void __launch_bounds__(256) expand_bitmask_kernel(uint64_t rows, uint32_t V, uint32_t words_per_row, uint64_t bits_row_stride_words, const uint32_t* __restrict__ bits,
+                                                             uint8_t* __restrict__ out) {
+    const uint32_t bytes_per_row = (V + 7) / 8;
+    const uint64_t total = rows * bytes_per_row;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint64_t row = i / bytes_per_row;
+        const uint32_t b = (uint32_t)(i - row * bytes_per_row);  // byte of bits within the row
+        const uint32_t w = __ldg(bits + row * bits_row_stride_words + (b >> 2));
+        const uint32_t byte = (w >> (8 * (b & 3))) & 0xffu;
+        // spread bit k of `byte` to byte k: 0 or 1
+        const uint32_t lo = ((byte & 0xfu) * 0x00204081u) & 0x01010101u;
+        const uint32_t hi = ((byte >> 4) * 0x00204081u) & 0x01010101u;
+        uint8_t* dst = out + row * V + (uint64_t)b * 8;
+        const uint32_t left = V - b * 8;
+        if (left >= 8 && (reinterpret_cast<uintptr_t>(dst) & 7u) == 0) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+        } else {
+            for (uint32_t k = 0; k < 8 && k < left; k++) dst[k] = (uint8_t)((byte >> k) & 1u);
+        }
+    }
+    (void)words_per_row;
+}
+
 }  // namespace nrl

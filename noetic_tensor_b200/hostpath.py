@@ -94,11 +94,14 @@ class HostForward:
         a.ref_logits = s["r"].data_ptr() if self.has_ref else 0
         capi.check(capi.lib().nrl_unpack_rows(C.byref(a), C.c_void_p(self.copy_stream.cuda_stream)), "nrl_unpack_rows")
 
-    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True):
+    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True, mask_bits=None):
         """The same results as `run`, the kernel reading the pinned host logits (and reference) in
         place. With `mask_by_copy` the byte mask, which is read whole, goes up by copies in
         `chunk_rows`-row chunks one chunk ahead of the kernel (the copy engine moves it faster than
-        loads over the link do); otherwise one launch reads everything in place."""
+        loads over the link do); otherwise one launch reads everything in place. A caller that holds
+        bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
+        v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and
+        nrl_expand_bitmask writes the byte mask on the device."""
         rows = logits.shape[0]
         pin = lambda dt: torch.empty(rows, dtype=dt).pin_memory()
         if out is None:
@@ -107,6 +110,10 @@ class HostForward:
         u = uniforms.to(self.dev, non_blocking=True)
         ref = ref if self.has_ref else None
         mask = mask if self.has_mask else None
+        if mask_bits is not None:
+            mask, mask_by_copy = mask_bits, True
+            if getattr(self, "_mapped_bits", None) is None or self._mapped_bits[0].shape[0] < min(chunk_rows, rows):
+                self._mapped_bits = [torch.empty(min(chunk_rows, rows), mask_bits.shape[1], dtype=torch.int32, device=self.dev) for _ in range(2)]
         by_copy = mask_by_copy and mask is not None
         if not by_copy:
             chunk_rows = rows
@@ -123,7 +130,12 @@ class HostForward:
                     if i >= 2:
                         self.copy_stream.wait_event(free)  # the kernel that read this buffer has finished
                     m = self._mapped_masks[i % 2][: r1 - r0]
-                    m.copy_(mask[r0:r1], non_blocking=True)
+                    if mask_bits is not None:
+                        b = self._mapped_bits[i % 2][: r1 - r0]
+                        b.copy_(mask_bits[r0:r1], non_blocking=True)
+                        ops.expand_bitmask(b, self.V, out=m)  # on the copy stream (torch's current stream here)
+                    else:
+                        m.copy_(mask[r0:r1], non_blocking=True)
                     ready.record(self.copy_stream)
                 compute.wait_event(ready)
             f = ops.row_forward(logits[r0:r1], ref_logits=None if ref is None else ref[r0:r1], allow=m, uniforms=u[r0:r1], device=self.dev)

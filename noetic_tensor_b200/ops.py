@@ -257,6 +257,26 @@ def group_advantages(rewards, *, norm_std=False, eps=0.0, unbiased=True):
     return out
 
 
+def expand_bitmask(bits, V, rows=None, out=None):
+    """U8 allow-mask [rows, V] from bit-packed masks: `bits` int32 [rows, ceil(V/32)] (or [1, …]
+    with `rows` given, broadcast), bit v of a row = bit (v mod 32) of word v / 32."""
+    dev = bits.device
+    if bits.dtype != torch.int32 or bits.dim() != 2 or not bits.is_contiguous() or dev.type != "cuda" or bits.shape[1] < (V + 31) // 32:
+        raise ValueError("bits: contiguous int32 CUDA tensor [rows, >= ceil(V/32)]")
+    stride = bits.shape[1]
+    if rows is None:
+        rows = bits.shape[0]
+    elif bits.shape[0] == 1 and rows != 1:
+        stride = 0
+    elif bits.shape[0] != rows:
+        raise ValueError("bits: [rows, words] or [1, words]")
+    if out is None:
+        out = torch.empty(rows, V, dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_expand_bitmask(rows, V, _p(bits), stride, _p(out), _stream(dev)), "nrl_expand_bitmask")
+    return out
+
+
 def check_status(status):
     """Raises the reference's error (src/nn/rl.rs:517-519) if any row was refused."""
     bad, bits = C.c_uint64(0), C.c_uint32(0)

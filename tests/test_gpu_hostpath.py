@@ -153,8 +153,31 @@ def test_mapped_host_rows_equal_the_resident_forward(dtype, ref, rows):
     # several chunks, the mask one chunk ahead: the launches of the resident forward over the same chunks
     chunk = max(16, rows // 3)
     got = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=chunk)
+    bits = torch.from_numpy(np.packbits(np.pad(m.cpu().numpy(), ((0, 0), (0, (-V) % 32))), axis=1, bitorder="little").view(np.int32)).pin_memory()
+    got_bits = hf.run_mapped(hx, hu, ref=hr, mask_bits=bits, chunk_rows=chunk)  # the same rows with bit-packed masks
+    for name in ("tokens", "logp", "entropy"):
+        assert torch.equal(_bits(got_bits[name]), _bits(got[name])), name
     parts = [ops.row_forward(x[a:a + chunk], ref_logits=None if r is None else r[a:a + chunk], allow=m[a:a + chunk], uniforms=u[a:a + chunk]) for a in range(0, rows, chunk)]
     for name in ("tokens", "logp", "entropy") + (("kl",) if ref else ()):
         assert torch.equal(_bits(got[name]), _bits(torch.cat([getattr(f, name) for f in parts]).cpu())), name
     with pytest.raises(ValueError, match="pinned"):
         ops.row_forward(x.cpu(), allow=pin(m), uniforms=u, device=dev)
+
+
+@pytest.mark.parametrize("V", [1, 7, 8, 31, 32, 33, 100, 4104, 128256])
+def test_expand_bitmask(V):
+    from noetic_tensor_b200 import ops
+
+    dev = torch.device("cuda:0")
+    g = np.random.default_rng(V)
+    rows = 5
+    m = (g.uniform(0, 1, (rows, V)) < 0.3).astype(np.uint8)
+    words = (V + 31) // 32
+    padded = np.zeros((rows, words * 32), np.uint8)
+    padded[:, :V] = m
+    bits = np.packbits(padded, axis=1, bitorder="little").view(np.uint32).astype(np.int64)
+    bits = torch.from_numpy(bits.astype(np.uint32).view(np.int32).reshape(rows, words)).to(dev)
+    out = ops.expand_bitmask(bits, V)
+    assert np.array_equal(out.cpu().numpy(), m)
+    one = ops.expand_bitmask(bits[:1].contiguous(), V, rows=4)
+    assert np.array_equal(one.cpu().numpy(), np.repeat(m[:1], 4, axis=0))
