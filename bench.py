@@ -355,6 +355,11 @@ def run_extras(dev, peak):
 
 
 def run_ours(args):
+    # stdout carries the one JSON line and nothing else: libraries that write to it (NCCL prints
+    # its version there when the communicator comes up) are sent to stderr until the line is printed
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     import torch
     import torch.distributed as dist
 
@@ -543,7 +548,9 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
             "bitwise_reproducible": reproducible, "refused_rows": bad, "extras": extras,
         }
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(json_fd, 1)
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
