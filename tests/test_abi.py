@@ -40,6 +40,9 @@ def test_struct_layouts():
     assert C.sizeof(capi.TokenLossArgs) == 8 + 3 * 8 + 3 * 8 + 8 + 8 + 4 * 8 + 8 + 3 * 8
     assert C.sizeof(capi.CeArgs) == 8 + 8 + 8 + 8 * 8
     assert C.sizeof(capi.GumbelArgs) == 4 * 4 + 8 + 5 * 8 + 32 + 8 + 2 * 8
+    assert C.sizeof(capi.LaneArgs) == 4 * 4 + 8 + 5 * 8
+    assert C.sizeof(capi.PackArgs) == 4 * 4 + 8 + 3 * 8 + 8 + 5 * 8 + 8
+    assert C.sizeof(capi.UnpackArgs) == 4 * 4 + 8 + 8 * 8
 
 
 def test_argument_checks_run_before_any_cuda_call():
