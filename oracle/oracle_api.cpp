@@ -299,6 +299,10 @@ extern "C" int orc_sample_gumbel(const void* logits, int dtype, int64_t rows, in
 // when t lies within 1e-6·Z of the cumulative sum just below or just above the chosen token (the
 // lower one only if an earlier token has mass): there an f32 evaluation may legitimately pick a
 // neighbour. status bit0: no allowed token; bit1: NaN.
+// PARITY UNPINNED for the sampled tokens: the reference has no inverse-CDF sampler (its own is
+// Gumbel-max, restated above), so this function is the definition, not a restatement. The values
+// it returns beside the token (log-prob, KL, entropy) are checked in the tests against the
+// restated engine's token_log_probs / reference_kl / categorical_entropy, which are pinned.
 extern "C" int orc_sample_inverse_cdf(const void* logits, int dtype, const void* ref_logits, int ref_dtype, int64_t rows, int64_t V, double temperature,
                                       const float* add_mask, int64_t add_stride, const uint8_t* allow, int64_t allow_stride, const float* uniforms,
                                       const int64_t* given_tokens, int64_t* tokens, uint8_t* boundary, double* logp, double* ref_logp, double* kl,

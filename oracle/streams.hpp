@@ -8,7 +8,9 @@
 //     source is not part of the reference tree). Words are consumed in order, block after block;
 //     `next_u64` is two consecutive words, low word first (rand_core 0.6.4 `BlockRng`).
 //     The reference's tests pin the stream only behaviourally (src/nn/tests/rl.rs:596-615), so
-//     the byte stream is checked against RFC 8439's zero-key/zero-nonce keystream instead.
+//     the byte stream is checked against RFC 8439's zero-key/zero-nonce keystream instead:
+//     PARITY UNPINNED against rand_chacha's own output for this stream (no vector of it exists
+//     in the reference tree and the crate cannot be built here).
 //   * bfloat16 round-to-nearest-even and exact upcast (src/tensor/half.rs:15-31).
 #pragma once
 #include <cstdint>
