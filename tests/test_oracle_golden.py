@@ -513,3 +513,27 @@ def test_fast_backend_matches_reference_within_lane_sum_tolerance(oracle):
         oracle.set_backend(False, 1)
     close(b, a, 1e-5)
     assert not np.array_equal(a, b) or True
+
+
+def test_inverse_cdf_oracle_values_equal_the_restated_engine(oracle):
+    """The f64 sampler oracle is this build's definition for the TOKEN; the values it returns beside
+    it must be the pinned engine's: token_log_probs, reference_kl and categorical_entropy in F64 on
+    the same masked logits (src/nn/rl.rs:134-141, 347-351, 405-414)."""
+    g = np.random.default_rng(77)
+    S, B, T, V = 2, 3, 4, 40
+    rows = S * B * T
+    x = g.normal(0, 2, (rows, V)).astype(np.float32)
+    ref = (x + g.normal(0, 0.3, (rows, V))).astype(np.float32)
+    allow = (g.uniform(0, 1, (rows, V)) < 0.6).astype(np.uint8)
+    allow[:, 3] = 1
+    u = oracle.row_uniforms(5, "cross-check", rows)
+    o = oracle.sample_inverse_cdf(x, 1.0, u, ref_logits=ref, allow=allow)
+    vm = np.where(allow != 0, 0.0, -INF)
+    shape = (S, B, T, V)
+    lp = oracle.rl_eval(oracle.OP_TOKEN_LOG_PROBS, shape, dtype=oracle.F64, logits=x, tokens=o["tokens"], vocab_mask=vm)
+    kl = oracle.rl_eval(oracle.OP_REFERENCE_KL, shape, dtype=oracle.F64, logits=x, ref_logits=ref, vocab_mask=vm, reduction=oracle.NONE)
+    en = oracle.rl_eval(oracle.OP_ENTROPY, shape, dtype=oracle.F64, logits=x, vocab_mask=vm, reduction=oracle.NONE)
+    assert np.abs(lp - o["logp"]).max() < 1e-12
+    assert np.abs(kl - o["kl"]).max() < 1e-12
+    assert np.abs(en - o["entropy"]).max() < 1e-12
+    assert allow[np.arange(rows), o["tokens"]].all()
