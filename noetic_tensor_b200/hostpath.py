@@ -102,6 +102,9 @@ class HostForward:
         bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
         v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and
         nrl_expand_bitmask writes the byte mask on the device."""
+        if mask is None and mask_bits is None:
+            # every logit is read: copies move whole rows about twice as fast as loads over the link
+            return self.run(logits, uniforms, ref=ref, mask=None, out=out)
         rows = logits.shape[0]
         pin = lambda dt: torch.empty(rows, dtype=dt).pin_memory()
         if out is None:
