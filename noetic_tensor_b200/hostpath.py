@@ -102,6 +102,8 @@ class HostForward:
         bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
         v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and
         nrl_expand_bitmask writes the byte mask on the device."""
+        if not self.has_mask:
+            mask = mask_bits = None
         if mask is None and mask_bits is None:
             # every logit is read: copies move whole rows about twice as fast as loads over the link
             return self.run(logits, uniforms, ref=ref, mask=None, out=out)
@@ -156,6 +158,8 @@ class HostForward:
     def run(self, logits, uniforms, ref=None, mask=None, out=None):
         """logits/ref [rows, V], mask [rows, V] u8, uniforms [rows]: pinned host tensors. Returns
         pinned host tensors tokens (i32), logp, kl, entropy (f32) and status (u8), complete on return."""
+        if (self.has_mask and mask is None) or (self.has_ref and ref is None):
+            raise ValueError("HostForward was built for rows with a mask / a reference stream: pass them")
         rows = logits.shape[0]
         if out is None:
             pin = lambda dt: torch.empty(rows, dtype=dt).pin_memory()
