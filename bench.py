@@ -262,7 +262,21 @@ def run_extras(dev, peak):
     res["headline_bwd_only"] = entry(rows, _time(lambda: ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones, g_ent=ones, out=d)), rows * V * (5 + 4),
                                      "row backward alone (reads logits, reference, mask; writes f32 gradients)")
     res["unmasked_fwd"] = entry(rows, _time(lambda: ops.row_forward(x, ref_logits=r, uniforms=u)), rows * V * 4, "same logits and reference without a mask: every byte is read")
-    del x, r, m, d, f
+    # the same rows with the mask bit-packed (one bit per token, read by the kernels as it is)
+    import numpy as np
+    bits = torch.from_numpy(np.packbits(m.cpu().numpy(), axis=1, bitorder="little").view(np.int32)).to(dev)
+    fb = ops.row_forward(x, ref_logits=r, allow_bits=bits, uniforms=u)
+    same = bool(torch.equal(fb.tokens, f.tokens) and torch.equal(fb.logp.view(torch.int32), f.logp.view(torch.int32)))
+    res["headline_fwd_bit_masks"] = entry(rows, _time(lambda: ops.row_forward(x, ref_logits=r, allow_bits=bits, uniforms=u)), rows * V * 4 + rows * (V // 8),
+                                          "headline forward with bit-packed masks (NRL_FWD_MASK_BITS): 4 B of logits + 1 bit of mask per token")
+    res["headline_fwd_bit_masks"]["same_bits_as_byte_masks"] = same
+
+    def fwd_bwd_bits():
+        g = ops.row_forward(x, ref_logits=r, allow_bits=bits, uniforms=u)
+        ops.row_backward(x, g, ref_logits=r, allow_bits=bits, g_logp=ones, g_kl=ones, g_ent=ones, out=d)
+
+    res["headline_fwd_bwd_bit_masks"] = entry(rows, _time(fwd_bwd_bits), rows * V * (4 + 4 + 4) + 2 * rows * (V // 8), "forward + backward with bit-packed masks")
+    del x, r, m, d, f, fb, bits
 
     # config 4: one PPO step, V = 151936, forward + token losses + backward
     V4, S4, B4, T4 = 151936, 1, 32, 256
@@ -515,7 +529,7 @@ def run_ours(args):
                                   "over the host link; the byte mask, read whole, goes up by copies in 2048-row chunks one chunk ahead of the kernel; uniforms go up and per-row results come back by copies, all inside the timed region; "
                                   "the byte count is an estimate (mask bytes + live vectors), the link has no counter here"},
                "bit_packed_masks": {"value": bits_rate, "this_rank_only": True, "same_tokens": bits_ok, "h2d_bytes_per_step_estimate": int(mapped_bytes - e2e_rows * V + e2e_rows * (V // 8)),
-                                    "note": "not the headline input format: the same rows from a caller that holds int32 bit masks [rows, V/32]; nrl_expand_bitmask writes the byte mask on the device"},
+                                    "note": "not the headline input format: the same rows from a caller that holds int32 bit masks [rows, V/32], which the kernels read as they are (NRL_FWD_MASK_BITS)"},
                "packed": {"value": packed_rate, "h2d_bytes_per_step": int(hf.h2d_bytes), "packed_chunks": hf.packed_chunks, "whole_chunks": hf.whole_chunks, "host_threads": hf.threads,
                           "note": "512-row chunks, double-buffered: host threads keep the vectors the mask allows (nrl_host_pack), those cross PCIe by copies, a kernel puts them in place "
                                   "(nrl_unpack_rows), then the same forward; the packing runs inside the timed region"},

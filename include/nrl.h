@@ -84,7 +84,11 @@ uint64_t nrl_launch_count(void);
 enum {
     NRL_FWD_SAMPLE = 1u << 0,  /* draw tokens (needs `uniforms`, writes `tokens`) */
     NRL_FWD_GREEDY = 1u << 1,  /* tokens = first maximum of z (temperature 0); writes `tokens` */
-    NRL_FWD_TOKENS_IN = 1u << 2 /* `tokens` is an input (token_log_probs of given tokens) */
+    NRL_FWD_TOKENS_IN = 1u << 2, /* `tokens` is an input (token_log_probs of given tokens) */
+    NRL_FWD_MASK_BITS = 1u << 3  /* `allow_mask` is bit-packed (no counterpart in the reference, whose masks are a byte or an
+                                    f32 per token): u32 words, bit v of a row = bit (v mod 32) of its word v / 32, and
+                                    `allow_row_stride` counts WORDS between rows (>= ceil(V / 32), or 0 for one row
+                                    broadcast). The kernels read V / 8 mask bytes per row instead of V */
 };
 
 typedef struct nrl_row_fwd_args {
@@ -176,7 +180,7 @@ typedef struct nrl_row_bwd_args {
     nrl_devptr d_logits; /* out f32 [rows, V] */
     uint32_t accumulate; /* 1: add into d_logits instead of overwriting it (the tape's `new + old`,
                             src/tensor/autodiff.rs:198-201, without a separate pass) */
-    uint32_t reserved0;
+    uint32_t mask_bits;  /* 1: allow_mask is bit-packed as with NRL_FWD_MASK_BITS (allow_row_stride in words) */
     nrl_devptr g_uniform;    /* f32 [rows] or 0: upstream gradient of −mean_v log π_v (the label-smoothing
                                 term of cross_entropy_with, src/nn/loss.rs:70-72); adds g·(π_j − 1/V).
                                 Not with masks or a temperature (NRL_E_UNSUPPORTED) */

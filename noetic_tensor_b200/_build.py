@@ -8,8 +8,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnrl.so")
-SOURCES = ["nrl_api.cu"]
-HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh", "lane_ops.cuh"]
+SOURCES = ["nrl_api.cu", "nrl_bits.cu"]  # the second compiles the row kernels again for bit-packed masks
+HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh", "lane_ops.cuh", "row_api.inl"]
 INCLUDE = os.path.join(os.path.dirname(HERE), "include", "nrl.h")
 
 
@@ -39,20 +39,33 @@ def up_to_date():
 def build(force=False, verbose=False):
     if not force and up_to_date():
         return LIB
-    cmd = [
+    common = [
         nvcc_path(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-        "--shared", "-Xcompiler", "-fPIC", "-cudart", "static", "--fmad=true",
-        f'-DNRL_SRC_HASH="{source_hash()}"',
-        "-o", LIB,
-    ] + [os.path.join(CSRC, s) for s in SOURCES]
+        "-Xcompiler", "-fPIC", "--fmad=true", f'-DNRL_SRC_HASH="{source_hash()}"',
+    ]
     if verbose:
-        cmd.insert(1, "-Xptxas=-v")
-    r = subprocess.run(cmd, capture_output=True, text=True)
+        common.insert(1, "-Xptxas=-v")
+    # one object per source, compiled side by side, then linked into the shared library
+    objs, procs = [], []
+    for src in SOURCES:
+        obj = os.path.join(HERE, "build", os.path.splitext(src)[0] + ".o")
+        os.makedirs(os.path.dirname(obj), exist_ok=True)
+        objs.append(obj)
+        procs.append(subprocess.Popen(common + ["-c", os.path.join(CSRC, src), "-o", obj], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    failed = False
+    for pr in procs:
+        out, err = pr.communicate()
+        if pr.returncode != 0:
+            sys.stderr.write(out + err)
+            failed = True
+        elif verbose:
+            sys.stderr.write(err)
+    if failed:
+        raise RuntimeError("nvcc failed building libnrl.so")
+    r = subprocess.run([nvcc_path(), "--shared", "-cudart", "static", "-o", LIB] + objs, capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
-        raise RuntimeError("nvcc failed building libnrl.so")
-    if verbose:
-        sys.stderr.write(r.stderr)
+        raise RuntimeError("nvcc failed linking libnrl.so")
     return LIB
 
 

@@ -12,7 +12,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnrl.so")
 
 F32, BF16 = 0, 1
-FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN = 1, 2, 4
+FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN, FWD_MASK_BITS = 1, 2, 4, 8
 LOSS_PG, LOSS_PPO, LOSS_K1, LOSS_K2, LOSS_K3 = range(5)
 REDUCE_NONE, REDUCE_SUM, REDUCE_TOKEN_MEAN, REDUCE_PER_SEQUENCE, REDUCE_SEQUENCE_MEAN = range(5)
 E_BAD_ARG, E_UNSUPPORTED, E_WORKSPACE, E_ROW_STATUS, E_NO_DEVICE = -1, -2, -3, -4, -5
@@ -34,7 +34,7 @@ class RowBwdArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("dtype", u32), ("V", u32), ("temperature", f32), ("rows", u64),
         ("logits", ptr), ("ref_logits", ptr), ("allow_mask", ptr), ("allow_row_stride", u64), ("add_mask", ptr), ("add_row_stride", u64),
-        ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr), ("accumulate", u32), ("reserved0", u32),
+        ("tokens", ptr), ("rowstats", ptr), ("kl", ptr), ("entropy", ptr), ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr), ("d_logits", ptr), ("accumulate", u32), ("mask_bits", u32),
         ("g_uniform", ptr), ("d_ref_logits", ptr),
     ]
 

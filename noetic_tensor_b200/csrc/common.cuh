@@ -153,19 +153,74 @@ struct Raw<NRL_F32> {
     }
 };
 
+// ---- the allow-mask of a row ---------------------------------------------------------------------
+// NRL_MASK_BITS 0: a byte per token (`mrow` points at the row's V bytes). NRL_MASK_BITS 1: a bit
+// per token (`mrow` points at the row's bit-packed words, read as bytes: bit v of the row is bit
+// v mod 8 of byte v / 8, which on a little-endian machine is bit v mod 32 of word v / 32). Either
+// way the kernels work on "the eight mask bytes of the vector at element v": with bits they are
+// spread out of one byte (0 or 1 each).
+#ifndef NRL_MASK_BITS
+#define NRL_MASK_BITS 0
+#endif
+__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint32_t spread4(uint32_t nibble) { return (nibble * 0x00204081u) & 0x01010101u; }  // bit k -> byte k
+// the eight mask bytes of the vector at element v (a multiple of 8)
+__device__ __forceinline__ uint2 ldg_mask8(const uint8_t* mrow, uint32_t v) {
+#if NRL_MASK_BITS
+    const uint32_t b = __ldg(mrow + (v >> 3));
+    return make_uint2(spread4(b & 0xfu), spread4(b >> 4));
+#else
+    return ldg_stream8(mrow + v);
+#endif
+}
+// the four mask bytes at element e (a multiple of 4)
+__device__ __forceinline__ uint32_t ldg_mask4(const uint8_t* mrow, uint32_t e) {
+#if NRL_MASK_BITS
+    return spread4((__ldg(mrow + (e >> 3)) >> (e & 4u)) & 0xfu);
+#else
+    return ldg_stream4(mrow + e);
+#endif
+}
+// what a scan needs of a vector's mask: something that is non-zero iff a token of it is allowed
+#if NRL_MASK_BITS
+typedef uint32_t MaskAny;
+__device__ __forceinline__ MaskAny ldg_mask_any(const uint8_t* mrow, uint32_t v) { return __ldg(mrow + (v >> 3)); }
+__device__ __forceinline__ MaskAny mask_any_none() { return 0u; }
+__device__ __forceinline__ uint32_t mask_any_value(MaskAny a) { return a; }
+#else
+typedef uint2 MaskAny;
+__device__ __forceinline__ MaskAny ldg_mask_any(const uint8_t* mrow, uint32_t v) { return ldg_stream8(mrow + v); }
+__device__ __forceinline__ MaskAny mask_any_none() { return make_uint2(0u, 0u); }
+__device__ __forceinline__ uint32_t mask_any_value(MaskAny a) { return a.x | a.y; }
+#endif
+
 // eight allow-mask bytes
 struct RawMask {
     uint2 q;
-    __device__ __forceinline__ void load(const uint8_t* base, uint64_t elem) { q = ldg_stream8(base + elem); }
-    __device__ __forceinline__ void load_scalar(const uint8_t* base, uint64_t elem, int n) {
+    __device__ __forceinline__ void load(const uint8_t* mrow, uint32_t v) { q = ldg_mask8(mrow, v); }
+#if NRL_MASK_BITS
+    // n tokens from element v on (any v): bits beyond n read as excluded
+    __device__ __forceinline__ void load_scalar(const uint8_t* mrow, uint32_t v, int n) {
+        uint32_t w = __ldg(mrow + (v >> 3));
+        if ((v & 7u) + (uint32_t)n > 8u) w |= (uint32_t)__ldg(mrow + (v >> 3) + 1) << 8;
+        w = (w >> (v & 7u)) & ((1u << n) - 1u);
+        q = make_uint2(spread4(w & 0xfu), spread4((w >> 4) & 0xfu));
+    }
+#else
+    __device__ __forceinline__ void load_scalar(const uint8_t* mrow, uint32_t v, int n) {
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int i = 0; i < 4; i++) {
-            if (i < n) lo |= (uint32_t)__ldg(base + elem + i) << (8 * i);
-            if (i + 4 < n) hi |= (uint32_t)__ldg(base + elem + i + 4) << (8 * i);
+            if (i < n) lo |= (uint32_t)__ldg(mrow + v + i) << (8 * i);
+            if (i + 4 < n) hi |= (uint32_t)__ldg(mrow + v + i + 4) << (8 * i);
         }
         q = make_uint2(lo, hi);
     }
+#endif
     __device__ __forceinline__ bool allowed(int i) const { return (((i < 4 ? q.x : q.y) >> (8 * (i & 3))) & 0xffu) != 0u; }
     __device__ __forceinline__ bool any() const { return (q.x | q.y) != 0u; }
 };

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
         if constexpr (ALLOW && VEC && !GENERAL) {
             // an excluded vector has zero gradient whatever its logits are: only its 8 mask bytes are read
             RawMask mk;
-            mk.load(f.allow, row * f.allow_stride + v);
+            mk.load(f.allow + row * f.allow_stride, v);
             const bool holds_token = tok >= (int32_t)v && tok < (int32_t)(v + kVec);  // its entry gets g_lp even if excluded
             if (!mk.any() && !holds_token) {
                 if (accumulate) continue;
@@ -146,11 +146,6 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_kernel(BwdParams p) {
 // lane takes 4 consecutive elements of each (element 4·lane and 128 + 4·lane of the tile): every
 // warp-wide store, and every load of f32 logits, covers 512 contiguous bytes. bf16 logits arrive
 // as 8-byte loads (256 contiguous bytes per warp), mask bytes as 4-byte loads.
-__device__ __forceinline__ uint32_t ldg_stream4(const void* p) {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-    return v;
-}
 
 template <int DT>
 struct Piece {  // 4 consecutive elements of one stream
@@ -216,7 +211,7 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_split_kernel(BwdParams
         for (int k = 0; k < 2; k++) {
             e[k] = t + k * kHalf + lane * 4;
             mk[k] = 0xffffffffu;
-            if (ALLOW) mk[k] = e[k] < t_end ? ldg_stream4(mrow + e[k]) : 0u;
+            if (ALLOW) mk[k] = e[k] < t_end ? ldg_mask4(mrow, e[k]) : 0u;
         }
 #pragma unroll
         for (int k = 0; k < 2; k++) {

@@ -69,13 +69,13 @@ struct VecLoader {
         if (VEC) {
             x.load(p.logits, e);
             if (REF) r.load(p.ref, e);
-            if (ALLOW) k.load(p.allow, row * p.allow_stride + v);
+            if (ALLOW) k.load(p.allow + row * p.allow_stride, v);
             if (GENERAL && p.add) am.load(p.add, row * p.add_stride + v);
         } else {
             int n = (int)(end - v < (uint32_t)kVec ? end - v : (uint32_t)kVec);
             x.load_scalar(p.logits, e, n);
             if (REF) r.load_scalar(p.ref, e, n);
-            if (ALLOW) k.load_scalar(p.allow, row * p.allow_stride + v, n);
+            if (ALLOW) k.load_scalar(p.allow + row * p.allow_stride, v, n);
             if (GENERAL && p.add) am.load_scalar(p.add, row * p.add_stride + v, n);
         }
     }
@@ -483,15 +483,22 @@ __device__ __forceinline__ Partial stream_part_compact(const FwdParams& p, uint6
     uint32_t head = 0, count = 0;  // warp-uniform ring state
 
     // this lane's mask bytes of the tile at `v`: pointer arithmetic is one 64-bit add per group
+    // (with a bit per token, kMaskStep bytes of the row's mask cover one element step of 8)
+#if NRL_MASK_BITS
+    const uint8_t* mp = p.allow + row * p.allow_stride + ((begin + lane * kVec) >> 3);
+    constexpr uint32_t kTileMask = kTile / 8;  // mask bytes a tile spans
+#else
     const uint8_t* mp = p.allow + row * p.allow_stride + begin + lane * kVec;
+    constexpr uint32_t kTileMask = kTile;
+#endif
     uint32_t v = begin + lane * kVec;
     uint32_t t0 = begin;  // warp-uniform tile base of the group in mk[]
-    uint32_t mk[kA];  // OR of a tile's eight mask bytes: all the scan needs
-    uint2 mn[kA];
+    uint32_t mk[kA];  // non-zero iff the tile's vector of this lane allows a token: all the scan needs
+    MaskAny mn[kA];
 #pragma unroll
     for (int j = 0; j < kA; j++) {
-        uint2 q = (v + j * kTile < end) ? ldg_stream8(mp + j * kTile) : make_uint2(0u, 0u);
-        mk[j] = q.x | q.y;
+        const MaskAny q = (v + j * kTile < end) ? ldg_mask_any(mp + j * kTileMask, 0) : mask_any_none();
+        mk[j] = mask_any_value(q);
     }
     // One loop with one copy of the arithmetic (a small instruction footprint): each turn scans
     // a group of mask tiles if any is left, then folds batches while at least 32 vectors are
@@ -502,11 +509,13 @@ __device__ __forceinline__ Partial stream_part_compact(const FwdParams& p, uint6
             // the next group's mask bytes fly while this group is scanned, and the group eight
             // ahead is pulled into L2 (one 128-byte line per lane 0..7) so that its loads are
             // short when their turn comes
-            const uint8_t* np = mp + kA * kTile;
+            const uint8_t* np = mp + kA * kTileMask;
             const uint32_t nv = v + kA * kTile;
+#if !NRL_MASK_BITS
             if (lane < 8 && t0 + 8 * kA * kTile + lane * 128 < end) prefetch_l2(mp - lane * kVec + 8 * kA * kTile + lane * 128);
+#endif
 #pragma unroll
-            for (int j = 0; j < kA; j++) mn[j] = (nv + j * kTile < end) ? ldg_stream8(np + j * kTile) : make_uint2(0u, 0u);
+            for (int j = 0; j < kA; j++) mn[j] = (nv + j * kTile < end) ? ldg_mask_any(np + j * kTileMask, 0) : mask_any_none();
 #pragma unroll
             for (int j = 0; j < kA; j++) {
                 const bool nz = mk[j] != 0u;
@@ -515,7 +524,7 @@ __device__ __forceinline__ Partial stream_part_compact(const FwdParams& p, uint6
                 count += __popc(ball);
             }
 #pragma unroll
-            for (int j = 0; j < kA; j++) mk[j] = mn[j].x | mn[j].y;
+            for (int j = 0; j < kA; j++) mk[j] = mask_any_value(mn[j]);
             mp = np;
             v = nv;
             t0 += kA * kTile;

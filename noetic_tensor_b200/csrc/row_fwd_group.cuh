@@ -130,7 +130,7 @@ __device__ __forceinline__ uint32_t regather_batch(const FwdParams& p, uint64_t 
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const uint32_t v = t0 + j * kTile + lane * kVec;
-            q[j] = (v >= v0 && v < end) ? ldg_stream8(mrow + v) : make_uint2(0u, 0u);
+            q[j] = (v >= v0 && v < end) ? ldg_mask8(mrow, v) : make_uint2(0u, 0u);
         }
 #pragma unroll
         for (int j = 0; j < 4; j++) {

@@ -100,8 +100,8 @@ class HostForward:
         `chunk_rows`-row chunks one chunk ahead of the kernel (the copy engine moves it faster than
         loads over the link do); otherwise one launch reads everything in place. A caller that holds
         bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
-        v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and
-        nrl_expand_bitmask writes the byte mask on the device."""
+        v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and the kernels read
+        the bits as they are (NRL_FWD_MASK_BITS)."""
         if not self.has_mask:
             mask = mask_bits = None
         if mask is None and mask_bits is None:
@@ -122,9 +122,11 @@ class HostForward:
         by_copy = mask_by_copy and mask is not None
         if not by_copy:
             chunk_rows = rows
-        elif getattr(self, "_mapped_masks", None) is None or self._mapped_masks[0].shape[0] < min(chunk_rows, rows):
-            self._mapped_masks = [torch.empty(min(chunk_rows, rows), self.V, dtype=torch.uint8, device=self.dev) for _ in range(2)]
-            self._mapped_events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(2)]
+        else:
+            if getattr(self, "_mapped_events", None) is None:
+                self._mapped_events = [(torch.cuda.Event(), torch.cuda.Event()) for _ in range(2)]
+            if mask_bits is None and (getattr(self, "_mapped_masks", None) is None or self._mapped_masks[0].shape[0] < min(chunk_rows, rows)):
+                self._mapped_masks = [torch.empty(min(chunk_rows, rows), self.V, dtype=torch.uint8, device=self.dev) for _ in range(2)]
         results = []
         for i, r0 in enumerate(range(0, rows, chunk_rows)):
             r1 = min(rows, r0 + chunk_rows)
@@ -134,16 +136,17 @@ class HostForward:
                 with torch.cuda.stream(self.copy_stream):
                     if i >= 2:
                         self.copy_stream.wait_event(free)  # the kernel that read this buffer has finished
-                    m = self._mapped_masks[i % 2][: r1 - r0]
                     if mask_bits is not None:
-                        b = self._mapped_bits[i % 2][: r1 - r0]
-                        b.copy_(mask_bits[r0:r1], non_blocking=True)
-                        ops.expand_bitmask(b, self.V, out=m)  # on the copy stream (torch's current stream here)
+                        m, bits = None, self._mapped_bits[i % 2][: r1 - r0]
+                        bits.copy_(mask_bits[r0:r1], non_blocking=True)
                     else:
+                        m, bits = self._mapped_masks[i % 2][: r1 - r0], None
                         m.copy_(mask[r0:r1], non_blocking=True)
                     ready.record(self.copy_stream)
                 compute.wait_event(ready)
-            f = ops.row_forward(logits[r0:r1], ref_logits=None if ref is None else ref[r0:r1], allow=m, uniforms=u[r0:r1], device=self.dev)
+            else:
+                bits = None
+            f = ops.row_forward(logits[r0:r1], ref_logits=None if ref is None else ref[r0:r1], allow=m, allow_bits=bits, uniforms=u[r0:r1], device=self.dev)
             if by_copy:
                 free.record(compute)
             for name in ("tokens", "logp", "kl", "entropy", "status"):

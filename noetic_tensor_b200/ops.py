@@ -46,6 +46,16 @@ def _masks(V, rows, allow, add, dev):
     return allow, a_stride, add, d_stride
 
 
+def _bit_mask(V, rows, allow_bits, dev):
+    """(tensor, stride in words) of a bit-packed allow-mask: int32 [rows, words >= ceil(V/32)] or
+    [1, words] (broadcast), bit v of a row = bit (v mod 32) of its word v / 32."""
+    if allow_bits.dtype != torch.int32 or allow_bits.dim() != 2 or not allow_bits.is_contiguous() or allow_bits.device != dev:
+        raise ValueError(f"allow_bits: contiguous int32 [rows, words] on {dev}")
+    if allow_bits.shape[1] < (V + 31) // 32 or allow_bits.shape[0] not in (1, rows):
+        raise ValueError("allow_bits: [rows, >= ceil(V/32)] or [1, >= ceil(V/32)]")
+    return allow_bits, (0 if allow_bits.shape[0] == 1 and rows != 1 else allow_bits.shape[1])
+
+
 class RowForward:
     """Outputs of nrl_row_fwd over [rows, V] logits (fields are None when not requested)."""
 
@@ -53,7 +63,7 @@ class RowForward:
 
 
 def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, uniforms=None, tokens=None, greedy=False,
-                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None, device=None):
+                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None, device=None, allow_bits=None):
     """Fused sample / log-prob / KL / entropy over logits [rows, V] (f32 or bf16, CUDA).
 
     Exactly one of: `uniforms` (sample by inverse CDF), `greedy=True`, `tokens` (given, int32), or
@@ -62,7 +72,11 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
     With `device` given, `logits`, `ref_logits` and the masks may be PINNED host tensors: pinned
     memory is mapped into the device's address space, so the kernel reads them in place over the
     host link (with a byte mask, only the mask and the vectors it allows cross it). Everything else
-    (uniforms, tokens, the outputs) lives on `device`."""
+    (uniforms, tokens, the outputs) lives on `device`.
+
+    `allow_bits` instead of `allow`: the mask bit-packed, int32 [rows, ceil(V/32)] (or [1, …]) on
+    the device, bit v of a row = bit (v mod 32) of word v / 32; the kernels read V/8 mask bytes
+    per row instead of V."""
     in_dev = logits.device
     dev = torch.device(device) if device is not None else in_dev
     if dev.type != "cuda":
@@ -85,6 +99,12 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
     allow, a.allow_row_stride, _, _ = _masks(V, rows, allow, None, dev if (allow is not None and allow.device == dev) else in_dev)
     _, _, add_mask, a.add_row_stride = _masks(V, rows, None, add_mask, dev if (add_mask is not None and add_mask.device == dev) else in_dev)
     a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
+    bits_flag = 0
+    if allow_bits is not None:
+        if allow is not None:
+            raise ValueError("give `allow` or `allow_bits`, not both")
+        allow_bits, a.allow_row_stride = _bit_mask(V, rows, allow_bits, dev)
+        a.allow_mask, bits_flag = _p(allow_bits), capi.FWD_MASK_BITS
     out = RowForward()
     f32 = dict(dtype=torch.float32, device=dev)
     mode = 0
@@ -101,7 +121,7 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
         out.tokens = tokens
     else:
         out.tokens = None
-    a.flags, a.tokens = mode, _p(out.tokens)
+    a.flags, a.tokens = mode | bits_flag, _p(out.tokens)
     has_ref = ref_logits is not None
     want_kl = has_ref if want_kl is None else want_kl
     want_ref_logp = (has_ref and mode != 0) if want_ref_logp is None else want_ref_logp
@@ -123,7 +143,7 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
 
 
 def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, g_logp=None, g_kl=None, g_ent=None, out=None, accumulate=False,
-                 g_uniform=None, d_ref=None, want_d_logits=True):
+                 g_uniform=None, d_ref=None, want_d_logits=True, allow_bits=None):
     """d(logits) [rows, V] f32 from the forward's saved statistics and per-row upstream gradients.
     `g_uniform`: upstream of −mean_v log π_v (label smoothing). `d_ref=True` (or a tensor) also
     returns the KL term's gradient w.r.t. ref_logits, g_kl·(ρ − π): the result is then the pair
@@ -136,6 +156,11 @@ def row_backward(logits, fwd, *, ref_logits=None, allow=None, add_mask=None, tem
     a.logits, a.ref_logits = _p(logits), _p(ref_logits)
     allow, a.allow_row_stride, add_mask, a.add_row_stride = _masks(V, rows, allow, add_mask, dev)
     a.allow_mask, a.add_mask = _p(allow), _p(add_mask)
+    if allow_bits is not None:
+        if allow is not None:
+            raise ValueError("give `allow` or `allow_bits`, not both")
+        allow_bits, a.allow_row_stride = _bit_mask(V, rows, allow_bits, dev)
+        a.allow_mask, a.mask_bits = _p(allow_bits), 1
     for name, g in (("g_logp", g_logp), ("g_kl", g_kl), ("g_ent", g_ent), ("g_uniform", g_uniform)):
         if g is not None:
             _need(g, torch.float32, (rows,), name, dev)
