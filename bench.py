@@ -406,11 +406,19 @@ def run_ours(args):
 
     if args.variant == "unmasked":  # a profiling variant: the same logits and reference without the mask
         mask = None
-    if args.variant == "backward" and not (args.no_e2e and args.no_extras):
-        raise SystemExit("--variant backward is a profiling variant: run it with --no-e2e --no-extras")
+    if args.variant in ("backward", "bitmask") and not (args.no_e2e and args.no_extras):
+        raise SystemExit(f"--variant {args.variant} is a profiling variant: run it with --no-e2e --no-extras")
 
     def step():
         return ops.row_forward(logits, ref_logits=ref, allow=mask, uniforms=u)
+
+    if args.variant == "bitmask":  # a profiling variant: the same rows with the mask bit-packed, read by the kernel as it is
+        import numpy as np
+
+        bits = torch.cat([torch.from_numpy(np.packbits(mask[a:a + 4096].cpu().numpy(), axis=1, bitorder="little").view(np.int32)) for a in range(0, rows, 4096)]).to(dev)
+
+        def step():
+            return ops.row_forward(logits, ref_logits=ref, allow_bits=bits, uniforms=u)
 
     if args.variant == "backward":  # a profiling variant: the step is one row_bwd launch over the resident rows
         saved = step()
@@ -460,13 +468,15 @@ def run_ours(args):
     # roofline of the one kernel a step launches (this rank's own launch time)
     peak, peak_kind = measured_peak()
     alg_bytes = rows * V * (BYTES_PER_ELEM if mask is not None else 4)
+    if args.variant == "bitmask":
+        alg_bytes = rows * V * 4 + rows * (V // 8)
     if args.variant == "backward":
         alg_bytes += rows * V * 4  # the forward's reads again + f32 d(logits) written
     launch_ms = ms / args.steps
     achieved = alg_bytes / (launch_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
-                "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_bwd_kernel<bf16, ref, allow>" if args.variant == "backward" else "row_fwd_grouped<bf16, ref, allow>" if mask is not None else "row_fwd_fused<bf16, ref>", "algorithmic_bytes_per_launch": alg_bytes,
-                "traffic": None if args.variant == "backward" else (NCU_TRAFFIC_RATIO if mask is not None else 1.0) * alg_bytes,
+                "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_bwd_kernel<bf16, ref, allow>" if args.variant == "backward" else "nrl_bits::row_fwd_grouped<bf16, ref, allow>" if args.variant == "bitmask" else "row_fwd_grouped<bf16, ref, allow>" if mask is not None else "row_fwd_fused<bf16, ref>", "algorithmic_bytes_per_launch": alg_bytes,
+                "traffic": None if args.variant in ("backward", "bitmask") else (NCU_TRAFFIC_RATIO if mask is not None else 1.0) * alg_bytes,
                 "note": "algorithmic bytes count every logit, reference and mask byte once (5 B per element); the kernel does not read logits the mask "
                         "excludes, so its DRAM traffic (`traffic`, from ncu) is below the algorithmic bytes and `frac` can exceed 1"}
     if roofline["traffic"]:
@@ -556,7 +566,7 @@ def run_ours(args):
         line = {
             "metric": METRIC, "value": value, "unit": "rows/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)" if args.variant == "headline" else "config 3 rows, the d(logits) kernel alone (profiling variant, not the headline)" if args.variant == "backward" else "config 3 logits + reference WITHOUT the mask (profiling variant, not the headline)",
+            "config": {"workload": "config 3 [8,32,1024,128256] bf16 + U8 grammar mask + bf16 reference stream (headline)" if args.variant == "headline" else "config 3 rows, the d(logits) kernel alone (profiling variant, not the headline)" if args.variant == "backward" else "config 3 rows with the mask bit-packed (profiling variant, not the headline)" if args.variant == "bitmask" else "config 3 logits + reference WITHOUT the mask (profiling variant, not the headline)",
                        "storage": "bf16 logits, f32 arithmetic", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
                        "rows_per_gpu_per_step": rows, "cache": "inputs (tens of GB) far larger than the 126 MB L2; no flush needed", "partition": f"rows split across {world} rank(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
@@ -578,8 +588,8 @@ def main():
     ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
     ap.add_argument("--e2e-rows", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward"],
-                    help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; neither is the headline")
+    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward", "bitmask"],
+                    help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; bitmask: the mask bit-packed; none of them is the headline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
     ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
