@@ -54,6 +54,19 @@ class ClockSampler:
 
     def __init__(self, index):
         self.index, self.rows, self.proc = index, [], None
+        self.t0 = self.t1 = None
+
+    def wait_first(self, limit=8.0):
+        """nvidia-smi needs a second or two to come up on a box with many GPUs: wait for its first line."""
+        t = time.perf_counter()
+        while self.proc and not self.rows and time.perf_counter() - t < limit:
+            time.sleep(0.02)
+
+    def begin(self):
+        self.t0 = time.perf_counter()
+
+    def end(self):
+        self.t1 = time.perf_counter()
 
     def start(self):
         try:
@@ -66,7 +79,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append([time.perf_counter()] + [c.strip() for c in line.split(",")])
 
     def stop(self):
         if not self.proc:
@@ -78,7 +91,10 @@ class ClockSampler:
         except Exception:
             pass
         sm, mx, reasons = [], None, set()
-        for r in self.rows:
+        rows = self.rows
+        if self.t0 is not None and self.t1 is not None:  # the samples that arrived while the region of interest ran
+            rows = [r for r in rows if self.t0 <= r[0] <= self.t1 + 0.12]
+        for r in (r[1:] for r in rows):
             try:
                 sm.append(float(r[0]))
                 mx = float(r[1])
@@ -430,16 +446,18 @@ def run_ours(args):
             ops.row_backward(logits, saved, ref_logits=ref, allow=mask, g_logp=ones, g_kl=ones, g_ent=ones, out=dbuf)
             return saved
 
+    sampler = ClockSampler(local)
+    sampler.start()  # before the warm-up: nvidia-smi is up and printing by the time the timed region starts
     for _ in range(max(3, args.warmup)):
         out = step()
     torch.cuda.synchronize()
     bad = int((out.status != 0).sum().item())
+    sampler.wait_first()
 
-    sampler = ClockSampler(local)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.begin()
     launches0 = capi.lib().nrl_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -447,11 +465,26 @@ def run_ours(args):
         out = step()
     e1.record()
     torch.cuda.synchronize()
+    sampler.end()
     if world > 1:
         dist.barrier()
     ms = e0.elapsed_time(e1)
     launches = capi.lib().nrl_launch_count() - launches0
     clocks = sampler.stop()
+    if not clocks.get("samples"):
+        # K steps can be shorter than the sampler's 100 ms period: the same step repeated for ~0.7 s right
+        # after the timed region (not timed, not counted) gives the clocks under this load
+        probe = ClockSampler(local)
+        probe.start()
+        probe.wait_first()
+        probe.begin()
+        t_end = time.perf_counter() + 0.7
+        while time.perf_counter() < t_end:
+            step()
+            torch.cuda.synchronize()
+        probe.end()
+        clocks = probe.stop()
+        clocks["from"] = "the same step repeated for 0.7 s right after the timed region, which was shorter than the sampler's period"
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -282,7 +282,13 @@ inline void fill_inputs(nrl_row_fwd_args& a, const Tensor& z, const Tensor* ref)
         if (ref->shape() != z.shape() || ref->dtype() != z.dtype()) throw std::runtime_error("categorical_kl: reference logits shape");
         a.ref_logits = ref->dev();
     }
-    if (z.allow_mask_) {
+    if (z.allow_mask_ && z.allow_mask_->dtype() == DType::I32) {
+        // bit-packed: I32 words [..., ceil(V/32)] (or one row), bit v of a row = bit v mod 32 of word v / 32
+        const size_t words = z.allow_mask_->shape().back();
+        a.allow_mask = z.allow_mask_->dev();
+        a.allow_row_stride = numel(z.allow_mask_->shape()) == words && r.rows != 1 ? 0 : words;
+        a.flags |= NRL_FWD_MASK_BITS;
+    } else if (z.allow_mask_) {
         a.allow_mask = z.allow_mask_->dev();
         a.allow_row_stride = numel(z.allow_mask_->shape()) == r.V && r.rows != 1 ? 0 : r.V;
     }
@@ -304,6 +310,7 @@ inline void row_bwd(const Saved& s, const Tensor* g_lp, const Tensor* g_kl, cons
     b.dtype = f.dtype; b.V = f.V; b.temperature = f.temperature; b.rows = f.rows;
     b.logits = f.logits; b.ref_logits = f.ref_logits; b.allow_mask = f.allow_mask; b.allow_row_stride = f.allow_row_stride;
     b.add_mask = f.add_mask; b.add_row_stride = f.add_row_stride;
+    b.mask_bits = (f.flags & NRL_FWD_MASK_BITS) ? 1 : 0;
     b.tokens = g_lp ? s.tokens.dev() : 0;
     b.rowstats = s.rowstats.dev();
     b.kl = g_kl ? s.kl.dev() : 0;
@@ -376,8 +383,10 @@ inline Tensor tempered_logits(const Tensor& logits, double temperature, const Te
     Tensor z = logits;
     z.tau_ = (float)temperature * logits.tau_;
     if (mask) {
-        if (mask->shape().back() != logits.shape().back()) throw std::runtime_error("tempered_logits: mask does not broadcast to the logits");
-        if (mask->dtype() == DType::U8) z.allow_mask_ = std::make_shared<Tensor>(*mask);
+        const bool bits = mask->dtype() == DType::I32;  // a bit per token instead of a byte: I32 words [..., ceil(V/32)]
+        if (bits ? mask->shape().back() != (logits.shape().back() + 31) / 32 : mask->shape().back() != logits.shape().back())
+            throw std::runtime_error("tempered_logits: mask does not broadcast to the logits");
+        if (mask->dtype() == DType::U8 || bits) z.allow_mask_ = std::make_shared<Tensor>(*mask);
         else if (mask->dtype() == DType::F32) z.add_mask_ = std::make_shared<Tensor>(*mask);
         else throw std::runtime_error("tempered_logits: mask dtype");
     }
@@ -396,10 +405,10 @@ inline IntTensor sample_categorical(const Tensor& logits, double temperature, co
     nrl_row_fwd_args a;
     detail::fill_inputs(a, z, nullptr);
     if (temperature == 0.0) {
-        a.flags = NRL_FWD_GREEDY;
+        a.flags |= NRL_FWD_GREEDY;
     } else {
         if (!uniforms || numel(uniforms->shape()) != r.rows) throw std::runtime_error("sample_categorical: one uniform per position");
-        a.flags = NRL_FWD_SAMPLE;
+        a.flags |= NRL_FWD_SAMPLE;
         a.uniforms = uniforms->dev();
     }
     a.tokens = tok.dev();
@@ -443,6 +452,7 @@ inline IntTensor sample_categorical(const Tensor& logits, double temperature, co
     Tensor status = Tensor::empty(Shape{(size_t)r.rows}, DType::U8, z.device());
     nrl_row_fwd_args f;
     detail::fill_inputs(f, z, nullptr);
+    if (f.flags & NRL_FWD_MASK_BITS) throw std::runtime_error("sample_categorical with the reference's noise takes byte or additive masks, not bit-packed ones");
     nrl_gumbel_args a;
     std::memset(&a, 0, sizeof a);
     a.struct_size = sizeof a;
@@ -488,7 +498,7 @@ inline void forward(const Tensor& z, const Tensor* ref, const IntTensor* tokens,
             if (t < 0 || (uint64_t)t >= r.V) throw std::runtime_error("gather index out of range");
         s.tokens = Tensor::empty(Shape{(size_t)r.rows}, DType::I32, z.device());
         cu(cudaMemcpy(s.tokens.ptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice), "upload tokens");
-        a.flags = NRL_FWD_TOKENS_IN;
+        a.flags |= NRL_FWD_TOKENS_IN;
         a.tokens = s.tokens.dev();
         a.logp = logp->dev();
     }

@@ -521,6 +521,39 @@ static void test_group_advantages() {
     CHECK(throws([] { rl::group_advantages_tensor(Tensor::from_f32({1, 2}, {2, 1}, dev), rl::GroupNorm::Std(0.0, true)); }, "at least 2"), "tensor n = 1 unbiased");
 }
 
+// ---- bit-packed vocabulary masks: the same results as the byte mask, bit for bit --------------------
+static void test_bit_masks() {
+    const size_t S = 2, B = 3, T = 4, V = 200, rows = S * B * T, words = (V + 31) / 32;
+    std::vector<float> x(rows * V), u(rows);
+    std::vector<uint8_t> m(rows * V);
+    std::vector<int32_t> bits(rows * words, 0);
+    uint32_t st = 12345u;
+    auto rnd = [&]() { st = st * 1664525u + 1013904223u; return (float)(st >> 8) / 16777216.0f; };
+    for (size_t i = 0; i < x.size(); i++) { x[i] = 6.f * rnd() - 3.f; m[i] = rnd() < 0.3f ? 1 : 0; }
+    for (size_t r = 0; r < rows; r++) {
+        m[r * V + 7] = 1;
+        u[r] = rnd();
+        for (size_t v = 0; v < V; v++)
+            if (m[r * V + v]) bits[r * words + v / 32] |= (int32_t)(1u << (v % 32));
+    }
+    Tensor tx = Tensor::from_f32(x, {S, B, T, V}, dev).require_grad();
+    Tensor tm = Tensor::from_u8(m, {S, B, T, V}, dev);
+    Tensor tb = Tensor::empty({S, B, T, words}, noetic::DType::I32, dev);
+    noetic::cu(cudaMemcpy(tb.ptr(), bits.data(), bits.size() * 4, cudaMemcpyHostToDevice), "upload bits");
+    Tensor tu = Tensor::from_f32(u, {S, B, T}, dev);
+    IntTensor ta = rl::sample_categorical(tx, 1.0, &tm, &tu), tc = rl::sample_categorical(tx, 1.0, &tb, &tu);
+    CHECK(ta.data == tc.data, "bit mask: sampled tokens");
+    Tensor la = rl::token_log_probs(rl::tempered_logits(tx, 1.0, &tm), ta), lb = rl::token_log_probs(rl::tempered_logits(tx, 1.0, &tb), ta);
+    CHECK(la.to_vec() == lb.to_vec(), "bit mask: log-probs");
+    Tensor ea = rl::categorical_entropy(rl::tempered_logits(tx, 1.0, &tm), nullptr, rl::TokenReduction::TokenMean);
+    Tensor eb = rl::categorical_entropy(rl::tempered_logits(tx, 1.0, &tb), nullptr, rl::TokenReduction::TokenMean);
+    CHECK(ea.to_vec() == eb.to_vec(), "bit mask: entropy");
+    // entropy token-mean is [S]: weight every seed by 1
+    Tensor up = Tensor::from_f32({1.f, 1.f}, {S}, dev);
+    auto ga = backward(ea, up).grad(tx)->to_vec(), gb = backward(eb, up).grad(tx)->to_vec();
+    CHECK(ga == gb, "bit mask: d(logits)");
+}
+
 // ---- lane operations (src/tensor/tests/standard.rs:8-24, 101-109; checks.rs:103-114) -------------
 static void test_lane_ops() {
     const float inf = INFINITY, nan = NAN;
@@ -697,7 +730,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"sample_categorical (reference noise)", test_sample_categorical_reference},
-        {"group_advantages", test_group_advantages}, {"lane operations", test_lane_ops}, {"ppo step", test_ppo_step},
+        {"group_advantages", test_group_advantages}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {
