@@ -520,6 +520,9 @@ def run_ours(args):
     e2e = None
     if not args.no_e2e:
         e2e_rows = min(args.e2e_rows, rows)
+        from noetic_tensor_b200.hostpath import bind_host_thread_near
+
+        near = bind_host_thread_near(dev)  # the pinned buffers below land in the memory next to this rank's GPU
         hf = HostForward(V, torch.bfloat16, chunk_rows=512, device=dev)
         if mask is None:
             raise SystemExit("--variant unmasked is a profiling variant: run it with --no-e2e")
@@ -566,7 +569,7 @@ def run_ours(args):
         best_mapped = mapped_rate > packed_rate
         e2e = {"value": max(mapped_rate, packed_rate), "unit": "rows/s", "mode": "mapped" if best_mapped else "packed",
                "h2d_bytes_per_step": int(mapped_bytes if best_mapped else hf.h2d_bytes), "d2h_bytes_per_step": e2e_rows * d2h,
-               "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "matches_resident_path": e2e_ok and mapped_ok,
+               "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "host_cpus_near_gpu": (len(near) if near else None), "matches_resident_path": e2e_ok and mapped_ok,
                "mapped": {"value": mapped_rate, "h2d_bytes_per_step_estimate": int(mapped_bytes),
                           "note": "nrl_row_fwd is given the pinned host logits and reference themselves (mapped into the device's address space) and fetches only the vectors the mask allows "
                                   "over the host link; the byte mask, read whole, goes up by copies in 2048-row chunks one chunk ahead of the kernel; uniforms go up and per-row results come back by copies, all inside the timed region; "

@@ -22,6 +22,31 @@ import torch
 from . import capi, ops
 
 
+def bind_host_thread_near(device):
+    """Restricts the calling process to the CPUs next to `device` on the PCIe tree (the
+    `local_cpulist` the kernel publishes for the GPU's PCI function), so that host buffers it then
+    allocates and first touches land in the memory of that NUMA node: a kernel or a copy that reads
+    them does not cross the socket interconnect. Returns the CPU set, or None when the topology is
+    not visible (a container without /sys, a single-node host): nothing is changed then."""
+    try:
+        p = torch.cuda.get_device_properties(torch.device(device))
+        addr = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{addr}/local_cpulist") as fh:
+            text = fh.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            if part:
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed or allowed == os.sched_getaffinity(0):
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:
+        return None
+
+
 class HostForward:
     def __init__(self, V, dtype, *, chunk_rows=512, ref=True, mask=True, device="cuda:0", packed=True, live_fraction=0.25, threads=None):
         self.dev = torch.device(device)
