@@ -11,7 +11,10 @@ logits, the reference and the mask is read from HBM once (5 bytes per element). 
 seeded synthetic data; the batch (tens of GB) is far larger than L2, so nothing is flushed
 between steps. One rank per GPU, rows partitioned across ranks, no collective on the data path.
 
-Prints one JSON line (see DESIGN.md for the fields).
+Prints one JSON line on stdout: the metric (rows/s over all ranks, device-timed, inputs resident),
+`roofline` of the one kernel a step launches, `cpu_baseline` (the CPU oracle on a sample of the
+rows), `e2e` (the same metric from pinned host memory through the host path, copies included),
+`clocks` sampled while the timed region ran, and `extras` (backward, other configurations).
 """
 import argparse
 import json
