@@ -119,14 +119,15 @@ class HostForward:
         a.ref_logits = s["r"].data_ptr() if self.has_ref else 0
         capi.check(capi.lib().nrl_unpack_rows(C.byref(a), C.c_void_p(self.copy_stream.cuda_stream)), "nrl_unpack_rows")
 
-    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True, mask_bits=None):
+    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True, mask_bits=None, first_chunk_rows=None):
         """The same results as `run`, the kernel reading the pinned host logits (and reference) in
         place. With `mask_by_copy` the byte mask, which is read whole, goes up by copies in
         `chunk_rows`-row chunks one chunk ahead of the kernel (the copy engine moves it faster than
         loads over the link do); otherwise one launch reads everything in place. A caller that holds
         bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
         v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and the kernels read
-        the bits as they are (NRL_FWD_MASK_BITS)."""
+        the bits as they are (NRL_FWD_MASK_BITS). `first_chunk_rows` makes the first chunk smaller:
+        its mask copy is the one nothing overlaps."""
         if not self.has_mask:
             mask = mask_bits = None
         if mask is None and mask_bits is None:
@@ -153,8 +154,11 @@ class HostForward:
             if mask_bits is None and (getattr(self, "_mapped_masks", None) is None or self._mapped_masks[0].shape[0] < min(chunk_rows, rows)):
                 self._mapped_masks = [torch.empty(min(chunk_rows, rows), self.V, dtype=torch.uint8, device=self.dev) for _ in range(2)]
         results = []
-        for i, r0 in enumerate(range(0, rows, chunk_rows)):
-            r1 = min(rows, r0 + chunk_rows)
+        starts = list(range(0, rows, chunk_rows))
+        if by_copy and first_chunk_rows and first_chunk_rows < min(chunk_rows, rows):
+            starts = [0] + list(range(first_chunk_rows, rows, chunk_rows))
+        for i, r0 in enumerate(starts):
+            r1 = starts[i + 1] if i + 1 < len(starts) else rows
             m = mask[r0:r1] if mask is not None else None
             if by_copy:
                 ready, free = self._mapped_events[i % 2]

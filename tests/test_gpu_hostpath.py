@@ -160,6 +160,13 @@ def test_mapped_host_rows_equal_the_resident_forward(dtype, ref, rows):
     parts = [ops.row_forward(x[a:a + chunk], ref_logits=None if r is None else r[a:a + chunk], allow=m[a:a + chunk], uniforms=u[a:a + chunk]) for a in range(0, rows, chunk)]
     for name in ("tokens", "logp", "entropy") + (("kl",) if ref else ()):
         assert torch.equal(_bits(got[name]), _bits(torch.cat([getattr(f, name) for f in parts]).cpu())), name
+    # a smaller first chunk (its mask copy is the exposed one): the same launches, resident
+    first = max(8, chunk // 4)
+    got = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=chunk, first_chunk_rows=first)
+    cuts = [0] + list(range(first, rows, chunk)) + [rows]
+    parts = [ops.row_forward(x[a:b], ref_logits=None if r is None else r[a:b], allow=m[a:b], uniforms=u[a:b]) for a, b in zip(cuts[:-1], cuts[1:])]
+    for name in ("tokens", "logp", "entropy"):
+        assert torch.equal(_bits(got[name]), _bits(torch.cat([getattr(f, name) for f in parts]).cpu())), ("first chunk", name)
     with pytest.raises(ValueError, match="pinned"):
         ops.row_forward(x.cpu(), allow=pin(m), uniforms=u, device=dev)
 
