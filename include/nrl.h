@@ -401,6 +401,11 @@ int nrl_lane_op(const nrl_lane_args* args, nrl_stream stream);
  * (v mod 32) of its word v / 32, rows `bits_row_stride_words` words apart (0 = one row broadcast
  * to all). nrl_expand_bitmask writes the U8 allow-mask [rows, V] (0 / 1) that nrl_row_fwd and
  * nrl_row_bwd take: a host caller uploads V / 8 bytes per row instead of V. */
+/* The other direction, on `threads` host threads (no CUDA call): a host byte mask u8 [rows, V] to
+ * bit-packed words u32 [rows, ceil(V / 32)] in the layout above, for callers whose rows live in
+ * host memory: the mask then crosses the host link as V / 8 bytes per row. */
+int nrl_host_pack_bits(uint64_t rows, uint32_t V, const uint8_t* allow_mask, uint32_t* bits, uint32_t threads);
+
 int nrl_expand_bitmask(uint64_t rows, uint32_t V, nrl_devptr bits, uint64_t bits_row_stride_words, nrl_devptr allow_mask, nrl_stream stream);
 
 /* zero_masked (src/nn/rl.rs:99-102) of per-row values: out[i] = mask[i] == 0 ? 0 : x[i]. */

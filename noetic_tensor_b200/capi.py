@@ -111,6 +111,7 @@ SYMBOLS = {
     "nrl_group_advantages": (C.c_int, [u64, u32, u32, C.c_double, u32, ptr, ptr, C.c_void_p]),
     "nrl_lane_op": (C.c_int, [C.POINTER(LaneArgs), C.c_void_p]),
     "nrl_expand_bitmask": (C.c_int, [u64, u32, ptr, u64, ptr, C.c_void_p]),
+    "nrl_host_pack_bits": (C.c_int, [u64, u32, C.c_void_p, C.c_void_p, u32]),
     "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
     "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),

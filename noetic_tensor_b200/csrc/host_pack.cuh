@@ -9,6 +9,8 @@
 // With a grammar mask that allows ~5 % of a 128 256-token vocabulary this is 82 KB per row over
 // the link instead of 641 KB.
 #pragma once
+#include <emmintrin.h>
+
 #include <thread>
 #include <vector>
 
@@ -80,6 +82,44 @@ static int host_pack_impl(nrl_pack_args* a) {
     a->live_vectors = total;
     if (total > a->capacity) return NRL_E_WORKSPACE;
     run(true);
+    return NRL_OK;
+}
+
+// A byte mask to a bit mask on the host (bit v of a row = bit v mod 32 of its word v / 32): 16
+// mask bytes per SSE2 compare. What the bit-mask kernels (NRL_FWD_MASK_BITS) then read is an
+// eighth of the bytes, which is what counts when the mask has to cross the host link.
+static void pack_bits_range(const uint8_t* mask, uint32_t* bits, uint64_t r0, uint64_t r1, uint32_t V, uint32_t words) {
+    const __m128i zero = _mm_setzero_si128();
+    for (uint64_t r = r0; r < r1; r++) {
+        const uint8_t* m = mask + r * V;
+        uint32_t* out = bits + r * words;
+        const uint32_t full = V / 32;
+        for (uint32_t w = 0; w < full; w++) {
+            const __m128i a = _mm_loadu_si128((const __m128i*)(m + 32 * w));
+            const __m128i b = _mm_loadu_si128((const __m128i*)(m + 32 * w + 16));
+            const uint32_t za = (uint32_t)_mm_movemask_epi8(_mm_cmpeq_epi8(a, zero));
+            const uint32_t zb = (uint32_t)_mm_movemask_epi8(_mm_cmpeq_epi8(b, zero));
+            out[w] = ~(za | (zb << 16));
+        }
+        if (full < words) {
+            uint32_t x = 0;
+            for (uint32_t v = full * 32; v < V; v++) x |= (uint32_t)(m[v] != 0) << (v & 31u);
+            out[full] = x;
+        }
+    }
+}
+
+static int host_pack_bits_impl(uint64_t rows, uint32_t V, const uint8_t* mask, uint32_t* bits, uint32_t threads) {
+    const uint32_t words = (V + 31) / 32;
+    const uint32_t nt = threads < 1 ? 1 : (threads > 256 ? 256 : threads);
+    std::vector<std::thread> th;
+    const uint64_t per = (rows + nt - 1) / nt;
+    for (uint32_t t = 1; t < nt; t++) {
+        const uint64_t r0 = t * per < rows ? t * per : rows, r1 = (t + 1) * per < rows ? (t + 1) * per : rows;
+        if (r0 < r1) th.emplace_back([=] { pack_bits_range(mask, bits, r0, r1, V, words); });
+    }
+    pack_bits_range(mask, bits, 0, per < rows ? per : rows, V, words);
+    for (auto& x : th) x.join();
     return NRL_OK;
 }
 

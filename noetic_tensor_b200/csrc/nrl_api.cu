@@ -361,6 +361,11 @@ extern "C" int nrl_host_pack(nrl_pack_args* a) {
     return NRL_E_UNSUPPORTED;
 }
 
+extern "C" int nrl_host_pack_bits(uint64_t rows, uint32_t V, const uint8_t* allow_mask, uint32_t* bits, uint32_t threads) {
+    if (rows == 0 || V == 0 || !allow_mask || !bits) return NRL_E_BAD_ARG;
+    return host_pack_bits_impl(rows, V, allow_mask, bits, threads);
+}
+
 extern "C" int nrl_unpack_rows(const nrl_unpack_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_unpack_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->V % kVec != 0 || a->V > 262144u || a->rows > 0x7fffffffull) return NRL_E_BAD_ARG;

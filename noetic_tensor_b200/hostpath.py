@@ -119,7 +119,7 @@ class HostForward:
         a.ref_logits = s["r"].data_ptr() if self.has_ref else 0
         capi.check(capi.lib().nrl_unpack_rows(C.byref(a), C.c_void_p(self.copy_stream.cuda_stream)), "nrl_unpack_rows")
 
-    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True, mask_bits=None, first_chunk_rows=None):
+    def run_mapped(self, logits, uniforms, ref=None, mask=None, out=None, chunk_rows=2048, mask_by_copy=True, mask_bits=None, first_chunk_rows=None, pack_bits_on_host=False):
         """The same results as `run`, the kernel reading the pinned host logits (and reference) in
         place. With `mask_by_copy` the byte mask, which is read whole, goes up by copies in
         `chunk_rows`-row chunks one chunk ahead of the kernel (the copy engine moves it faster than
@@ -127,7 +127,9 @@ class HostForward:
         bit-packed masks passes `mask_bits` (pinned int32 [rows, ceil(V/32)], bit v of a row = bit
         v mod 32 of word v / 32) instead of `mask`: V/8 bytes per row go up and the kernels read
         the bits as they are (NRL_FWD_MASK_BITS). `first_chunk_rows` makes the first chunk smaller:
-        its mask copy is the one nothing overlaps."""
+        its mask copy is the one nothing overlaps. With `pack_bits_on_host` a BYTE mask is turned
+        into bits by host threads chunk by chunk (nrl_host_pack_bits, one chunk ahead of the kernel)
+        so that only V/8 mask bytes per row cross the link; the results are the byte mask's."""
         if not self.has_mask:
             mask = mask_bits = None
         if mask is None and mask_bits is None:
@@ -141,6 +143,15 @@ class HostForward:
         u = uniforms.to(self.dev, non_blocking=True)
         ref = ref if self.has_ref else None
         mask = mask if self.has_mask else None
+        host_pack = bool(pack_bits_on_host and mask is not None and mask_bits is None)
+        byte_mask = mask
+        if host_pack:  # bits are made per chunk below; `mask_bits` stands for "the kernels get bits"
+            words = (self.V + 31) // 32
+            n_stage = min(chunk_rows, rows)
+            if getattr(self, "_host_bits", None) is None or self._host_bits[0].shape[0] < n_stage:
+                self._host_bits = [torch.empty(n_stage, words, dtype=torch.int32).pin_memory() for _ in range(2)]
+                self._host_bits_copied = [torch.cuda.Event() for _ in range(2)]
+            mask_bits = self._host_bits[0]  # only its shape is used before the loop
         if mask_bits is not None:
             mask, mask_by_copy = mask_bits, True
             if getattr(self, "_mapped_bits", None) is None or self._mapped_bits[0].shape[0] < min(chunk_rows, rows):
@@ -165,7 +176,15 @@ class HostForward:
                 with torch.cuda.stream(self.copy_stream):
                     if i >= 2:
                         self.copy_stream.wait_event(free)  # the kernel that read this buffer has finished
-                    if mask_bits is not None:
+                    if host_pack:
+                        stage = self._host_bits[i % 2][: r1 - r0]
+                        if i >= 2:
+                            self._host_bits_copied[i % 2].synchronize()  # the copy out of this staging buffer is done
+                        capi.check(capi.lib().nrl_host_pack_bits(r1 - r0, self.V, byte_mask.data_ptr() + r0 * self.V, stage.data_ptr(), self.threads), "nrl_host_pack_bits")
+                        m, bits = None, self._mapped_bits[i % 2][: r1 - r0]
+                        bits.copy_(stage, non_blocking=True)
+                        self._host_bits_copied[i % 2].record(self.copy_stream)
+                    elif mask_bits is not None:
                         m, bits = None, self._mapped_bits[i % 2][: r1 - r0]
                         bits.copy_(mask_bits[r0:r1], non_blocking=True)
                     else:

@@ -160,6 +160,10 @@ def test_mapped_host_rows_equal_the_resident_forward(dtype, ref, rows):
     parts = [ops.row_forward(x[a:a + chunk], ref_logits=None if r is None else r[a:a + chunk], allow=m[a:a + chunk], uniforms=u[a:a + chunk]) for a in range(0, rows, chunk)]
     for name in ("tokens", "logp", "entropy") + (("kl",) if ref else ()):
         assert torch.equal(_bits(got[name]), _bits(torch.cat([getattr(f, name) for f in parts]).cpu())), name
+    # the byte mask packed into bits by host threads, chunk by chunk: the byte mask's results
+    got_hb = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=chunk, pack_bits_on_host=True)
+    for name in ("tokens", "logp", "entropy"):
+        assert torch.equal(_bits(got_hb[name]), _bits(got[name])), ("host-packed bits", name)
     # a smaller first chunk (its mask copy is the exposed one): the same launches, resident
     first = max(8, chunk // 4)
     got = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=chunk, first_chunk_rows=first)

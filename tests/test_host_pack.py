@@ -61,3 +61,18 @@ def test_pack_argument_checks():
     assert capi.lib().nrl_host_pack(C.byref(a)) == capi.E_BAD_ARG
     a.struct_size, a.rows, a.V = C.sizeof(a), 1, 12  # V not a multiple of 8
     assert capi.lib().nrl_host_pack(C.byref(a)) == capi.E_BAD_ARG
+
+
+@pytest.mark.parametrize("V", [1, 31, 32, 33, 100, 4104, 128256])
+def test_pack_bits_on_the_host(V):
+    """nrl_host_pack_bits: bit v of a row = bit v mod 32 of word v / 32, any non-zero byte allowed."""
+    g = np.random.default_rng(V)
+    rows = 5 if V > 10000 else 23
+    m = (g.uniform(0, 1, (rows, V)) < 0.3).astype(np.uint8) * g.integers(1, 255, (rows, V)).astype(np.uint8)
+    words = (V + 31) // 32
+    want = np.packbits(np.pad(m != 0, ((0, 0), (0, (-V) % 32))), axis=1, bitorder="little").view(np.uint32)
+    for threads in (1, 3, 16):
+        bits = np.full((rows, words), 0xFFFFFFFF, np.uint32)
+        rc = capi.lib().nrl_host_pack_bits(rows, V, m.ctypes.data_as(C.c_void_p), bits.ctypes.data_as(C.c_void_p), threads)
+        assert rc == 0 and np.array_equal(bits, want)
+    assert capi.lib().nrl_host_pack_bits(0, V, None, None, 1) == capi.E_BAD_ARG
