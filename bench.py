@@ -558,13 +558,13 @@ def run_ours(args):
         mapped_rate = world * e2e_rows / float(tm.item())
         mapped_ok = bool((mout["tokens"][:64] == out.tokens[:64].cpu()).all())
         # the same byte mask turned into bits by host threads inside the timed region: V/8 mask bytes per row cross the link
-        hf.run_mapped(hx, hu, ref=hr, mask=hm, first_chunk_rows=512, pack_bits_on_host=True)
+        hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=1184, first_chunk_rows=512, pack_bits_on_host=True)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            pout = hf.run_mapped(hx, hu, ref=hr, mask=hm, first_chunk_rows=512, pack_bits_on_host=True)
+            pout = hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=1184, first_chunk_rows=512, pack_bits_on_host=True)
         tp = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(tp, op=dist.ReduceOp.MAX)
@@ -593,7 +593,7 @@ def run_ours(args):
                                   "over the host link; the byte mask, read whole, goes up by copies in 2048-row chunks (the first one 512 rows) one chunk ahead of the kernel; uniforms go up and per-row results come back by copies, all inside the timed region; "
                                   "the byte count is an estimate (mask bytes + live vectors), the link has no counter here"},
                "mapped_host_bits": {"value": hostbits_rate, "h2d_bytes_per_step_estimate": int(hostbits_bytes), "host_threads": hf.threads, "same_tokens_as_mapped": hostbits_ok,
-                                    "note": "as `mapped`, but host threads turn each chunk's byte mask into one bit per token (nrl_host_pack_bits, inside the timed region, one chunk ahead of the kernel) "
+                                    "note": "as `mapped` with 1184-row chunks, but host threads turn each chunk's byte mask into one bit per token (nrl_host_pack_bits, inside the timed region, one chunk ahead of the kernel) "
                                             "and the kernels read the bits (NRL_FWD_MASK_BITS): the mask crosses the link as V/8 bytes per row; results are the byte mask's bit for bit"},
                "bit_packed_masks": {"value": bits_rate, "this_rank_only": True, "same_tokens": bits_ok, "h2d_bytes_per_step_estimate": int(mapped_bytes - e2e_rows * V + e2e_rows * (V // 8)),
                                     "note": "not the headline input format: the same rows from a caller that holds int32 bit masks [rows, V/32], which the kernels read as they are (NRL_FWD_MASK_BITS)"},
