@@ -62,7 +62,14 @@ def test_bit_masks_equal_byte_masks(rows, V, dtype, ref, tau, density):
         b = ops.row_forward(x, ref_logits=r, allow_bits=bits, temperature=tau, **kw)
         for name in ("tokens", "logp", "ref_logp", "kl", "entropy", "rowstats", "status"):
             same(getattr(a, name), getattr(b, name), (mode, name))
+    # given tokens (the log-prob of one element per row: the single-element mask read), allowed and excluded ones
     f = ops.row_forward(x, ref_logits=r, allow=m, temperature=tau, uniforms=u)
+    given = f.tokens.clone()
+    given[::3] = torch.randint(0, V, (given[::3].numel(),), generator=gen, device=dev, dtype=torch.int32)
+    a = ops.row_forward(x, ref_logits=r, allow=m, temperature=tau, tokens=given)
+    b = ops.row_forward(x, ref_logits=r, allow_bits=bits, temperature=tau, tokens=given)
+    for name in ("logp", "ref_logp", "kl", "entropy", "status"):
+        same(getattr(a, name), getattr(b, name), ("given tokens", name))
     score = (torch.rand(rows, generator=gen, device=dev) < 0.8).float()
     kw = dict(g_logp=score, g_ent=-0.01 * score, temperature=tau)
     if ref:
