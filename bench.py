@@ -38,9 +38,6 @@ FALLBACK_HBM_GBS = 6650.0
 # DRAM bytes per launch ÷ algorithmic bytes per launch, from the ncu capture summarised in
 # profiles/ (None until a capture exists for the current kernel).
 NCU_TRAFFIC_RATIO = 0.626  # profiles/row_fwd_grouped_bf16_ref_allow_4096rows.md: 1.6437 GB of DRAM traffic per 2.6267 GB algorithmic
-# Measured-peak read bandwidth of a pure streaming read kernel on this pool (for context only).
-
-
 
 def measured_peak():
     try:
@@ -122,6 +119,41 @@ def make_inputs(rows, seed, device):
     mask = synth.grammar_masks(rows, V, gen, device)
     u = synth.uniforms(rows, gen, device)
     return logits, ref, mask, u
+
+
+def necessary_bytes(mask, granule):
+    """Bytes a launch over these rows cannot avoid moving when memory is fetched in aligned granules
+    of `granule` bytes: the byte mask whole, plus every granule of the bf16 logits and of the bf16
+    reference that holds at least one allowed token. Counted on the device, outside the timing."""
+    rows, v = mask.shape
+    elems = granule // 2
+    live = 0
+    for r0 in range(0, rows, 4096):
+        m = mask[r0:r0 + 4096]
+        live += int(m.view(m.shape[0], v // elems, elems).ne(0).any(dim=2).sum().item())
+    return rows * v + 2 * live * granule
+
+
+def close(a, b):
+    """1e-5 relative or 1e-6 absolute, the path's tolerance; NaN equals NaN."""
+    import torch
+
+    a, b = a.double().cpu(), b.double().cpu()
+    d = (a - b).abs()
+    ok = (d <= 1e-6) | (d <= 1e-5 * b.abs()) | (a == b) | (torch.isnan(a) & torch.isnan(b))
+    return int((~ok).sum().item())
+
+
+def compare_with_resident(host_out, res, n):
+    """Every row of a host path's results against the resident launch's: tokens that differ (the two
+    run different decompositions of a row when the chunk sizes differ, so a uniform on a CDF step
+    may fall either way), and log-prob / KL / entropy outside the tolerance on rows with the same token."""
+    import torch
+
+    tok_h, tok_r = host_out["tokens"][:n], res.tokens[:n].cpu()
+    same = tok_h == tok_r
+    bad = close(host_out["logp"][:n][same], res.logp[:n].cpu()[same]) + close(host_out["kl"][:n], res.kl[:n]) + close(host_out["entropy"][:n], res.entropy[:n])
+    return {"rows": n, "tokens_differing": int((~same).sum().item()), "values_outside_tolerance": bad}
 
 
 def cpu_reference_rows(logits_bits, ref_bits, allow, root, fast, threads):
@@ -511,13 +543,79 @@ def run_ours(args):
     launch_ms = ms / args.steps
     achieved = alg_bytes / (launch_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind + " copy bandwidth",
-                "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_bwd_kernel<bf16, ref, allow>" if args.variant == "backward" else "nrl_bits::row_fwd_grouped<bf16, ref, allow>" if args.variant == "bitmask" else "row_fwd_grouped<bf16, ref, allow>" if mask is not None else "row_fwd_fused<bf16, ref>", "algorithmic_bytes_per_launch": alg_bytes,
+                "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "row_bwd_kernel<bf16, ref, allow>" if args.variant == "backward" else "nrl_bits::row_fwd_grouped<bf16, ref, allow>" if args.variant == "bitmask" else "row_fwd_grouped<bf16, ref, allow>" if mask is not None else "row_fwd_grouped<bf16, ref, no mask>", "algorithmic_bytes_per_launch": alg_bytes,
                 "traffic": None if args.variant in ("backward", "bitmask") else (NCU_TRAFFIC_RATIO if mask is not None else 1.0) * alg_bytes,
                 "note": "algorithmic bytes count every logit, reference and mask byte once (5 B per element); the kernel does not read logits the mask "
                         "excludes, so its DRAM traffic (`traffic`, from ncu) is below the algorithmic bytes and `frac` can exceed 1"}
     if roofline["traffic"]:
         roofline["dram_GBps"] = roofline["traffic"] / (launch_ms * 1e-3) / 1e9
         roofline["dram_frac"] = roofline["dram_GBps"] / peak
+    if mask is not None and args.variant == "headline":
+        # What the masks make necessary: a launch cannot move less than the mask plus the aligned granules of
+        # logits and reference that hold an allowed token. `frac` is stated on the 32-byte sector (the unit
+        # the memory system addresses); the coarser granules are given beside it.
+        nec = {g: necessary_bytes(mask, g) for g in (32, 64, 128)}
+        roofline["frac_algorithmic"] = roofline["frac"]
+        roofline["necessary_bytes_per_launch"] = nec[32]
+        roofline["necessary_bytes_per_launch_64B_granules"] = nec[64]
+        roofline["necessary_bytes_per_launch_128B_granules"] = nec[128]
+        roofline["necessary_bytes_per_row"] = nec[32] / rows
+        roofline["achieved_necessary"] = nec[32] / (launch_ms * 1e-3) / 1e9
+        roofline["frac"] = roofline["achieved_necessary"] / peak
+        roofline["note"] = ("`frac` = necessary bytes ÷ launch time ÷ peak, the necessary bytes being the byte mask whole plus every aligned 32-byte sector of logits and of "
+                            "reference that holds an allowed token (counted on the device from the masks of this run); `achieved` / `frac_algorithmic` count every logit, reference "
+                            "and mask byte once (5 B per element) although the kernel never reads logits the mask excludes; `traffic` is the DRAM traffic ncu measured on a smaller "
+                            "capture scaled by rows")
+
+    # Strong scaling (the partition the path is meant for): ONE config-3 batch split along S, then B, over the
+    # ranks, no collective on the data path; and the TokenReduction that spans ranks, run over NCCL and held to
+    # the bits of the one-GPU kernel.
+    strong = None
+    if args.variant == "headline" and not args.no_strong and rows % T == 0:
+        from noetic_tensor_b200 import shard
+
+        S_j, B_j = (rows // ROWS_PER_SEED, B) if rows % ROWS_PER_SEED == 0 else (1, rows // T)
+        r0, r1 = shard.row_range(S_j, B_j, T, rank, world)
+        lg, rf, mk, uu = logits[r0:r1], ref[r0:r1], mask[r0:r1], u[r0:r1]
+
+        def sstep():
+            return ops.row_forward(lg, ref_logits=rf, allow=mk, uniforms=uu)
+
+        for _ in range(3):
+            so = sstep()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(args.steps):
+            so = sstep()
+        s1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        tmax = torch.tensor([s0.elapsed_time(s1) / args.steps], device=dev, dtype=torch.float64)
+        tmin = tmax.clone()
+        if world > 1:
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            dist.all_reduce(tmin, op=dist.ReduceOp.MIN)
+        per_local = so.logp.reshape(-1, T).contiguous()
+        full = shard.gather_sequences(per_local, S_j, B_j).reshape(S_j, B_j, T).contiguous()
+        bitwise = True
+        for red in (capi.REDUCE_SUM, capi.REDUCE_TOKEN_MEAN, capi.REDUCE_PER_SEQUENCE, capi.REDUCE_SEQUENCE_MEAN):
+            sharded = shard.ShardedReduction(per_local, None, red, S_j, B_j).value
+            whole = ops.reduce_tokens(full, None, red)
+            bitwise = bitwise and bool(torch.equal(sharded.view(torch.int32), whole.view(torch.int32)))
+        flag = torch.tensor([1 if bitwise else 0], device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        total_rows = S_j * B_j * T
+        strong = {"scaling": "strong", "rows_total_per_step": total_rows, "rows_this_rank": r1 - r0, "ms_per_step": float(tmax.item()), "ms_per_step_fastest_rank": float(tmin.item()),
+                  "value": total_rows / (float(tmax.item()) * 1e-3), "unit": "rows/s", "sharded_reduce_bitwise": bool(flag.item()),
+                  "note": f"one config-3 batch of {S_j} seed(s) split along S then B over {world} rank(s) (shard.row_range), each rank one launch over its rows, max over ranks; "
+                          "no collective on the data path. The cross-rank TokenReduction (nrl_reduce_tokens_partial -> all_gather of two floats per sequence over NCCL -> "
+                          "nrl_reduce_tokens_fold) is compared, outside the timed region, with nrl_reduce_tokens on the gathered per-token values: same bits for Sum, TokenMean, "
+                          "PerSequence, SequenceMean"}
 
     # end to end from host memory: pinned inputs cross PCIe every step, results come back
     e2e = None
@@ -542,7 +640,7 @@ def run_ours(args):
         te = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
         if world > 1:
             dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e_ok = bool((hout["tokens"][:64] == out.tokens[:64].cpu()).all())
+        cmp_packed = compare_with_resident(hout, out, e2e_rows)
         packed_rate = world * e2e_rows / float(te.item())
         # the same rows read in place: pinned host memory is mapped into the device's address space
         hf.run_mapped(hx, hu, ref=hr, mask=hm, first_chunk_rows=512)
@@ -556,7 +654,7 @@ def run_ours(args):
         if world > 1:
             dist.all_reduce(tm, op=dist.ReduceOp.MAX)
         mapped_rate = world * e2e_rows / float(tm.item())
-        mapped_ok = bool((mout["tokens"][:64] == out.tokens[:64].cpu()).all())
+        cmp_mapped = compare_with_resident(mout, out, e2e_rows)
         # the same byte mask turned into bits by host threads inside the timed region: V/8 mask bytes per row cross the link
         hf.run_mapped(hx, hu, ref=hr, mask=hm, chunk_rows=1184, first_chunk_rows=512, pack_bits_on_host=True)
         if world > 1:
@@ -570,6 +668,7 @@ def run_ours(args):
             dist.all_reduce(tp, op=dist.ReduceOp.MAX)
         hostbits_rate = world * e2e_rows / float(tp.item())
         hostbits_ok = bool((pout["tokens"] == mout["tokens"]).all())
+        cmp_hostbits = compare_with_resident(pout, out, e2e_rows)
         # a caller that holds bit-packed masks (what grammar engines emit): V/8 mask bytes per row go up
         import numpy as np
         hbits = torch.from_numpy(np.packbits(hm.numpy(), axis=1, bitorder="little").view(np.int32)).pin_memory()
@@ -580,6 +679,9 @@ def run_ours(args):
             bout = hf.run_mapped(hx, hu, ref=hr, mask_bits=hbits, first_chunk_rows=512)
         bits_rate = e2e_rows / ((time.perf_counter() - t0) / e2e_steps)
         bits_ok = bool((bout["tokens"] == mout["tokens"]).all())
+        cmp_bits = compare_with_resident(bout, out, e2e_rows)
+        all_cmp = {"packed": cmp_packed, "mapped": cmp_mapped, "mapped_host_bits": cmp_hostbits, "bit_packed_masks": cmp_bits}
+        e2e_matches = all(c["values_outside_tolerance"] == 0 and c["tokens_differing"] <= max(1, e2e_rows // 1000) for c in all_cmp.values())
         h2d, d2h = hf.bytes_per_row()
         mapped_bytes = e2e_rows * (V + 4) + hf.live_vectors * 8 * 2 * 2  # the mask whole and the uniforms + the live vectors of bf16 logits and reference
         hostbits_bytes = mapped_bytes - e2e_rows * V + e2e_rows * (V // 8)
@@ -587,7 +689,8 @@ def run_ours(args):
         best = max(modes, key=lambda k: modes[k][0])
         e2e = {"value": modes[best][0], "unit": "rows/s", "mode": best,
                "h2d_bytes_per_step": int(modes[best][1]), "d2h_bytes_per_step": e2e_rows * d2h,
-               "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "host_cpus_near_gpu": (len(near) if near else None), "matches_resident_path": e2e_ok and mapped_ok and hostbits_ok,
+               "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "host_cpus_near_gpu": (len(near) if near else None), "matches_resident_path": e2e_matches, "vs_resident_path": all_cmp,
+               "h2d_bytes_note": "for the mapped modes an estimate: the mask bytes that are copied plus 16 B per live vector per stream; the link moves at least a 32-byte sector per isolated vector and has no counter here",
                "mapped": {"value": mapped_rate, "h2d_bytes_per_step_estimate": int(mapped_bytes),
                           "note": "nrl_row_fwd is given the pinned host logits and reference themselves (mapped into the device's address space) and fetches only the vectors the mask allows "
                                   "over the host link; the byte mask, read whole, goes up by copies in 2048-row chunks (the first one 512 rows) one chunk ahead of the kernel; uniforms go up and per-row results come back by copies, all inside the timed region; "
@@ -627,7 +730,13 @@ def run_ours(args):
                        "storage": "bf16 logits, f32 arithmetic", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
                        "rows_per_gpu_per_step": rows, "cache": "inputs (tens of GB) far larger than the 126 MB L2; no flush needed", "partition": f"rows split across {world} rank(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "bitwise_reproducible": reproducible, "refused_rows": bad, "extras": extras,
+            "bitwise_reproducible": reproducible, "refused_rows": bad, "strong_scaling": strong,
+            "samplers": {"ours": "inverse CDF against one caller-supplied uniform per row, fused into the forward (what the path is defined on)",
+                         "reference_arm": "the reference's Gumbel-max (one ChaCha20 u64 and two f64 logarithms per logit) on the host cores",
+                         "same_algorithm_on_device": None if not extras else {"rows_per_s": extras["reference_gumbel_sampler"]["rows_per_s"],
+                                                                              "vs_cpu_baseline_1_core": (extras["reference_gumbel_sampler"]["rows_per_s"] / cpu_baseline["value"]) if cpu_baseline else None,
+                                                                              "what": "nrl_sample_gumbel: the reference's own sampler, token for token, on the device (extras.reference_gumbel_sampler)"}},
+            "extras": extras,
         }
         sys.stdout.flush()
         os.dup2(json_fd, 1)
@@ -649,6 +758,7 @@ def main():
                     help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; bitmask: the mask bit-packed; none of them is the headline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling measurement and the cross-rank TokenReduction check")
     ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":

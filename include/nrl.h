@@ -22,8 +22,9 @@
  *     (src/tensor/gpu/mod.rs:39-40); every floating-point output is F32
  *     (src/tensor/gpu/mod.rs:335-342).
  *
- * Everything is computed in f32 with f64 only in per-row finalisation; no atomics and a fixed
- * reduction order, so results are bitwise identical from run to run on the same device.
+ * Everything is computed in f32 with f64 only in per-row finalisation; no atomics in any
+ * reduction (one shared-memory ticket counter hands out work, which does not touch results) and a
+ * fixed reduction order, so results are bitwise identical from run to run on the same device.
  */
 #ifndef NRL_H
 #define NRL_H
@@ -47,7 +48,8 @@ enum {
     NRL_E_UNSUPPORTED = -2, /* dtype / option this build has no kernel for */
     NRL_E_WORKSPACE = -3,   /* scratch buffer missing or too small */
     NRL_E_ROW_STATUS = -4,  /* reported by nrl_check_status: a row had no allowed token or a NaN */
-    NRL_E_NO_DEVICE = -5    /* no CUDA device / no current context */
+    NRL_E_NO_DEVICE = -5,   /* no CUDA device / no current context */
+    NRL_E_NOT_FINITE = -6   /* reported by nrl_check_scored_finite: a scored log-probability is -inf, +inf or NaN */
 };
 
 /* ---------------------------------------------------------------------------------------------
@@ -85,10 +87,15 @@ enum {
     NRL_FWD_SAMPLE = 1u << 0,  /* draw tokens (needs `uniforms`, writes `tokens`) */
     NRL_FWD_GREEDY = 1u << 1,  /* tokens = first maximum of z (temperature 0); writes `tokens` */
     NRL_FWD_TOKENS_IN = 1u << 2, /* `tokens` is an input (token_log_probs of given tokens) */
-    NRL_FWD_MASK_BITS = 1u << 3  /* `allow_mask` is bit-packed (no counterpart in the reference, whose masks are a byte or an
+    NRL_FWD_MASK_BITS = 1u << 3, /* `allow_mask` is bit-packed (no counterpart in the reference, whose masks are a byte or an
                                     f32 per token): u32 words, bit v of a row = bit (v mod 32) of its word v / 32, and
                                     `allow_row_stride` counts WORDS between rows (>= ceil(V / 32), or 0 for one row
                                     broadcast). The kernels read V / 8 mask bytes per row instead of V */
+    NRL_FWD_ROW_PER_BLOCK = 1u << 4 /* always take the kernel that gives every row a thread block of its own, also for the
+                                    many-row shapes that otherwise run the kernel in which a block owns a group of rows.
+                                    The two split a row into parts differently, so results agree to rounding, not to the
+                                    bit; each is reproducible run to run. For comparisons and for callers that must get
+                                    the same bits whatever the number of rows in the call */
 };
 
 typedef struct nrl_row_fwd_args {
@@ -241,6 +248,25 @@ enum { NRL_REDUCE_NONE = 0, NRL_REDUCE_SUM = 1, NRL_REDUCE_TOKEN_MEAN = 2, NRL_R
 
 int nrl_reduce_tokens(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr out, nrl_stream stream);
 int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr mask, nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream);
+
+/* The same reductions when the sequences of one job live on several GPUs (one process per device,
+ * src/tensor/cuda/backend.rs:106-138; the seed axis is partitioned, then B). The reduction has two
+ * fixed steps: one warp sums a sequence to the pair (sum of per, sum of mask); a seed's pairs are
+ * folded in sequence order in f64 (reduce_tokens and per_sequence, src/nn/rl.rs:69-92).
+ * nrl_reduce_tokens runs both; a sharded caller runs step 1 on the sequences it holds
+ * (nrl_reduce_tokens_partial: `per`, `mask` f32 [n_seq, T] -> `pairs` f32 [n_seq, 2]), gathers the
+ * pairs of all S*B sequences in sequence order (a few bytes per sequence: the one collective of
+ * the path) and runs step 2 (nrl_reduce_tokens_fold: `pairs` f32 [S*B, 2] -> out [S] or [S, B]).
+ * The result has the bits of nrl_reduce_tokens on one GPU, for any number of GPUs.
+ * nrl_reduce_tokens_bwd_pairs is the backward for such a caller: it holds sequences
+ * [seq_begin, seq_begin + n_seq) of the S*B (flat index s*B + b); `pairs` are the gathered pairs of
+ * all sequences (their counts give the divisors), `mask` and `d_per` cover the local sequences
+ * [n_seq, T], `g_out` is the gradient of the whole reduced value ([S] or [S, B]; for
+ * NRL_REDUCE_NONE the local [n_seq, T], and `pairs` may be 0). */
+int nrl_reduce_tokens_partial(uint64_t n_seq, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr pairs, nrl_stream stream);
+int nrl_reduce_tokens_fold(uint32_t reduction, uint64_t S, uint64_t B, nrl_devptr pairs, nrl_devptr out, nrl_stream stream);
+int nrl_reduce_tokens_bwd_pairs(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, uint64_t seq_begin, uint64_t n_seq, nrl_devptr pairs, nrl_devptr mask,
+                                nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream);
 
 /* ---------------------------------------------------------------------------------------------
  * The cross-entropy family of nn::loss over the same row kernels (src/nn/loss.rs:10-79):
@@ -423,6 +449,19 @@ int nrl_group_advantages(uint64_t groups, uint32_t n, uint32_t norm_std, double 
  * *first_bad_row if any byte is non-zero. Synchronises the stream: this is the host read the
  * reference's sampler does (src/nn/rl.rs:516-519). */
 int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64_t* first_bad_row, uint32_t* bits);
+
+/* check_scored_finite (src/nn/rl.rs:204-211), the check the reference's losses run in debug
+ * builds (debug_check, :213-221, called from policy_gradient_loss :230, clipped_policy_loss
+ * :268-269 and kl_estimate :386-387): every scored log-probability is finite. `logp` is f32 [n]
+ * (n = S·B·T), `mask` the f32 scoring mask [n] or 0 (every position scored). One small kernel finds
+ * the first flat position with mask != 0 whose value is not finite and leaves (position, value bits)
+ * in `result`, 16 bytes of device memory of the caller's, 8-byte aligned; the call then reads
+ * them back and synchronises the stream (the reference's check is a host read too). Returns NRL_OK
+ * when there is none, else NRL_E_NOT_FINITE with *first_position and *value set; the wrapper
+ * formats the reference's message "{what}: the scored log-probability at flat position {i} is
+ * {value} (not finite)". A -inf there is a scored token the distribution excludes (a sampling
+ * mask that was not applied to the training logits, or a token from elsewhere). */
+int nrl_check_scored_finite(nrl_devptr logp, nrl_devptr mask, uint64_t n, nrl_devptr result, nrl_stream stream, uint64_t* first_position, float* value);
 
 #ifdef __cplusplus
 }

@@ -12,10 +12,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libnrl.so")
 
 F32, BF16 = 0, 1
-FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN, FWD_MASK_BITS = 1, 2, 4, 8
+FWD_SAMPLE, FWD_GREEDY, FWD_TOKENS_IN, FWD_MASK_BITS, FWD_ROW_PER_BLOCK = 1, 2, 4, 8, 16
 LOSS_PG, LOSS_PPO, LOSS_K1, LOSS_K2, LOSS_K3 = range(5)
 REDUCE_NONE, REDUCE_SUM, REDUCE_TOKEN_MEAN, REDUCE_PER_SEQUENCE, REDUCE_SEQUENCE_MEAN = range(5)
-E_BAD_ARG, E_UNSUPPORTED, E_WORKSPACE, E_ROW_STATUS, E_NO_DEVICE = -1, -2, -3, -4, -5
+E_BAD_ARG, E_UNSUPPORTED, E_WORKSPACE, E_ROW_STATUS, E_NO_DEVICE, E_NOT_FINITE = -1, -2, -3, -4, -5, -6
 STATIC_SCRATCH_BYTES = 64 * 1024
 
 u32, u64, f32, f64, ptr = C.c_uint32, C.c_uint64, C.c_float, C.c_double, C.c_uint64
@@ -104,6 +104,9 @@ SYMBOLS = {
     "nrl_clip_fraction": (C.c_int, [C.POINTER(TokenLossArgs), ptr, C.c_void_p]),
     "nrl_reduce_tokens": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_reduce_tokens_bwd": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_reduce_tokens_partial": (C.c_int, [u64, u64, ptr, ptr, ptr, C.c_void_p]),
+    "nrl_reduce_tokens_fold": (C.c_int, [u32, u64, u64, ptr, ptr, C.c_void_p]),
+    "nrl_reduce_tokens_bwd_pairs": (C.c_int, [u32, u64, u64, u64, u64, u64, ptr, ptr, ptr, ptr, C.c_void_p]),
     "nrl_mask_rows": (C.c_int, [u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_row_sum": (C.c_int, [u32, u64, u32, ptr, ptr, C.c_void_p]),
     "nrl_ce_tokens": (C.c_int, [C.POINTER(CeArgs), C.c_void_p]),
@@ -115,6 +118,7 @@ SYMBOLS = {
     "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
     "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
+    "nrl_check_scored_finite": (C.c_int, [ptr, ptr, u64, ptr, C.c_void_p, C.POINTER(u64), C.POINTER(f32)]),
 }
 
 _lib = None

@@ -35,7 +35,7 @@ extern "C" int nrl_version(void) { return 100; }
 
 extern "C" const char* nrl_key(void) {
     // what results depend on: the target, the arithmetic options, the kernel sources
-    return "cuda-sm100a-nvcc" NRL_STR(__CUDACC_VER_MAJOR__) "." NRL_STR(__CUDACC_VER_MINOR__) "-nofastmath-ex2approx-nrl-" NRL_SRC_HASH;
+    return "cuda-sm100a-nvcc" NRL_STR(__CUDACC_VER_MAJOR__) "." NRL_STR(__CUDACC_VER_MINOR__) "-fmadon-ex2approxftz-nrl-" NRL_SRC_HASH;
 }
 
 extern "C" uint64_t nrl_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -48,6 +48,7 @@ extern "C" const char* nrl_error_string(int code) {
         case NRL_E_WORKSPACE: return "nrl: scratch buffer missing or too small (for nrl_row_fwd_static: the shape needs more than the fixed NRL_STATIC_SCRATCH_BYTES)";
         case NRL_E_ROW_STATUS: return "nrl: a row has no allowed token (every logit -inf) or a NaN";
         case NRL_E_NO_DEVICE: return "nrl: no CUDA device or no current context";
+        case NRL_E_NOT_FINITE: return "nrl: a scored log-probability is not finite";
         default: return code > 0 ? cudaGetErrorString((cudaError_t)code) : "nrl: unknown error";
     }
 }
@@ -170,6 +171,7 @@ extern "C" int nrl_clip_fraction(const nrl_token_loss_args* a, nrl_devptr out, n
     int rc = fill_tok(p, a);
     if (rc) return rc;
     if (a->kind != NRL_LOSS_PPO || !out) return NRL_E_BAD_ARG;
+    if (a->S > 0x7fffffffull) return NRL_E_UNSUPPORTED;
     clip_fraction_kernel<<<(unsigned)a->S, kRedThreads, 0, (cudaStream_t)stream>>>(p, a->B * a->T, (float*)out);
     return after_launch();
 }
@@ -180,18 +182,50 @@ extern "C" int nrl_reduce_tokens(uint32_t reduction, uint64_t S, uint64_t B, uin
         if (per == out) return NRL_OK;
         return cuda_rc(cudaMemcpyAsync((void*)out, (const void*)per, S * B * T * sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
     }
-    reduce_tokens_kernel<<<(unsigned)S, kRedThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)per, (const float*)mask, (float*)out);
+    if (S > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    reduce_tokens_kernel<<<(unsigned)S, kFoldThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)per, (const float*)mask, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_reduce_tokens_partial(uint64_t n_seq, uint64_t T, nrl_devptr per, nrl_devptr mask, nrl_devptr pairs, nrl_stream stream) {
+    if (n_seq == 0 || T == 0 || !per || !pairs || (pairs & 7u) || ((per | mask) & 3u)) return NRL_E_BAD_ARG;
+    const uint64_t blocks = (n_seq + 7) / 8;
+    if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    seq_pairs_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(n_seq, T, (const float*)per, (const float*)mask, (float2*)pairs);
+    return after_launch();
+}
+
+extern "C" int nrl_reduce_tokens_fold(uint32_t reduction, uint64_t S, uint64_t B, nrl_devptr pairs, nrl_devptr out, nrl_stream stream) {
+    if (S == 0 || B == 0 || !pairs || !out || (pairs & 7u) || (out & 3u)) return NRL_E_BAD_ARG;
+    if (reduction == NRL_REDUCE_NONE || reduction > NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_BAD_ARG;
+    const uint64_t n = reduction == NRL_REDUCE_PER_SEQUENCE ? S * B : S;
+    const uint64_t blocks = (n + 127) / 128;
+    if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    fold_pairs_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(reduction, S, B, (const float2*)pairs, (float*)out);
+    return after_launch();
+}
+
+extern "C" int nrl_reduce_tokens_bwd_pairs(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, uint64_t seq_begin, uint64_t n_seq, nrl_devptr pairs, nrl_devptr mask,
+                                           nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream) {
+    if (S == 0 || B == 0 || T == 0 || n_seq == 0 || !g_out || !d_per || reduction > NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_BAD_ARG;
+    if (seq_begin + n_seq > S * B || (reduction != NRL_REDUCE_NONE && (!pairs || (pairs & 7u)))) return NRL_E_BAD_ARG;
+    const uint64_t blocks = (n_seq + 7) / 8;
+    if (blocks > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    reduce_tokens_bwd_pairs_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(reduction, B, T, seq_begin, n_seq, (const float2*)pairs, (const float*)mask, (const float*)g_out,
+                                                                                  (float*)d_per);
     return after_launch();
 }
 
 extern "C" int nrl_reduce_tokens_bwd(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, nrl_devptr mask, nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream) {
     if (S == 0 || B == 0 || T == 0 || !g_out || !d_per || reduction > NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_BAD_ARG;
-    reduce_tokens_bwd_kernel<<<(unsigned)S, kRedThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)mask, (const float*)g_out, (float*)d_per);
+    if (S > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    reduce_tokens_bwd_kernel<<<(unsigned)S, kFoldThreads, 0, (cudaStream_t)stream>>>(reduction, B, T, (const float*)mask, (const float*)g_out, (float*)d_per);
     return after_launch();
 }
 
 extern "C" int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devptr out, nrl_stream stream) {
     if (n == 0 || !x || !out) return NRL_E_BAD_ARG;
+    if ((n + 255) / 256 > 0x7fffffffull) return NRL_E_UNSUPPORTED;
     mask_rows_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(n, (const float*)x, (const float*)mask, (float*)out);
     return after_launch();
 }
@@ -199,6 +233,7 @@ extern "C" int nrl_mask_rows(uint64_t n, nrl_devptr x, nrl_devptr mask, nrl_devp
 extern "C" int nrl_group_advantages(uint64_t groups, uint32_t n, uint32_t norm_std, double eps, uint32_t unbiased, nrl_devptr rewards, nrl_devptr out, nrl_stream stream) {
     if (groups == 0 || n == 0 || !rewards || !out || ((rewards | out) & 3u)) return NRL_E_BAD_ARG;
     if (norm_std && (!(eps >= 0.0) || (unbiased && n < 2))) return NRL_E_BAD_ARG;
+    if ((groups + 127) / 128 > 0x7fffffffull) return NRL_E_UNSUPPORTED;
     group_advantages_kernel<<<(unsigned)((groups + 127) / 128), 128, 0, (cudaStream_t)stream>>>(groups, n, norm_std != 0, eps, unbiased != 0, (const float*)rewards, (float*)out);
     return after_launch();
 }
@@ -396,20 +431,38 @@ extern "C" int nrl_expand_bitmask(uint64_t rows, uint32_t V, nrl_devptr bits, ui
 
 extern "C" int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64_t* first_bad_row, uint32_t* bits) {
     if (!status || rows == 0) return NRL_E_BAD_ARG;
-    uint8_t* host = (uint8_t*)malloc(rows);
-    if (!host) return NRL_E_BAD_ARG;
-    cudaError_t e = cudaMemcpyAsync(host, (const void*)status, rows, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
-    int rc = cuda_rc(e);
-    if (!rc) {
-        for (uint64_t i = 0; i < rows; i++)
+    // read back in pieces of a fixed size: no host allocation that could fail
+    static const uint64_t kPiece = 1u << 15;
+    uint8_t host[kPiece];
+    for (uint64_t r0 = 0; r0 < rows; r0 += kPiece) {
+        const uint64_t n = rows - r0 < kPiece ? rows - r0 : kPiece;
+        cudaError_t e = cudaMemcpyAsync(host, (const void*)(status + r0), n, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+        if (e != cudaSuccess) return (int)e;
+        for (uint64_t i = 0; i < n; i++)
             if (host[i]) {
-                if (first_bad_row) *first_bad_row = i;
+                if (first_bad_row) *first_bad_row = r0 + i;
                 if (bits) *bits = host[i];
-                rc = NRL_E_ROW_STATUS;
-                break;
+                return NRL_E_ROW_STATUS;
             }
     }
-    free(host);
-    return rc;
+    return NRL_OK;
+}
+
+extern "C" int nrl_check_scored_finite(nrl_devptr logp, nrl_devptr mask, uint64_t n, nrl_devptr result, nrl_stream stream, uint64_t* first_position, float* value) {
+    if (!logp || n == 0 || !result || (result & 7u) || ((logp | mask) & 3u)) return NRL_E_BAD_ARG;
+    first_nonfinite_kernel<<<1, kScanThreads, 0, (cudaStream_t)stream>>>(n, (const float*)logp, (const float*)mask, (uint64_t*)result);
+    int rc = after_launch();
+    if (rc) return rc;
+    uint64_t host[2] = {~0ull, 0ull};
+    cudaError_t e = cudaMemcpyAsync(host, (const void*)result, sizeof host, cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    if (e != cudaSuccess) return (int)e;
+    if (host[0] == ~0ull) return NRL_OK;
+    if (first_position) *first_position = host[0];
+    if (value) {
+        const uint32_t b = (uint32_t)host[1];
+        memcpy(value, &b, sizeof b);
+    }
+    return NRL_E_NOT_FINITE;
 }

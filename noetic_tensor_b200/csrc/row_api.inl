@@ -18,13 +18,6 @@ static uint32_t fwd_nsplit(uint64_t rows, uint32_t V) {
     return (uint32_t)(need < max_split ? need : max_split);
 }
 
-// NRL_GROUPED=0 in the environment turns the grouped kernel off (for comparisons; read per call so
-// that a test can switch between the two kernels).
-static bool grouped_enabled() {
-    const char* e = getenv("NRL_GROUPED");
-    return !(e && e[0] == '0');
-}
-
 template <int DT, bool REF, bool ALLOW, bool GENERAL, bool VEC>
 static int launch_fwd(const FwdParams& p, cudaStream_t st) {
     if (p.nsplit == 1) {
@@ -35,7 +28,7 @@ static int launch_fwd(const FwdParams& p, cudaStream_t st) {
             q.nsplit = kGroupSplit;
             q.tiles_per_block = (p.tiles_per_block + q.nsplit - 1) / q.nsplit;
             const uint32_t part_vectors = (q.tiles_per_block + q.parts_per_block - 1) / q.parts_per_block * (kTile / kVec);
-            if (grouped_enabled() && !(p.flags & NRL_FWD_GREEDY) && p.rows >= 2ull * 148 * group_rows<ALLOW>() && part_vectors < 0xffffu && q.tiles_per_block >= 16) {
+            if (!(p.flags & (NRL_FWD_GREEDY | NRL_FWD_ROW_PER_BLOCK)) && p.rows >= 2ull * 148 * group_rows<ALLOW>() && part_vectors < 0xffffu && q.tiles_per_block >= 16) {
                 row_fwd_grouped<DT, REF, ALLOW><<<(unsigned)((p.rows + group_rows<ALLOW>() - 1) / group_rows<ALLOW>()), kThreads, 0, st>>>(q);
                 return after_launch();
             }
@@ -126,7 +119,7 @@ int NRL_ROW_FWD_ENTRY(const nrl_row_fwd_args* a, nrl_stream stream) {
     if (rc) return rc;
     uint32_t mode = a->flags & (NRL_FWD_SAMPLE | NRL_FWD_GREEDY | NRL_FWD_TOKENS_IN);
     if (mode & (mode - 1)) return NRL_E_BAD_ARG;  // more than one mode
-    if (a->flags & ~(uint32_t)(NRL_FWD_SAMPLE | NRL_FWD_GREEDY | NRL_FWD_TOKENS_IN | (NRL_MASK_BITS ? NRL_FWD_MASK_BITS : 0u))) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_FWD_SAMPLE | NRL_FWD_GREEDY | NRL_FWD_TOKENS_IN | NRL_FWD_ROW_PER_BLOCK | (NRL_MASK_BITS ? NRL_FWD_MASK_BITS : 0u))) return NRL_E_BAD_ARG;
     if ((mode & NRL_FWD_SAMPLE) && !a->uniforms) return NRL_E_BAD_ARG;
     if (mode && !a->tokens) return NRL_E_BAD_ARG;
     if (!mode && (a->logp || a->ref_logp)) return NRL_E_BAD_ARG;  // log-prob of which token?

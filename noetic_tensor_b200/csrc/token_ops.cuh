@@ -145,81 +145,204 @@ __global__ void __launch_bounds__(kRedThreads) clip_fraction_kernel(TokParams p,
     if (threadIdx.x == 0) out[s] = hits / fmaxf(cnt, 1.f);
 }
 
-// TokenReduction forward: one block per seed; each sequence is summed by the block in a fixed
-// tree, sequences are combined in index order in f64.
-__global__ void __launch_bounds__(kRedThreads) reduce_tokens_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* per, const float* mask, float* out) {
-    __shared__ float sm[2 * kRedThreads / 32];
-    const uint64_t s = blockIdx.x;
-    double tot = 0.0, count = 0.0, seq_tot = 0.0, nonempty = 0.0;
-    for (uint64_t b = 0; b < B; b++) {
-        const uint64_t base = (s * B + b) * T;
-        float v = 0.f, c = 0.f;
-        for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) {
-            v += per[base + t];
-            c += mask ? mask[base + t] : 1.f;
-        }
-        block_sum2<kRedThreads>(v, c, sm);
-        if (threadIdx.x == 0) {
-            tot += (double)v;
-            count += (double)c;
-            float ps = v / fmaxf(c, 1.f);
-            if (reduction == NRL_REDUCE_PER_SEQUENCE) out[s * B + b] = ps;
-            seq_tot += (double)ps;
-            nonempty += (double)fminf(c, 1.f);
-        }
+// ---- TokenReduction (src/nn/rl.rs:36-92) -----------------------------------------------------------
+//
+// Two fixed steps, the same whoever runs them: (1) one WARP sums a sequence — lane l adds the
+// elements l, l + 32, … of the sequence in that order, then the 32 lane sums meet in a butterfly —
+// giving the pair (Σ per, Σ mask) of that sequence; (2) a seed's pairs are folded in sequence order
+// in f64. nrl_reduce_tokens does both in one kernel (a block per seed, its warps taking the
+// seed's sequences side by side); callers whose sequences are spread over several GPUs run step
+// 1 where the sequences live (seq_pairs_kernel), gather the pairs and run step 2
+// (fold_pairs_kernel): the bits are the same for any number of GPUs.
+constexpr int kFoldThreads = 1024;  // 32 warps per seed
+constexpr int kSeqChunk = 1024;     // sequences of a seed held in shared memory between the two steps
+
+__device__ __forceinline__ void seq_sum(const float* __restrict__ per, const float* __restrict__ mask, uint64_t base, uint64_t T, float& v, float& c) {
+    const int lane = threadIdx.x & 31;
+    v = 0.f;
+    c = 0.f;
+    for (uint64_t t = lane; t < T; t += 32) {
+        if (per) v += per[base + t];
+        c += mask ? mask[base + t] : 1.f;
     }
-    if (threadIdx.x == 0) {
-        if (reduction == NRL_REDUCE_SUM) out[s] = (float)tot;
-        if (reduction == NRL_REDUCE_TOKEN_MEAN) out[s] = (float)tot / fmaxf((float)count, 1.f);
-        if (reduction == NRL_REDUCE_SEQUENCE_MEAN) out[s] = (float)seq_tot / fmaxf((float)nonempty, 1.f);
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        v += __shfl_xor_sync(0xffffffffu, v, s);
+        c += __shfl_xor_sync(0xffffffffu, c, s);
     }
 }
 
-// TokenReduction backward: d_per from the reduced value's upstream gradient.
-__global__ void __launch_bounds__(kRedThreads) reduce_tokens_bwd_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* mask, const float* g_out, float* d_per) {
-    __shared__ float sm[2 * kRedThreads / 32];
-    __shared__ float sh_scale;
+struct SeedFold {
+    double tot = 0.0, count = 0.0, seq_tot = 0.0, nonempty = 0.0;
+    __device__ __forceinline__ void add(float v, float c) {
+        tot += (double)v;
+        count += (double)c;
+        seq_tot += (double)(v / fmaxf(c, 1.f));  // per_sequence (src/nn/rl.rs:88-92)
+        nonempty += (double)fminf(c, 1.f);
+    }
+    __device__ __forceinline__ float value(uint32_t reduction) const {
+        if (reduction == NRL_REDUCE_SUM) return (float)tot;
+        if (reduction == NRL_REDUCE_TOKEN_MEAN) return (float)tot / fmaxf((float)count, 1.f);
+        return (float)seq_tot / fmaxf((float)nonempty, 1.f);  // SEQUENCE_MEAN
+    }
+    __device__ __forceinline__ float scale(uint32_t reduction) const {
+        if (reduction == NRL_REDUCE_TOKEN_MEAN) return fmaxf((float)count, 1.f);
+        if (reduction == NRL_REDUCE_SEQUENCE_MEAN) return fmaxf((float)nonempty, 1.f);
+        return 1.f;
+    }
+};
+
+// One block per seed: both steps.
+__global__ void __launch_bounds__(kFoldThreads) reduce_tokens_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* per, const float* mask, float* out) {
+    __shared__ float sv[kSeqChunk], sc[kSeqChunk];
     const uint64_t s = blockIdx.x;
-    // the seed-level divisor
-    float seed_scale = 1.f;
-    if (reduction == NRL_REDUCE_TOKEN_MEAN || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
-        double count = 0.0, nonempty = 0.0;
-        for (uint64_t b = 0; b < B; b++) {
-            const uint64_t base = (s * B + b) * T;
-            float c = 0.f, z = 0.f;
-            for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) c += mask ? mask[base + t] : 1.f;
-            block_sum2<kRedThreads>(c, z, sm);
-            if (threadIdx.x == 0) {
-                count += (double)c;
-                nonempty += (double)fminf(c, 1.f);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    SeedFold f;
+    for (uint64_t b0 = 0; b0 < B; b0 += kSeqChunk) {
+        const int n = (int)(B - b0 < (uint64_t)kSeqChunk ? B - b0 : (uint64_t)kSeqChunk);
+        for (int j = warp; j < n; j += kFoldThreads / 32) {
+            float v, c;
+            seq_sum(per, mask, (s * B + b0 + j) * T, T, v, c);
+            if (lane == 0) {
+                sv[j] = v;
+                sc[j] = c;
+                if (reduction == NRL_REDUCE_PER_SEQUENCE) out[s * B + b0 + j] = v / fmaxf(c, 1.f);
             }
         }
-        if (threadIdx.x == 0) sh_scale = reduction == NRL_REDUCE_TOKEN_MEAN ? fmaxf((float)count, 1.f) : fmaxf((float)nonempty, 1.f);
+        __syncthreads();
+        if (threadIdx.x == 0 && reduction != NRL_REDUCE_PER_SEQUENCE)
+            for (int j = 0; j < n; j++) f.add(sv[j], sc[j]);
+        __syncthreads();
+    }
+    if (threadIdx.x == 0 && reduction != NRL_REDUCE_PER_SEQUENCE) out[s] = f.value(reduction);
+}
+
+// Step 1 alone: pairs[q] = (Σ per, Σ mask) of sequence q, one warp each.
+__global__ void __launch_bounds__(256) seq_pairs_kernel(uint64_t n_seq, uint64_t T, const float* per, const float* mask, float2* pairs) {
+    const uint64_t q = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (q >= n_seq) return;
+    float v, c;
+    seq_sum(per, mask, q * T, T, v, c);
+    if ((threadIdx.x & 31) == 0) pairs[q] = make_float2(v, c);
+}
+
+// Step 2 alone: one thread per seed folds its B pairs in sequence order (PER_SEQUENCE: one thread per sequence).
+__global__ void fold_pairs_kernel(uint32_t reduction, uint64_t S, uint64_t B, const float2* pairs, float* out) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (reduction == NRL_REDUCE_PER_SEQUENCE) {
+        if (i < S * B) out[i] = pairs[i].x / fmaxf(pairs[i].y, 1.f);
+        return;
+    }
+    if (i >= S) return;
+    SeedFold f;
+    for (uint64_t b = 0; b < B; b++) f.add(pairs[i * B + b].x, pairs[i * B + b].y);
+    out[i] = f.value(reduction);
+}
+
+// TokenReduction backward: d_per from the reduced value's upstream gradient. One block per seed:
+// the seed's divisor first (the counts of all its sequences, folded as in the forward), then its
+// warps write the sequences side by side.
+__global__ void __launch_bounds__(kFoldThreads) reduce_tokens_bwd_kernel(uint32_t reduction, uint64_t B, uint64_t T, const float* mask, const float* g_out, float* d_per) {
+    __shared__ float sc[kSeqChunk];
+    __shared__ float sh_scale;
+    const uint64_t s = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    float seed_scale = 1.f;
+    if (reduction == NRL_REDUCE_TOKEN_MEAN || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
+        SeedFold f;
+        for (uint64_t b0 = 0; b0 < B; b0 += kSeqChunk) {
+            const int n = (int)(B - b0 < (uint64_t)kSeqChunk ? B - b0 : (uint64_t)kSeqChunk);
+            for (int j = warp; j < n; j += kFoldThreads / 32) {
+                float v, c;
+                seq_sum(nullptr, mask, (s * B + b0 + j) * T, T, v, c);
+                if (lane == 0) sc[j] = c;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0)
+                for (int j = 0; j < n; j++) f.add(0.f, sc[j]);
+            __syncthreads();
+        }
+        if (threadIdx.x == 0) sh_scale = f.scale(reduction);
         __syncthreads();
         seed_scale = sh_scale;
     }
-    for (uint64_t b = 0; b < B; b++) {
+    for (uint64_t b = warp; b < B; b += kFoldThreads / 32) {
         const uint64_t base = (s * B + b) * T;
-        float g;
+        float g = 0.f;
         if (reduction == NRL_REDUCE_PER_SEQUENCE || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
-            float c = 0.f, z = 0.f;
-            for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) c += mask ? mask[base + t] : 1.f;
-            block_sum2<kRedThreads>(c, z, sm);
-            if (threadIdx.x == 0) sh_scale = fmaxf(c, 1.f);
-            __syncthreads();
-            float seq_scale = sh_scale;
-            __syncthreads();
+            float v, c;
+            seq_sum(nullptr, mask, base, T, v, c);
+            const float seq_scale = fmaxf(c, 1.f);
             g = reduction == NRL_REDUCE_PER_SEQUENCE ? g_out[s * B + b] / seq_scale : (g_out[s] / seed_scale) / seq_scale;
         } else if (reduction == NRL_REDUCE_TOKEN_MEAN) {
             g = g_out[s] / seed_scale;
-        } else {
-            g = g_out[s];  // SUM
+        } else if (reduction == NRL_REDUCE_SUM) {
+            g = g_out[s];
         }
-        for (uint64_t t = threadIdx.x; t < T; t += kRedThreads) {
-            bool scored = mask ? mask[base + t] != 0.f : true;
-            float gi = reduction == NRL_REDUCE_NONE ? g_out[base + t] : g;
+        for (uint64_t t = lane; t < T; t += 32) {
+            const bool scored = mask ? mask[base + t] != 0.f : true;
+            const float gi = reduction == NRL_REDUCE_NONE ? g_out[base + t] : g;
             d_per[base + t] = scored ? gi : 0.f;
         }
+    }
+}
+
+// The same backward for a caller that holds only the sequences [seq_begin, seq_begin + n_seq) of
+// the job: the counts come from the gathered pairs of ALL sequences, `mask` and `d_per` cover
+// the local sequences, `g_out` is the whole reduced value's gradient ([S] or [S, B]; for NONE the
+// local [n_seq, T]). One warp per local sequence.
+__global__ void __launch_bounds__(256) reduce_tokens_bwd_pairs_kernel(uint32_t reduction, uint64_t B, uint64_t T, uint64_t seq_begin, uint64_t n_seq,
+                                                                      const float2* pairs, const float* mask, const float* g_out, float* d_per) {
+    const uint64_t q = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (q >= n_seq) return;
+    const int lane = threadIdx.x & 31;
+    const uint64_t seq = seq_begin + q, s = seq / B;
+    float g = 0.f;
+    if (reduction != NRL_REDUCE_NONE) {
+        float seed_scale = 1.f;
+        if (reduction == NRL_REDUCE_TOKEN_MEAN || reduction == NRL_REDUCE_SEQUENCE_MEAN) {
+            SeedFold f;
+            for (uint64_t b = 0; b < B; b++) f.add(0.f, pairs[s * B + b].y);
+            seed_scale = f.scale(reduction);
+        }
+        const float seq_scale = fmaxf(pairs[seq].y, 1.f);
+        if (reduction == NRL_REDUCE_PER_SEQUENCE) g = g_out[seq] / seq_scale;
+        else if (reduction == NRL_REDUCE_SEQUENCE_MEAN) g = (g_out[s] / seed_scale) / seq_scale;
+        else if (reduction == NRL_REDUCE_TOKEN_MEAN) g = g_out[s] / seed_scale;
+        else g = g_out[s];
+    }
+    const uint64_t base = q * T;
+    for (uint64_t t = lane; t < T; t += 32) {
+        const bool scored = mask ? mask[base + t] != 0.f : true;
+        const float gi = reduction == NRL_REDUCE_NONE ? g_out[base + t] : g;
+        d_per[base + t] = scored ? gi : 0.f;
+    }
+}
+
+// check_scored_finite (src/nn/rl.rs:204-211) on the device: the first flat position whose mask is
+// non-zero (no mask: every position) and whose value is not finite. One block; a thread keeps
+// the smallest such index of its strided share, the block takes the minimum in a fixed tree (a
+// minimum does not depend on the order anyway). out[0] = the index or ~0, out[1] = the value's bits.
+constexpr int kScanThreads = 1024;
+__global__ void __launch_bounds__(kScanThreads) first_nonfinite_kernel(uint64_t n, const float* x, const float* mask, uint64_t* out) {
+    __shared__ uint64_t sm[kScanThreads / 32];
+    uint64_t first = ~0ull;
+    for (uint64_t i = threadIdx.x; i < n && first == ~0ull; i += kScanThreads) {
+        const float v = x[i];
+        const bool scored = mask ? mask[i] != 0.f : true;
+        if (scored && !(fabsf(v) <= FLT_MAX)) first = i;
+    }
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const uint64_t o = __shfl_xor_sync(0xffffffffu, first, s);
+        first = o < first ? o : first;
+    }
+    if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = first;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kScanThreads / 32; w++) first = sm[w] < first ? sm[w] : first;
+        out[0] = first;
+        out[1] = first == ~0ull ? 0ull : (uint64_t)__float_as_uint(x[first]);
     }
 }
 

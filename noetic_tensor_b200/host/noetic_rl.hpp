@@ -540,6 +540,33 @@ inline Tensor token_log_probs(const Tensor& logits, const IntTensor& tokens) {
     return logp;
 }
 
+// src/nn/rl.rs:204-211: every scored log-probability (mask != 0; no mask: all) is finite. Returns
+// an empty string, or the reference's error text naming the first flat position. A host read.
+inline std::string check_scored_finite(const std::string& what, const Tensor& logp, const Tensor* mask) {
+    if (logp.dtype() != DType::F32) throw std::runtime_error("check_scored_finite: F32 log-probabilities");
+    if (mask && numel(mask->shape()) != numel(logp.shape())) throw std::runtime_error("rl: mask shape");
+    Tensor result = Tensor::empty(Shape{4}, DType::F32, logp.device());  // 16 bytes of device scratch
+    uint64_t pos = 0;
+    float value = 0.f;
+    const int rc = nrl_check_scored_finite(logp.dev(), mask ? mask->dev() : 0, numel(logp.shape()), result.dev(), detail::stream(), &pos, &value);
+    if (rc == NRL_E_NOT_FINITE) {
+        const char* v = value != value ? "NaN" : (value > 0 ? "inf" : "-inf");  // Rust's `{}` of an f64
+        return what + ": the scored log-probability at flat position " + std::to_string(pos) + " is " + v + " (not finite)";
+    }
+    nrl(rc, "check_scored_finite");
+    return std::string();
+}
+
+// src/nn/rl.rs:213-221: the losses run the check in debug builds (here: unless NDEBUG is defined).
+inline void debug_check(const char* what, const Tensor& logp, const Tensor* mask) {
+#ifndef NDEBUG
+    const std::string e = check_scored_finite(what, logp, mask);
+    if (!e.empty()) throw std::runtime_error(e);
+#else
+    (void)what; (void)logp; (void)mask;
+#endif
+}
+
 namespace detail {
 // a token-level loss of logp [S,B,T]: one node whose backward hands d/dlogp to logp's node
 inline Tensor token_level(uint32_t kind, const Tensor& logp, const Tensor* other, const Tensor* weights, const Tensor* mask, TokenReduction red, const Clip* clip, bool has_clamp, double clamp) {
@@ -609,14 +636,22 @@ inline Tensor token_level(uint32_t kind, const Tensor& logp, const Tensor* other
 
 // src/nn/rl.rs:228-235
 inline Tensor policy_gradient_loss(const Tensor& logp, const Tensor& weights, const Tensor* mask, TokenReduction reduction) {
+    if (logp.rank() != 3) throw std::runtime_error("policy_gradient_loss: logp [S, B, T]");
+    debug_check("policy_gradient_loss", logp, mask);
     return detail::token_level(NRL_LOSS_PG, logp, nullptr, &weights, mask, reduction, nullptr, false, 0.0);
 }
 // src/nn/rl.rs:265-287
 inline Tensor clipped_policy_loss(const Tensor& logp, const Tensor& old_logp, const Tensor& advantages, const Tensor* mask, const Clip& clip, TokenReduction reduction) {
+    clip.check();
+    if (logp.rank() != 3) throw std::runtime_error("clipped_policy_loss: logp [S, B, T]");
+    debug_check("clipped_policy_loss", logp, mask);
+    debug_check("clipped_policy_loss (old log-probabilities)", old_logp, mask);
     return detail::token_level(NRL_LOSS_PPO, logp, &old_logp, &advantages, mask, reduction, &clip, false, 0.0);
 }
 // src/nn/rl.rs:380-400
 inline Tensor kl_estimate(const Tensor& logp, const Tensor& ref_logp, KlEstimator e, bool has_delta_clamp, double delta_clamp, const Tensor* mask, TokenReduction reduction) {
+    debug_check("kl_estimate", logp, mask);
+    debug_check("kl_estimate (reference log-probabilities)", ref_logp, mask);
     return detail::token_level((uint32_t)e, logp, &ref_logp, nullptr, mask, reduction, nullptr, has_delta_clamp, delta_clamp);
 }
 // src/nn/rl.rs:293-317 (untracked)

@@ -27,7 +27,9 @@ def bind_host_thread_near(device):
     `local_cpulist` the kernel publishes for the GPU's PCI function), so that host buffers it then
     allocates and first touches land in the memory of that NUMA node: a kernel or a copy that reads
     them does not cross the socket interconnect. Returns the CPU set, or None when the topology is
-    not visible (a container without /sys, a single-node host): nothing is changed then."""
+    not visible (a container without /sys, a single-node host): nothing is changed then.
+    The narrowing lasts until the caller undoes it: `os.sched_setaffinity(0, previous)` with the
+    set `os.sched_getaffinity(0)` gave before the call, or use `host_threads_near` below."""
     try:
         p = torch.cuda.get_device_properties(torch.device(device))
         addr = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
@@ -47,13 +49,42 @@ def bind_host_thread_near(device):
         return None
 
 
+class host_threads_near:
+    """`with host_threads_near(device):` — `bind_host_thread_near` for the block, the process's
+    previous CPU affinity restored on leaving it."""
+
+    def __init__(self, device):
+        self.device = device
+
+    def __enter__(self):
+        self.previous = os.sched_getaffinity(0)
+        self.cpus = bind_host_thread_near(self.device)
+        return self.cpus
+
+    def __exit__(self, *exc):
+        if self.cpus is not None:
+            os.sched_setaffinity(0, self.previous)
+        return False
+
+
+def default_host_threads():
+    """Host threads one rank may use for packing: the CPUs this process may run on, shared evenly
+    among the ranks of this host (LOCAL_WORLD_SIZE, as torchrun sets it), at most 32."""
+    try:
+        cpus = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cpus = os.cpu_count() or 1
+    local_world = max(1, int(os.environ.get("LOCAL_WORLD_SIZE", "1") or 1))
+    return max(1, min(cpus // local_world, 32))
+
+
 class HostForward:
     def __init__(self, V, dtype, *, chunk_rows=512, ref=True, mask=True, device="cuda:0", packed=True, live_fraction=0.25, threads=None):
         self.dev = torch.device(device)
         self.V, self.dtype, self.chunk = V, dtype, chunk_rows
         self.has_ref, self.has_mask = ref, mask
         self.packed = bool(packed and mask and V % 8 == 0 and V <= 262144)
-        self.threads = int(threads or min(os.cpu_count() or 1, 32))
+        self.threads = int(threads or default_host_threads())
         self.words = (V // 8 + 63) // 64
         self.capacity = max(1, int(chunk_rows * (V // 8) * live_fraction))  # live vectors a chunk's staging buffers hold
         mk = lambda dt, *shape: torch.empty(*shape, dtype=dt, device=self.dev)
@@ -148,13 +179,13 @@ class HostForward:
         if host_pack:  # bits are made per chunk below; `mask_bits` stands for "the kernels get bits"
             words = (self.V + 31) // 32
             n_stage = min(chunk_rows, rows)
-            if getattr(self, "_host_bits", None) is None or self._host_bits[0].shape[0] < n_stage:
+            if getattr(self, "_host_bits", None) is None or self._host_bits[0].shape[0] < n_stage or self._host_bits[0].shape[1] != words:
                 self._host_bits = [torch.empty(n_stage, words, dtype=torch.int32).pin_memory() for _ in range(2)]
                 self._host_bits_copied = [torch.cuda.Event() for _ in range(2)]
             mask_bits = self._host_bits[0]  # only its shape is used before the loop
         if mask_bits is not None:
             mask, mask_by_copy = mask_bits, True
-            if getattr(self, "_mapped_bits", None) is None or self._mapped_bits[0].shape[0] < min(chunk_rows, rows):
+            if getattr(self, "_mapped_bits", None) is None or self._mapped_bits[0].shape[0] < min(chunk_rows, rows) or self._mapped_bits[0].shape[1] != mask_bits.shape[1]:
                 self._mapped_bits = [torch.empty(min(chunk_rows, rows), mask_bits.shape[1], dtype=torch.int32, device=self.dev) for _ in range(2)]
         by_copy = mask_by_copy and mask is not None
         if not by_copy:

@@ -63,7 +63,7 @@ class RowForward:
 
 
 def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperature=1.0, uniforms=None, tokens=None, greedy=False,
-                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None, device=None, allow_bits=None):
+                want_logp=True, want_entropy=True, want_kl=None, want_ref_logp=None, workspace=None, device=None, allow_bits=None, row_per_block=False):
     """Fused sample / log-prob / KL / entropy over logits [rows, V] (f32 or bf16, CUDA).
 
     Exactly one of: `uniforms` (sample by inverse CDF), `greedy=True`, `tokens` (given, int32), or
@@ -76,7 +76,10 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
 
     `allow_bits` instead of `allow`: the mask bit-packed, int32 [rows, ceil(V/32)] (or [1, …]) on
     the device, bit v of a row = bit (v mod 32) of word v / 32; the kernels read V/8 mask bytes
-    per row instead of V."""
+    per row instead of V.
+
+    `row_per_block=True` (NRL_FWD_ROW_PER_BLOCK): the kernel with one thread block per row also
+    where the call has enough rows for the grouped kernel."""
     in_dev = logits.device
     dev = torch.device(device) if device is not None else in_dev
     if dev.type != "cuda":
@@ -121,7 +124,7 @@ def row_forward(logits, *, ref_logits=None, allow=None, add_mask=None, temperatu
         out.tokens = tokens
     else:
         out.tokens = None
-    a.flags, a.tokens = mode | bits_flag, _p(out.tokens)
+    a.flags, a.tokens = mode | bits_flag | (capi.FWD_ROW_PER_BLOCK if row_per_block else 0), _p(out.tokens)
     has_ref = ref_logits is not None
     want_kl = has_ref if want_kl is None else want_kl
     want_ref_logp = (has_ref and mode != 0) if want_ref_logp is None else want_ref_logp
@@ -310,6 +313,66 @@ def check_status(status):
     if rc == capi.E_ROW_STATUS:
         raise RuntimeError(f"sample_categorical: position {bad.value} has no allowed token (every logit −∞ or a NaN)")
     capi.check(rc, "nrl_check_status")
+
+
+def _rust_float(v):
+    """How Rust's `{}` prints a non-finite f64 (the reference's message carries the value)."""
+    if v != v:
+        return "NaN"
+    return "inf" if v > 0 else "-inf"
+
+
+def check_scored_finite(what, logp, mask=None):
+    """`check_scored_finite(what, logp, mask)` (src/nn/rl.rs:204-211): None when every scored
+    log-probability (mask != 0; no mask: all) is finite, else the reference's error text, which
+    names the first flat position. A host read: it synchronises the stream."""
+    dev = logp.device
+    if dev.type != "cuda" or logp.dtype != torch.float32 or not logp.is_contiguous():
+        raise ValueError("check_scored_finite: a contiguous float32 CUDA tensor")
+    if mask is not None:
+        _need(mask, torch.float32, logp.shape, "mask", dev)
+    result = torch.empty(2, dtype=torch.int64, device=dev)
+    pos, val = C.c_uint64(0), C.c_float(0.0)
+    with torch.cuda.device(dev):
+        rc = capi.lib().nrl_check_scored_finite(_p(logp), _p(mask), logp.numel(), _p(result), _stream(dev), C.byref(pos), C.byref(val))
+    if rc == capi.E_NOT_FINITE:
+        return f"{what}: the scored log-probability at flat position {pos.value} is {_rust_float(val.value)} (not finite)"
+    capi.check(rc, "nrl_check_scored_finite")
+    return None
+
+
+def reduce_tokens_partial(per, mask):
+    """Step 1 of a TokenReduction on the sequences this caller holds: `per`, `mask` [n_seq, T] ->
+    pairs [n_seq, 2] = (sum of per, sum of mask) per sequence (nrl_reduce_tokens_partial)."""
+    n_seq, T = per.shape
+    dev = per.device
+    _need(per, torch.float32, (n_seq, T), "per", dev)
+    if mask is not None:
+        _need(mask, torch.float32, (n_seq, T), "mask", dev)
+    pairs = torch.empty(n_seq, 2, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_reduce_tokens_partial(n_seq, T, _p(per), _p(mask), _p(pairs), _stream(dev)), "nrl_reduce_tokens_partial")
+    return pairs
+
+
+def reduce_tokens_fold(pairs, S, B, reduction):
+    """Step 2: the pairs of all S·B sequences, in sequence order, folded per seed (nrl_reduce_tokens_fold)."""
+    dev = pairs.device
+    _need(pairs, torch.float32, (S * B, 2), "pairs", dev)
+    out = torch.empty((S, B) if reduction == capi.REDUCE_PER_SEQUENCE else (S,), dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_reduce_tokens_fold(reduction, S, B, _p(pairs), _p(out), _stream(dev)), "nrl_reduce_tokens_fold")
+    return out
+
+
+def reduce_tokens_backward_pairs(reduction, S, B, T, seq_begin, n_seq, pairs, mask, g_out):
+    """d_per [n_seq, T] of the local sequences from the whole reduced value's gradient and the
+    gathered pairs (nrl_reduce_tokens_bwd_pairs)."""
+    dev = g_out.device
+    d = torch.empty(n_seq, T, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_reduce_tokens_bwd_pairs(reduction, S, B, T, seq_begin, n_seq, _p(pairs), _p(mask), _p(g_out), _p(d), _stream(dev)), "nrl_reduce_tokens_bwd_pairs")
+    return d
 
 
 def row_sum(logits):

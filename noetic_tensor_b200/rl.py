@@ -10,6 +10,8 @@ Masks: `mask` is the scoring mask [S,B,T] of 0/1 floats (src/nn/rl.rs:9-14); `vo
 either a float additive mask broadcastable as [1,V] or [rows,V] (the reference's form,
 src/nn/rl.rs:471-486) or a uint8/bool allow-mask of the same shapes.
 """
+import os
+
 import torch
 
 from . import capi, ops
@@ -18,6 +20,26 @@ NONE, SUM, TOKEN_MEAN, PER_SEQUENCE, SEQUENCE_MEAN = range(5)
 K1, K2, K3 = capi.LOSS_K1, capi.LOSS_K2, capi.LOSS_K3
 LOG_RATIO_CLAMP = 20.0  # src/nn/rl.rs:146
 KL_DELTA_CLAMP = 20.0  # src/nn/rl.rs:150
+
+
+# The reference's losses check their scored log-probabilities in debug builds only
+# (`debug_check`, src/nn/rl.rs:213-221: a host read). Here the switch is this flag, set from the
+# environment variable NOETIC_RL_DEBUG (any value but "" and "0") when the module is imported.
+DEBUG_CHECKS = os.environ.get("NOETIC_RL_DEBUG", "0") not in ("", "0")
+
+
+def check_scored_finite(what, logp, mask=None):
+    """`check_scored_finite` (src/nn/rl.rs:204-211): None, or the error text naming the first scored
+    position whose log-probability is not finite."""
+    return ops.check_scored_finite(what, logp.contiguous(), None if mask is None else mask.contiguous())
+
+
+def debug_check(what, logp, mask=None):
+    """`debug_check` (src/nn/rl.rs:213-221): raises the check's message when DEBUG_CHECKS is on."""
+    if DEBUG_CHECKS:
+        e = check_scored_finite(what, logp, mask)
+        if e is not None:
+            raise RuntimeError(e)
 
 
 class Clip:
@@ -150,11 +172,25 @@ def token_log_probs(logits, tokens, mask=None):
     return Loss(value, backward)
 
 
+_CHECK_NAMES = {
+    capi.LOSS_PG: ("policy_gradient_loss", None),
+    capi.LOSS_PPO: ("clipped_policy_loss", "clipped_policy_loss (old log-probabilities)"),
+    capi.LOSS_K1: ("kl_estimate", "kl_estimate (reference log-probabilities)"),
+    capi.LOSS_K2: ("kl_estimate", "kl_estimate (reference log-probabilities)"),
+    capi.LOSS_K3: ("kl_estimate", "kl_estimate (reference log-probabilities)"),
+}
+
+
 def _token_level(kind, logits, tokens, mask, reduction, **kw):
     t = _TokenLogProbs(logits, tokens)
     lp = t.logp.reshape(t.lead) if len(t.lead) == 3 else None
     if lp is None:
         raise ValueError("logp must be [S, B, T]")
+    # the checks of src/nn/rl.rs:230, 268-269, 386-387
+    what, what_other = _CHECK_NAMES[kind]
+    debug_check(what, lp, mask)
+    if what_other is not None:
+        debug_check(what_other, kw["other"], mask)
     per, _ = ops.token_loss(kind, lp, mask=mask, want_grad=False, **kw)
     value = ops.reduce_tokens(per, mask, reduction)
 

@@ -230,6 +230,27 @@ def group_advantages(rewards, n, norm="mean", eps=0.0, unbiased=True):
     return out
 
 
+def _rust_f64(v):
+    """`{}` of an f64 in Rust for the values that matter here."""
+    if np.isnan(v):
+        return "NaN"
+    if np.isinf(v):
+        return "inf" if v > 0 else "-inf"
+    return repr(float(v))
+
+
+def check_scored_finite(what, logp, mask=None):
+    """`check_scored_finite` (src/nn/rl.rs:204-211): None when every scored log-probability is
+    finite, else the reference's error text naming the first flat position."""
+    v = _f64(logp).ravel()
+    m = None if mask is None else _f64(mask).ravel()
+    lib().orc_check_scored_finite.restype = C.c_int64
+    i = lib().orc_check_scored_finite(_ptr(v), _ptr(m), C.c_int64(v.size))
+    if i < 0:
+        return None
+    return f"{what}: the scored log-probability at flat position {i} is {_rust_f64(v[i])} (not finite)"
+
+
 def sha256(data: bytes) -> bytes:
     out = (C.c_uint8 * 32)()
     lib().orc_sha256(data, C.c_int64(len(data)), out)

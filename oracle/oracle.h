@@ -72,6 +72,9 @@ typedef struct orc_rl_case {
 const char* orc_last_error(void);
 int orc_set_backend(int fast, int threads);
 int orc_rl_eval(const orc_rl_case* c);
+/* check_scored_finite (src/nn/rl.rs:204-211): the first flat position whose mask (NULL = every
+ * position scored) is non-zero and whose log-probability is not finite, or -1. */
+int64_t orc_check_scored_finite(const double* logp, const double* mask, int64_t n);
 int orc_group_advantages(const double* rewards, int64_t len, int64_t n, int norm_std, double eps, int unbiased, double* out);
 
 void orc_sha256(const void* data, int64_t n, uint8_t out[32]);

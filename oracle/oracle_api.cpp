@@ -186,6 +186,13 @@ extern "C" int orc_lane_op(int op, int engine_dtype, const void* x, int x_dtype,
     }
 }
 
+// check_scored_finite (src/nn/rl.rs:204-211): `(0..v.len()).find(|&i| m.is_none_or(|m| m[i] != 0.0) && !v[i].is_finite())`.
+extern "C" int64_t orc_check_scored_finite(const double* logp, const double* mask, int64_t n) {
+    for (int64_t i = 0; i < n; i++)
+        if ((!mask || mask[i] != 0.0) && !std::isfinite(logp[i])) return i;
+    return -1;
+}
+
 extern "C" int orc_group_advantages(const double* rewards, int64_t len, int64_t n, int norm_std, double eps, int unbiased, double* out) {
     try {
         auto v = group_advantages(rewards, (size_t)len, (size_t)n, norm_std, eps, unbiased != 0);

@@ -4,6 +4,7 @@
 // closed forms. Run by tests/test_gpu_host_cpp.py; exits non-zero on the first failed check.
 #include <algorithm>
 #include <cstdio>
+#include <limits>
 #include <random>
 
 #include "../../noetic_tensor_b200/host/noetic_loss.hpp"
@@ -521,6 +522,30 @@ static void test_group_advantages() {
     CHECK(throws([] { rl::group_advantages_tensor(Tensor::from_f32({1, 2}, {2, 1}, dev), rl::GroupNorm::Std(0.0, true)); }, "at least 2"), "tensor n = 1 unbiased");
 }
 
+// ---- check_scored_finite (src/nn/tests/rl.rs:837-855) -------------------------------------------
+static void test_check_scored_finite() {
+    const float ninf = -std::numeric_limits<float>::infinity();
+    Tensor lp = Tensor::from_f32({-1.0f, ninf, -2.0f}, {1, 1, 3}, dev);
+    const std::string e = rl::check_scored_finite("test", lp, nullptr);
+    CHECK(e.find("position 1") != std::string::npos && e == "test: the scored log-probability at flat position 1 is -inf (not finite)", "%s", e.c_str());
+    Tensor m = Tensor::from_f32({1.0f, 0.0f, 1.0f}, {1, 1, 3}, dev);
+    CHECK(rl::check_scored_finite("test", lp, &m).empty(), "a -inf at a masked position passes");
+    CHECK(rl::check_scored_finite("test", Tensor::from_f32({-1.0f, -3.0f, -2.0f}, {1, 1, 3}, dev), nullptr).empty(), "finite values pass");
+    Tensor nan = Tensor::from_f32({-1.0f, -2.0f, std::nanf("")}, {1, 1, 3}, dev);
+    CHECK(rl::check_scored_finite("x", nan, nullptr) == "x: the scored log-probability at flat position 2 is NaN (not finite)", "NaN is named");
+#ifndef NDEBUG
+    // debug builds refuse a scored log-probability of -inf in the losses
+    Tensor two = Tensor::from_f32({-1.0f, ninf}, {1, 1, 2}, dev);
+    Tensor w = Tensor::from_f32({1.0f}, {1, 1}, dev);
+    CHECK(throws([&] { rl::policy_gradient_loss(two, w, nullptr, TokenReduction::Sum); }, "not finite"), "policy_gradient_loss refuses");
+    Tensor old = Tensor::from_f32({-1.0f, -1.0f}, {1, 1, 2}, dev);
+    CHECK(throws([&] { rl::clipped_policy_loss(old, two, w, nullptr, rl::Clip::symmetric(0.2), TokenReduction::Sum); }, "clipped_policy_loss (old log-probabilities)"), "old log-probs checked");
+    CHECK(throws([&] { rl::kl_estimate(old, two, rl::KlEstimator::K3, false, 0.0, nullptr, TokenReduction::Sum); }, "kl_estimate (reference log-probabilities)"), "reference log-probs checked");
+    Tensor skip = Tensor::from_f32({1.0f, 0.0f}, {1, 1, 2}, dev);
+    (void)rl::policy_gradient_loss(two, w, &skip, TokenReduction::Sum);  // unscored: passes
+#endif
+}
+
 // ---- bit-packed vocabulary masks: the same results as the byte mask, bit for bit --------------------
 static void test_bit_masks() {
     const size_t S = 2, B = 3, T = 4, V = 200, rows = S * B * T, words = (V + 31) / 32;
@@ -730,7 +755,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"sample_categorical (reference noise)", test_sample_categorical_reference},
-        {"group_advantages", test_group_advantages}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
+        {"group_advantages", test_group_advantages}, {"check_scored_finite", test_check_scored_finite}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {

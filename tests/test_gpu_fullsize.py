@@ -39,6 +39,29 @@ def _check_sample(oracle, f, x, r, m, u, idx, V):
     return int(differ.sum()), int(o["boundary"].sum())
 
 
+def _check_grad_sample(oracle, d, x, r, m, tokens, idx, V, g_lp, g_kl, g_ent):
+    """d(logits) of rows `idx` against the oracle's tape (f64 to 2e-6, f32 to the reference's
+    device tolerance 1e-4 of |Δ|/(1+|ref|), src/nn/tests/gpu/rl.rs:106-123), with the rows' allow
+    mask as the full additive −inf vocabulary mask."""
+    n = idx.numel()
+    xi, ri = _bits(x[idx]), (None if r is None else _bits(r[idx]))
+    vm = None if m is None else np.where(m[idx].cpu().numpy() != 0, 0.0, -np.inf)
+    tok = tokens[idx].cpu().numpy().astype(np.int64)
+    up = lambda g: g[idx].cpu().numpy().astype(np.float64)
+    got = d[idx].cpu().numpy().astype(np.float64).ravel()
+    shape = (1, 1, n, V)
+    for dt, tol in ((oracle.F64, 2e-6), (oracle.F32, 1e-4)):
+        want = np.zeros(n * V)
+        if g_lp is not None:
+            want += oracle.rl_eval(oracle.OP_TOKEN_LOG_PROBS, shape, dtype=dt, logits=xi, tokens=tok, vocab_mask=vm, upstream=up(g_lp))[1]
+        if g_ent is not None:
+            want += oracle.rl_eval(oracle.OP_ENTROPY, shape, dtype=dt, logits=xi, vocab_mask=vm, upstream=up(g_ent))[1]
+        if g_kl is not None:
+            want += oracle.rl_eval(oracle.OP_REFERENCE_KL, shape, dtype=dt, logits=xi, ref_logits=ri, vocab_mask=vm, upstream=up(g_kl))[1]
+        err = np.abs(got - want) / (1.0 + np.abs(want))
+        assert np.nanmax(err) <= tol and not np.isnan(got).any(), f"d(logits) vs oracle dtype {dt}: {np.nanmax(err):.3e}"
+
+
 def _properties(f, m, rows, V):
     tok = f.tokens.long()
     assert (f.status == 0).all()
@@ -82,6 +105,7 @@ def test_config3_headline_rows(oracle):
     assert (d[score == 0] == 0).all(), "an unscored row has a gradient"
     assert (d[m == 0] == 0).all(), "an excluded token has a gradient"
     assert d.sum(dim=1).abs().max().item() < 2e-3
+    _check_grad_sample(oracle, d, x, r, m, f.tokens, idx[:8], V, score, 0.04 * score, -0.01 * score)
 
 
 def test_config4_ppo_rows(oracle):
@@ -104,6 +128,7 @@ def test_config4_ppo_rows(oracle):
     ones = torch.ones(rows, device=dev)
     d = ops.row_backward(x, f, ref_logits=r, g_logp=ones, g_kl=0.04 * ones, g_ent=-0.01 * ones)
     assert torch.isfinite(d).all() and d.sum(dim=1).abs().max().item() < 2e-3
+    _check_grad_sample(oracle, d, x, r, None, f.tokens, idx[:6], V, ones, 0.04 * ones, -0.01 * ones)
     # the sampled token's entry is the only positive one of the log-prob term
     d1 = ops.row_backward(x, f, g_logp=ones)
     picked = d1[torch.arange(rows, device=dev), f.tokens.long()]
@@ -134,3 +159,4 @@ def test_config5_sparse_rows(oracle):
     ones = torch.ones(rows, device=dev)
     d = ops.row_backward(x, f, ref_logits=r, allow=m, g_logp=ones, g_kl=ones)
     assert (d[m == 0] == 0).all() and torch.isfinite(d).all()
+    _check_grad_sample(oracle, d, x, r, m, f.tokens, idx[:4], V, ones, ones, None)

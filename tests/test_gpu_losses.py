@@ -277,3 +277,98 @@ def test_all_masked_and_one_token(oracle):
         assert all(v == 0.0 for i, v in enumerate(per.tolist()) if i != len(per) - 2)
         for r in (rl.TOKEN_MEAN, rl.SEQUENCE_MEAN, rl.SUM):
             assert f(one, r).value.cpu().tolist() == [0.0, only], (name, r)
+
+
+def test_check_scored_finite_names_the_first_position(oracle):
+    """check_scored_finite (src/nn/rl.rs:204-211; its test src/nn/tests/rl.rs:837-846) through the C
+    ABI: the same verdict and message as the oracle's restatement, on the reference's hand cases
+    and on random placements of −inf / NaN / +inf under random scoring masks."""
+    from noetic_tensor_b200 import ops, rl
+
+    dev = torch.device("cuda:0")
+    t = lambda a: torch.tensor(a, dtype=torch.float32, device=dev)
+    lp = [-1.0, -np.inf, -2.0]
+    assert rl.check_scored_finite("test", t(lp).reshape(1, 1, 3)) == oracle.check_scored_finite("test", lp)
+    assert "position 1" in rl.check_scored_finite("test", t(lp).reshape(1, 1, 3))
+    assert rl.check_scored_finite("test", t(lp).reshape(1, 1, 3), t([1.0, 0.0, 1.0]).reshape(1, 1, 3)) is None
+    assert rl.check_scored_finite("test", t([-1.0, -3.0, -2.0]).reshape(1, 1, 3)) is None
+    g = np.random.default_rng(16)
+    for n in (1, 31, 1024, 1025, 70_001):
+        for _ in range(6):
+            v = -g.uniform(0, 9, n)
+            bad = g.choice(n, size=min(n, int(g.integers(0, 4))), replace=False)
+            v[bad] = g.choice([-np.inf, np.inf, np.nan], size=bad.size)
+            m = (g.uniform(0, 1, n) < 0.6).astype(np.float64) if g.uniform() < 0.7 else None
+            got = ops.check_scored_finite("policy_gradient_loss", t(v), None if m is None else t(m))
+            assert got == oracle.check_scored_finite("policy_gradient_loss", v.astype(np.float32), m)
+
+
+def test_losses_refuse_non_finite_scored_log_probs_in_debug_mode(monkeypatch):
+    """src/nn/tests/rl.rs:847-855 (debug builds): a scored token the vocabulary mask excludes has
+    log-probability −inf and the losses refuse it, naming the position; unscored it passes; with
+    the switch off nothing is read back."""
+    from noetic_tensor_b200 import rl
+
+    dev = torch.device("cuda:0")
+    V = 16
+    logits = torch.zeros(1, 1, 2, V, device=dev)
+    allow = torch.ones(1, V, dtype=torch.uint8, device=dev)
+    allow[0, 5] = 0
+    tokens = torch.tensor([[[3, 5]]], dtype=torch.int32, device=dev)
+    w = torch.ones(1, 1, device=dev)
+    z = rl.Tempered(logits, 1.0, allow)
+    monkeypatch.setattr(rl, "DEBUG_CHECKS", True)
+    with pytest.raises(RuntimeError, match=r"policy_gradient_loss: the scored log-probability at flat position 1 is -inf \(not finite\)"):
+        rl.policy_gradient_loss(z, tokens, w, reduction=rl.SUM)
+    skip = torch.tensor([[[1.0, 0.0]]], device=dev)
+    rl.policy_gradient_loss(z, tokens, w, mask=skip, reduction=rl.SUM)
+    old = torch.tensor([[[-1.0, float("-inf")]]], device=dev)
+    ok_tokens = torch.tensor([[[3, 4]]], dtype=torch.int32, device=dev)
+    with pytest.raises(RuntimeError, match=r"clipped_policy_loss \(old log-probabilities\): .* position 1 is -inf"):
+        rl.clipped_policy_loss(z, ok_tokens, old, w, reduction=rl.SUM)
+    with pytest.raises(RuntimeError, match=r"kl_estimate \(reference log-probabilities\): .* position 1 is -inf"):
+        rl.kl_estimate(z, ok_tokens, old, rl.K3, reduction=rl.SUM)
+    monkeypatch.setattr(rl, "DEBUG_CHECKS", False)
+    assert torch.isinf(rl.policy_gradient_loss(z, tokens, w, reduction=rl.SUM).value).all()
+
+
+@pytest.mark.parametrize("S,B,T", [(2, 3, 4), (3, 5, 7), (8, 32, 1024), (4, 256, 128), (2, 1100, 33), (1, 1, 1)])
+def test_token_reduction_bits_do_not_depend_on_the_number_of_gpus(S, B, T):
+    """nrl_reduce_tokens equals, to the bit, the two-step form a sharded caller runs
+    (nrl_reduce_tokens_partial on each shard's sequences -> pairs concatenated in sequence order ->
+    nrl_reduce_tokens_fold) for 1, 2, 3 and 8 shards, and both equal the stated operand order
+    evaluated on the host (tests/truth.py). The backward from gathered pairs equals
+    nrl_reduce_tokens_bwd on every shard."""
+    import truth
+    from noetic_tensor_b200 import ops, shard
+
+    dev = torch.device("cuda:0")
+    g = np.random.default_rng(S * 1000 + B)
+    mask = (g.uniform(0, 1, (S, B, T)) < 0.7).astype(np.float32)
+    mask[0, 0] = 0.0
+    per = (g.normal(0, 2, (S, B, T)).astype(np.float32)) * mask
+    tp, tm = torch.from_numpy(per).to(dev), torch.from_numpy(mask).to(dev)
+    host_pairs = truth.warp_seq_pairs(per.reshape(S * B, T), mask.reshape(S * B, T))
+    for use_mask in (True, False):
+        m = tm if use_mask else None
+        hp = host_pairs if use_mask else truth.warp_seq_pairs(per.reshape(S * B, T), None)
+        for r in (1, 2, 3, 4):
+            whole = ops.reduce_tokens(tp, m, r)
+            assert np.array_equal(whole.cpu().numpy().view(np.int32), truth.fold_pairs(hp, S, B, r).view(np.int32)), (r, "vs the stated order")
+            up = torch.from_numpy(g.normal(0, 1, tuple(whole.shape)).astype(np.float32)).to(dev)
+            d_whole = ops.reduce_tokens_backward((S, B, T), m, r, up).reshape(S * B, T)
+            for world in (1, 2, 3, 8):
+                pieces = []
+                for rank in range(world):
+                    b, e = shard.sequence_range(S, B, rank, world)
+                    if e > b:
+                        pieces.append(ops.reduce_tokens_partial(tp.reshape(S * B, T)[b:e].contiguous(), None if m is None else m.reshape(S * B, T)[b:e].contiguous()))
+                pairs = torch.cat(pieces).contiguous()
+                assert np.array_equal(pairs.cpu().numpy().view(np.int32), hp.view(np.int32))
+                folded = ops.reduce_tokens_fold(pairs, S, B, r)
+                assert torch.equal(folded.view(torch.int32), whole.view(torch.int32)), (r, world)
+                for rank in range(world):
+                    b, e = shard.sequence_range(S, B, rank, world)
+                    if e > b:
+                        d = ops.reduce_tokens_backward_pairs(r, S, B, T, b, e - b, pairs, None if m is None else m.reshape(S * B, T)[b:e].contiguous(), up)
+                        assert torch.equal(d.view(torch.int32), d_whole[b:e].view(torch.int32)), (r, world, rank, "backward")

@@ -94,18 +94,16 @@ def run_case(oracle, rows, V, dtype, *, ref, allow_kind, add, tau, seed, scale=2
     S, B, T = 1, 1, rows
     glp, gkl, gen = (g.uniform(-1, 1, rows).astype(np.float32) for _ in range(3))
     d = ops.row_backward(xt, f2, g_logp=to_dev(glp, None), g_kl=to_dev(gkl, None) if ref else None, g_ent=to_dev(gen, None), **kw).cpu().numpy().astype(np.float64)
+    # the reference's vocabulary mask is additive and broadcasts at the logits' rank (src/nn/rl.rs:475-486):
+    # a per-row allow-mask is the full [1,1,rows,V] additive mask with -inf at excluded tokens
     vm = None
     if addm is not None or allow is not None:
-        if (allow is not None and allow.shape[0] != 1):
-            vm = "per-row"
-        else:
-            vm = np.zeros(V)
-            if addm is not None:
-                vm = vm + addm[0]
-            if allow is not None:
-                vm = np.where(allow[0] != 0, vm, -INF)
-    if isinstance(vm, str):
-        return  # the reference API has no per-row vocabulary mask at [1,1,1,V]; covered by the f64 check below
+        per_row = allow is not None and allow.shape[0] != 1
+        vm = np.zeros((rows, V) if per_row else V)
+        if addm is not None:
+            vm = vm + addm[0]
+        if allow is not None:
+            vm = np.where((allow if per_row else allow[0]) != 0, vm, -INF)
     for dt, tol in ((oracle.F64, 2e-6), (oracle.F32, 1e-4)):
         want = np.zeros(rows * V)
         _, g1 = oracle.rl_eval(oracle.OP_TOKEN_LOG_PROBS, (S, B, T, V), dtype=dt, logits=xh, tokens=o["tokens"], vocab_mask=vm, temperature=tau, upstream=glp)
@@ -292,8 +290,6 @@ def test_grouped_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref, d
     must equal the one-block-per-row kernel's within the tolerance (it splits rows finer); sampled
     tokens may differ only on CDF boundary rows; the densest masks overflow the per-part log and
     take the scan fallback."""
-    import os
-
     from noetic_tensor_b200 import ops
 
     g = torch.Generator(device=dev())
@@ -310,13 +306,10 @@ def test_grouped_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref, d
     u = torch.rand(rows, generator=g, device=dev())
     runs = {}
     for mode in ("1", "0"):
-        os.environ["NRL_GROUPED"] = mode
-        try:
-            runs[mode] = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
-            again = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
-            given = ops.row_forward(x, ref_logits=r, allow=m, tokens=runs[mode].tokens.clamp_min(0))
-        finally:
-            os.environ.pop("NRL_GROUPED", None)
+        kw = dict(row_per_block=(mode == "0"))
+        runs[mode] = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u, **kw)
+        again = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u, **kw)
+        given = ops.row_forward(x, ref_logits=r, allow=m, tokens=runs[mode].tokens.clamp_min(0), **kw)
         assert torch.equal(again.tokens, runs[mode].tokens) and torch.equal(again.logp.view(torch.int32), runs[mode].logp.view(torch.int32))
         ok = runs[mode].status == 0
         assert torch.equal(given.logp.view(torch.int32)[ok], runs[mode].logp.view(torch.int32)[ok]), "log-prob of the given token differs from the sampled one's"
@@ -342,3 +335,66 @@ def test_grouped_forward_equals_the_per_row_kernel(oracle, rows, V, keep, ref, d
         assert_close(f.logp[idx].cpu().numpy()[same], o["logp"][same], "logp")
     # (every differing row was checked above to be one of the oracle's boundary rows)
     assert len(differ) <= max(4, rows // 50), f"{len(differ)} rows differ between the two kernels"
+
+
+def _grammar_mask_np(g, rows, V):
+    """1–4 contiguous allowed bands of width 64–4096 (clipped to V) plus 1 % random tokens: most
+    8-token vectors of a row are excluded whole, some hold one allowed token."""
+    m = g.uniform(0, 1, (rows, V)) < 0.01
+    for r in range(rows):
+        for _ in range(int(g.integers(1, 5))):
+            w = int(g.integers(64, min(4096, V) + 1))
+            s = int(g.integers(0, max(1, V - w)))
+            m[r, s:s + w] = True
+    m[:, 0] = True
+    return m.astype(np.uint8)
+
+
+@pytest.mark.parametrize("rows,V,dtype,ref,bits", [
+    (12, 4104, torch.bfloat16, True, False), (6, 32000, torch.bfloat16, True, False), (3, 128256, torch.bfloat16, True, False),
+    (12, 4104, torch.float32, True, False), (6, 32000, torch.float32, False, False), (3, 128256, torch.float32, True, False),
+    (6, 32000, torch.bfloat16, False, False),
+    (12, 4104, torch.bfloat16, True, True), (3, 128256, torch.bfloat16, True, True), (6, 32000, torch.float32, True, True)])
+def test_masked_backward_values_against_oracle(oracle, rows, V, dtype, ref, bits):
+    """d(logits) of rows under per-row grammar masks (whole excluded vectors: the backward kernels'
+    zero-fill branch, the bf16 + reference kernel and the split f32 kernel, byte and bit masks)
+    against the oracle's tape on the full [1,1,rows,V] additive −inf mask, at the reference's device
+    tolerance (src/nn/tests/gpu/rl.rs:106-123: |Δ|/(1+|ref|) ≤ 1e-4 against f32, tighter against
+    f64), excluded entries and unscored rows exactly zero."""
+    from noetic_tensor_b200 import ops
+
+    g = np.random.default_rng(7 * V + rows + int(bits))
+    x = g.normal(0, 3.0, (rows, V)).astype(np.float32)
+    xt, xh = stored(x, dtype)
+    rt = rh = None
+    if ref:
+        rt, rh = stored((x + g.normal(0, 0.1, (rows, V))).astype(np.float32), dtype)
+    allow = _grammar_mask_np(g, rows, V)
+    u = oracle.row_uniforms(V, "masked backward", rows)
+    mkw = {}
+    if bits:
+        from test_gpu_bitmask import pack_bits
+
+        mkw["allow_bits"] = pack_bits(allow).to(dev())
+    else:
+        mkw["allow"] = to_dev(allow, None)
+    o = oracle.sample_inverse_cdf(xh, 1.0, u, ref_logits=rh, allow=allow)
+    f = ops.row_forward(xt, ref_logits=rt, tokens=to_dev(o["tokens"].astype(np.int32), None), **mkw)
+    score = np.ones(rows, np.float32)
+    score[1] = 0.0
+    glp, gkl, gen = (g.uniform(-1, 1, rows).astype(np.float32) * score for _ in range(3))
+    d = ops.row_backward(xt, f, ref_logits=rt, g_logp=to_dev(glp, None), g_kl=to_dev(gkl, None) if ref else None, g_ent=to_dev(gen, None), **mkw).cpu().numpy().astype(np.float64)
+    assert (d[allow == 0] == 0).all(), "a gradient at an excluded token"
+    assert (d[1] == 0).all(), "a gradient on an unscored row"
+    vm = np.where(allow != 0, 0.0, -INF)
+    shape = (1, 1, rows, V)
+    for dt, tol in ((oracle.F64, 2e-6), (oracle.F32, 1e-4)):
+        _, want = oracle.rl_eval(oracle.OP_TOKEN_LOG_PROBS, shape, dtype=dt, logits=xh, tokens=o["tokens"], vocab_mask=vm, upstream=glp)
+        _, g3 = oracle.rl_eval(oracle.OP_ENTROPY, shape, dtype=dt, logits=xh, vocab_mask=vm, upstream=gen)
+        want = want + g3
+        if ref:
+            _, g2 = oracle.rl_eval(oracle.OP_REFERENCE_KL, shape, dtype=dt, logits=xh, ref_logits=rh, vocab_mask=vm, upstream=gkl)
+            want = want + g2
+        err = np.abs(d.ravel() - want) / (1.0 + np.abs(want))
+        assert np.nanmax(err) <= tol, f"d(logits) vs oracle dtype {dt}: {np.nanmax(err):.3e}"
+        assert not np.isnan(d).any()

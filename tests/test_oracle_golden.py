@@ -537,3 +537,14 @@ def test_inverse_cdf_oracle_values_equal_the_restated_engine(oracle):
     assert np.abs(kl - o["kl"]).max() < 1e-12
     assert np.abs(en - o["entropy"]).max() < 1e-12
     assert allow[np.arange(rows), o["tokens"]].all()
+
+
+def test_scored_log_probs_must_be_finite(oracle):
+    """src/nn/tests/rl.rs:837-846: finite scored values pass; a −inf at a scored position is named;
+    one at a masked position passes."""
+    lp = [-1.0, -np.inf, -2.0]
+    e = oracle.check_scored_finite("test", lp)
+    assert e == "test: the scored log-probability at flat position 1 is -inf (not finite)"
+    assert oracle.check_scored_finite("test", lp, [1.0, 0.0, 1.0]) is None
+    assert oracle.check_scored_finite("test", [-1.0, -3.0, -2.0]) is None
+    assert "position 2 is NaN" in oracle.check_scored_finite("test", [0.0, -1.0, np.nan, -np.inf])

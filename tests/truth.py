@@ -92,3 +92,75 @@ class Case:
     def logp_host(self):
         lp = log_softmax_host(self.logits, self.v)
         return lp[np.arange(self.n), self.tokens]
+
+
+# ---- the operand order of the library's TokenReduction kernels, for bit comparisons -------------
+# Step 1 (one warp per sequence): lane l adds the elements l, l + 32, ... in order in f32, then the
+# 32 lane sums meet in a butterfly (xor 16, 8, 4, 2, 1). Step 2: a seed's pairs folded in sequence
+# order in f64. tests/test_gpu_losses.py holds nrl_reduce_tokens to these bits on the GPU, and
+# tests/test_shard_gloo.py runs the multi-rank plumbing over them on the CPU.
+
+def warp_seq_pairs(per, mask):
+    per = np.asarray(per, dtype=np.float32)
+    n_seq, T = per.shape
+    mask = np.ones_like(per) if mask is None else np.asarray(mask, dtype=np.float32)
+    out = np.zeros((n_seq, 2), dtype=np.float32)
+    for k, x in enumerate((per, mask)):
+        pad = (-T) % 32
+        xp = np.concatenate([x, np.zeros((n_seq, pad), np.float32)], axis=1).reshape(n_seq, -1, 32)
+        lanes = np.zeros((n_seq, 32), dtype=np.float32)
+        for j in range(xp.shape[1]):
+            # a lane past the end of the sequence adds nothing (the kernel's loop simply ends)
+            live = (j * 32 + np.arange(32)) < T
+            lanes = np.where(live, (lanes + xp[:, j, :]).astype(np.float32), lanes)
+        for s in (16, 8, 4, 2, 1):
+            lanes = (lanes + lanes[:, np.arange(32) ^ s]).astype(np.float32)
+        out[:, k] = lanes[:, 0]
+    return out
+
+
+def fold_pairs(pairs, S, B, reduction):
+    pairs = np.asarray(pairs, dtype=np.float32).reshape(S, B, 2)
+    v, c = pairs[..., 0], pairs[..., 1]
+    ps = (v / np.maximum(c, np.float32(1.0))).astype(np.float32)
+    if reduction == 3:
+        return ps
+    out = np.zeros(S, dtype=np.float32)
+    for s in range(S):
+        tot = count = seq_tot = nonempty = 0.0
+        for b in range(B):
+            tot += float(v[s, b])
+            count += float(c[s, b])
+            seq_tot += float(ps[s, b])
+            nonempty += float(min(c[s, b], np.float32(1.0)))
+        if reduction == 1:
+            out[s] = np.float32(tot)
+        elif reduction == 2:
+            out[s] = np.float32(tot) / max(np.float32(count), np.float32(1.0))
+        else:
+            out[s] = np.float32(seq_tot) / max(np.float32(nonempty), np.float32(1.0))
+    return out
+
+
+def bwd_pairs(reduction, S, B, T, seq_begin, n_seq, pairs, mask, g_out):
+    pairs = np.asarray(pairs, dtype=np.float32).reshape(S, B, 2)
+    g_out = np.asarray(g_out, dtype=np.float32)
+    d = np.zeros((n_seq, T), dtype=np.float32)
+    for q in range(n_seq):
+        seq = seq_begin + q
+        s = seq // B
+        cnt = float(pairs[s, :, 1].astype(np.float64).sum())
+        non = float(np.minimum(pairs[s, :, 1], np.float32(1.0)).astype(np.float64).sum())
+        seq_scale = max(pairs[s, seq % B, 1], np.float32(1.0))
+        if reduction == 3:
+            g = g_out.reshape(-1)[seq] / seq_scale
+        elif reduction == 4:
+            g = (g_out[s] / max(np.float32(non), np.float32(1.0))) / seq_scale
+        elif reduction == 2:
+            g = g_out[s] / max(np.float32(cnt), np.float32(1.0))
+        else:
+            g = g_out[s]
+        d[q] = np.float32(g)
+    if mask is not None:
+        d = np.where(np.asarray(mask) != 0, d, np.float32(0.0))
+    return d
