@@ -441,6 +441,18 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     capi.lib()
+    l2_fetch = None
+    if args.l2_fetch_granularity:
+        # cudaLimitMaxL2FetchGranularity: a hint of this process's context (it ends with the process; nothing
+        # about the GPU itself changes). An experiment switch for profiler captures, not part of the headline.
+        import ctypes
+
+        rt = ctypes.CDLL("libcudart.so.12")
+        torch.zeros(1, device=dev)
+        rc = rt.cudaDeviceSetLimit(5, ctypes.c_size_t(args.l2_fetch_granularity))
+        now = ctypes.c_size_t(0)
+        rt.cudaDeviceGetLimit(ctypes.byref(now), 5)
+        l2_fetch = {"asked": args.l2_fetch_granularity, "rc": rc, "now": now.value}
 
     # resident batch: as many whole seeds of the config as fit, leaving headroom
     free, total = torch.cuda.mem_get_info(dev)
@@ -556,16 +568,18 @@ def run_ours(args):
         # the memory system addresses); the coarser granules are given beside it.
         nec = {g: necessary_bytes(mask, g) for g in (32, 64, 128)}
         roofline["frac_algorithmic"] = roofline["frac"]
-        roofline["necessary_bytes_per_launch"] = nec[32]
+        roofline["necessary_bytes_per_launch"] = nec[128]
         roofline["necessary_bytes_per_launch_64B_granules"] = nec[64]
-        roofline["necessary_bytes_per_launch_128B_granules"] = nec[128]
-        roofline["necessary_bytes_per_row"] = nec[32] / rows
-        roofline["achieved_necessary"] = nec[32] / (launch_ms * 1e-3) / 1e9
+        roofline["necessary_bytes_per_launch_32B_sectors"] = nec[32]
+        roofline["necessary_bytes_per_row"] = nec[128] / rows
+        roofline["achieved_necessary"] = nec[128] / (launch_ms * 1e-3) / 1e9
         roofline["frac"] = roofline["achieved_necessary"] / peak
-        roofline["note"] = ("`frac` = necessary bytes ÷ launch time ÷ peak, the necessary bytes being the byte mask whole plus every aligned 32-byte sector of logits and of "
-                            "reference that holds an allowed token (counted on the device from the masks of this run); `achieved` / `frac_algorithmic` count every logit, reference "
-                            "and mask byte once (5 B per element) although the kernel never reads logits the mask excludes; `traffic` is the DRAM traffic ncu measured on a smaller "
-                            "capture scaled by rows")
+        roofline["frac_32B_sectors"] = nec[32] / (launch_ms * 1e-3) / 1e9 / peak
+        roofline["note"] = ("`frac` = necessary bytes ÷ launch time ÷ peak. Necessary bytes: the byte mask whole plus every aligned 128-byte granule of logits and of reference that "
+                            "holds an allowed token, counted on the device from the masks of this run. 128 bytes is what this GPU's DRAM moves for an isolated 16-byte load: ncu counts "
+                            "1.05x these bytes for the launch, the same with cudaLimitMaxL2FetchGranularity at 32, 64 and 128 (profiles/row_fwd_grouped_sector_counters_4096rows.md); on "
+                            "32-byte sectors the figure would be `frac_32B_sectors`. `achieved` / `frac_algorithmic` count every logit, reference and mask byte once (5 B per element) "
+                            "although the kernel never reads logits the mask excludes; `traffic` is the DRAM traffic ncu measured on a 4096-row capture scaled by rows")
 
     # Strong scaling (the partition the path is meant for): ONE config-3 batch split along S, then B, over the
     # ranks, no collective on the data path; and the TokenReduction that spans ranks, run over NCCL and held to
@@ -730,7 +744,7 @@ def run_ours(args):
                        "storage": "bf16 logits, f32 arithmetic", "S_resident_per_gpu": s_res, "B": B, "T": T, "V": V,
                        "rows_per_gpu_per_step": rows, "cache": "inputs (tens of GB) far larger than the 126 MB L2; no flush needed", "partition": f"rows split across {world} rank(s), no collective"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "bitwise_reproducible": reproducible, "refused_rows": bad, "strong_scaling": strong,
+            "bitwise_reproducible": reproducible, "refused_rows": bad, "strong_scaling": strong, "l2_fetch_granularity": l2_fetch,
             "samplers": {"ours": "inverse CDF against one caller-supplied uniform per row, fused into the forward (what the path is defined on)",
                          "reference_arm": "the reference's Gumbel-max (one ChaCha20 u64 and two f64 logarithms per logit) on the host cores",
                          "same_algorithm_on_device": None if not extras else {"rows_per_s": extras["reference_gumbel_sampler"]["rows_per_s"],
@@ -758,6 +772,7 @@ def main():
                     help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; bitmask: the mask bit-packed; none of them is the headline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
+    ap.add_argument("--l2-fetch-granularity", type=int, default=0, help="set cudaLimitMaxL2FetchGranularity (32, 64, 128) for this process: an experiment switch for profiler captures")
     ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling measurement and the cross-rank TokenReduction check")
     ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
     args = ap.parse_args()

@@ -82,6 +82,16 @@ uint64_t nrl_launch_count(void);
  * Z = Σ e_v, the token is min{k : Σ_{v≤k} e_v > u·Z} for the row's uniform u in [0, 1).
  * A row with no allowed token or with a NaN gets token −1, NaN outputs and a non-zero status byte
  * (bit 0: no allowed token; bit 1: NaN), where the reference panics (src/nn/rl.rs:516-519).
+ *
+ * KL where the two sides exclude different tokens (src/nn/rl.rs:322-325 asks for the same
+ * vocabulary mask on both sides; the allow-mask here always applies to both): a token whose
+ * policy logit is −inf contributes 0 whatever the reference holds, as in the reference
+ * (`mask_fill(zero_p, 0)`). A token the reference excludes (z_ref = −inf) while the policy's logit
+ * is finite makes the row's KL non-finite, as in the reference: +inf while π_v > 0 in f32, NaN once
+ * π_v has underflowed to 0 (0·inf). The two underflow at different points: the reference's
+ * `exp(logp)` at logp < −103.97 (f32 denormals), this library's flush-to-zero exponential at
+ * z_v − m < −87.34; in between the reference gives +inf and this library NaN. The backward of such
+ * a row is NaN in every entry (KL enters every entry of the gradient).
  */
 enum {
     NRL_FWD_SAMPLE = 1u << 0,  /* draw tokens (needs `uniforms`, writes `tokens`) */

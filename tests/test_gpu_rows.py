@@ -398,3 +398,40 @@ def test_masked_backward_values_against_oracle(oracle, rows, V, dtype, ref, bits
         err = np.abs(d.ravel() - want) / (1.0 + np.abs(want))
         assert np.nanmax(err) <= tol, f"d(logits) vs oracle dtype {dt}: {np.nanmax(err):.3e}"
         assert not np.isnan(d).any()
+
+
+@pytest.mark.parametrize("rows,V", [(4, 64), (4, 4096), (3000, 4096)])
+def test_kl_when_the_reference_excludes_a_token_the_policy_keeps(oracle, rows, V):
+    """categorical_kl with a token excluded on one side only (src/nn/rl.rs:322-325): excluded by the
+    policy → contributes 0; excluded by the reference alone → KL +inf while the policy's
+    probability is positive, NaN (0·inf) once it has underflowed, exactly as Cpu(Reference) gives
+    on the same inputs. Between the two underflow points (the reference's exp at −103.97, this
+    library's flush-to-zero exponential at −87.34) both are non-finite: +inf there, NaN here."""
+    from noetic_tensor_b200 import ops
+
+    z = np.full((rows, V), -1.0, np.float32)
+    z[:, 0] = 0.0
+    zr = z.copy()
+    zr[:, 5] = -INF
+    shape = (1, 1, 4, V)
+    for value, same_as_reference in ((-200.0, True), (-1.0, True), (-INF, True), (-95.0, False)):
+        za = z.copy()
+        za[:, 5] = value
+        want = oracle.rl_eval(oracle.OP_KL, shape, dtype=oracle.F32, logits=za[:4], ref_logits=zr[:4])
+        for dtype in (torch.float32, torch.bfloat16):
+            got = ops.row_forward(to_dev(za, dtype), ref_logits=to_dev(zr, dtype)).kl.cpu().numpy()
+            assert (got == got[0]).all() or np.isnan(got).all()
+            if same_as_reference:
+                assert np.array_equal(np.isnan(got[:4]), np.isnan(want)) and np.array_equal(np.isinf(got[:4]), np.isinf(want)), (value, got[:4], want)
+                if np.isfinite(want).all():
+                    assert_close(got[:4], want, "kl")
+            else:
+                assert np.isinf(want).all() and not np.isfinite(got).any()
+    # the backward of a row whose KL is NaN is NaN throughout; the row beside it is untouched
+    za = z.copy()
+    za[0, 5] = -200.0
+    zr2 = z.copy()
+    zr2[0, 5] = -INF
+    f = ops.row_forward(to_dev(za, None), ref_logits=to_dev(zr2, None))
+    d = ops.row_backward(to_dev(za, None), f, ref_logits=to_dev(zr2, None), g_kl=to_dev(np.ones(rows, np.float32), None)).cpu().numpy()
+    assert np.isnan(d[0]).sum() >= V - 2 and np.isfinite(d[1:]).all()
