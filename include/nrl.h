@@ -460,6 +460,50 @@ int nrl_group_advantages(uint64_t groups, uint32_t n, uint32_t norm_std, double 
  * reference's sampler does (src/nn/rl.rs:516-519). */
 int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64_t* first_bad_row, uint32_t* bits);
 
+/* ---------------------------------------------------------------------------------------------
+ * Readout-fused row statistics: the step before the path taken into it. The reference computes
+ * logits = hidden · W with `Decoder::head` (src/nn/decoder.rs:270-279; `Linear` holds W as
+ * [in, out] = [d, V], src/nn/linear.rs:1-3, 51-58), on CUDA through `hgemm_bf16_f32acc`
+ * (src/tensor/cuda/half_gemm.rs:32-168: operands rounded to bf16, f32 accumulators,
+ * mma.sync.m16n8k16), writes the [rows, V] logits and then reads them back in token_log_probs /
+ * categorical_entropy (src/nn/rl.rs:134-141, 405-414). nrl_readout_fwd does the product on the
+ * B200 tensor cores (tcgen05.mma, bf16 operands, f32 accumulators in tensor memory, TMA-fed) and
+ * folds each finished 128 × 256 tile of logits into the rows' maximum, log-sum-exp and entropy
+ * sums straight from tensor memory, so the logits are never written or re-read:
+ *   rowstats[r] = (m, ln Z, 0, 0), entropy[r] = ln Z − Σ e_v (z_v − m) / Z,
+ *   logp[r] = z_token − m − ln Z for the given token (NRL_FWD_TOKENS_IN semantics),
+ * with z = the f32 accumulators (the reference's logits are f32 too), or, with
+ * NRL_READOUT_ROUND_BF16, z rounded to bf16 first — what a bf16 logits tensor handed to
+ * nrl_row_fwd would hold. `hidden` is bf16 [rows, d], `weights` bf16 [d, V] (the reference's
+ * layout) or, with NRL_READOUT_W_VD, [V, d]; d and V multiples of 8, both 16-byte aligned.
+ * `logits_out` (optional, bf16 [rows, V]) receives the rounded logits, for comparisons.
+ * Needs compute capability 10.x (NRL_E_UNSUPPORTED otherwise) and
+ * nrl_readout_workspace_bytes(rows, V) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
+ * a NaN, bit 2 the kernel gave up a bounded wait (an internal error: outputs of that row are NaN).
+ * Results are bitwise reproducible run to run. */
+enum { NRL_READOUT_W_VD = 1u << 0, NRL_READOUT_ROUND_BF16 = 1u << 1 };
+
+typedef struct nrl_readout_args {
+    uint32_t struct_size;
+    uint32_t flags;          /* NRL_READOUT_* */
+    uint32_t V;              /* vocabulary size, a multiple of 8 */
+    uint32_t d;              /* model width, a multiple of 8 */
+    uint64_t rows;           /* S·B·T */
+    nrl_devptr hidden;       /* bf16 [rows, d] */
+    nrl_devptr weights;      /* bf16 [d, V], or [V, d] with NRL_READOUT_W_VD */
+    nrl_devptr tokens;       /* i32 [rows] given tokens, or 0 */
+    nrl_devptr logp;         /* out f32 [rows] (needs tokens), or 0 */
+    nrl_devptr entropy;      /* out f32 [rows], or 0 */
+    nrl_devptr rowstats;     /* out f32 [rows, 4], or 0 */
+    nrl_devptr status;       /* out u8 [rows], or 0 */
+    nrl_devptr logits_out;   /* out bf16 [rows, V], or 0 */
+    nrl_devptr workspace;    /* scratch */
+    uint64_t workspace_bytes;
+} nrl_readout_args;
+
+uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V);
+int nrl_readout_fwd(const nrl_readout_args* args, nrl_stream stream);
+
 /* check_scored_finite (src/nn/rl.rs:204-211), the check the reference's losses run in debug
  * builds (debug_check, :213-221, called from policy_gradient_loss :230, clipped_policy_loss
  * :268-269 and kl_estimate :386-387): every scored log-probability is finite. `logp` is f32 [n]

@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnrl.so")
 SOURCES = ["nrl_api.cu", "nrl_bits.cu"]  # the second compiles the row kernels again for bit-packed masks
-HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh", "lane_ops.cuh", "row_api.inl"]
+HEADERS = ["common.cuh", "row_fwd.cuh", "row_fwd_kernels.cuh", "row_fwd_group.cuh", "row_bwd.cuh", "token_ops.cuh", "ce_ops.cuh", "gumbel.cuh", "host_pack.cuh", "lane_ops.cuh", "readout.cuh", "row_api.inl"]
 INCLUDE = os.path.join(os.path.dirname(HERE), "include", "nrl.h")
 
 

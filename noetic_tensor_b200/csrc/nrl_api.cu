@@ -13,6 +13,7 @@
 #include "gumbel.cuh"
 #include "host_pack.cuh"
 #include "lane_ops.cuh"
+#include "readout.cuh"
 
 #define NRL_STR2(x) #x
 #define NRL_STR(x) NRL_STR2(x)
@@ -465,4 +466,100 @@ extern "C" int nrl_check_scored_finite(nrl_devptr logp, nrl_devptr mask, uint64_
         memcpy(value, &b, sizeof b);
     }
     return NRL_E_NOT_FINITE;
+}
+
+// ---- readout-fused row statistics (tcgen05) ---------------------------------------------------------
+
+// Column ranges per row block: the count (at most 16, each range at least 8 tiles) that fills the
+// 148 SMs' waves best; a function of (rows, V) only, so results do not depend on anything else.
+static uint32_t readout_nsplit(uint64_t rows, uint32_t V) {
+    const uint64_t rb = (rows + kRoBM - 1) / kRoBM;
+    const uint32_t tiles = (V + kRoBN - 1) / kRoBN;
+    uint32_t best = 1;
+    double best_eff = 0.0;
+    for (uint32_t s = 1; s <= 16 && (s == 1 || tiles / s >= 8); s++) {
+        const uint64_t ctas = rb * s;
+        const double eff = (double)ctas / (148.0 * (double)((ctas + 147) / 148));
+        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V) {
+    if (rows == 0 || V == 0) return 0;
+    return rows * readout_nsplit(rows, V) * kRoPartFloats * sizeof(float);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup: the library links no libcuda.
+static int encode_bf16_2d(CUtensorMap* map, uint64_t base, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+    static std::atomic<void*> fn{nullptr};
+    void* f = fn.load(std::memory_order_acquire);
+    if (!f) {
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q);
+        if (e != cudaSuccess) return (int)e;
+        if (q != cudaDriverEntryPointSuccess || !f) return NRL_E_UNSUPPORTED;
+        fn.store(f, std::memory_order_release);
+    }
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {inner * 2};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = ((EncodeTiledFn)f)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NRL_OK : NRL_E_BAD_ARG;
+}
+
+extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
+    if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16)) return NRL_E_BAD_ARG;
+    // TMA wants 16-byte aligned bases and row pitches
+    if (a->V % 8 != 0 || a->d % 8 != 0 || ((a->hidden | a->weights) & 15u)) return NRL_E_UNSUPPORTED;
+    if ((a->tokens & 3u) || (a->logp & 3u) || (a->entropy & 3u) || (a->rowstats & 15u) || (a->logits_out & 3u) || (a->workspace & 15u)) return NRL_E_BAD_ARG;
+    if (a->logp && !a->tokens) return NRL_E_BAD_ARG;
+    int dev = 0, cc_major = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return (int)e;
+    if (cc_major != 10) return NRL_E_UNSUPPORTED;  // tcgen05 / tensor memory
+    ReadoutParams p;
+    memset(&p, 0, sizeof p);
+    p.rows = a->rows;
+    p.V = a->V;
+    p.d = a->d;
+    p.tiles = (a->V + kRoBN - 1) / kRoBN;
+    p.nsplit = readout_nsplit(a->rows, a->V);
+    const uint64_t rb = (a->rows + kRoBM - 1) / kRoBM;
+    if (rb * p.nsplit > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    p.row_blocks = (uint32_t)rb;
+    p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
+    p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
+    p.tokens = (const int32_t*)a->tokens;
+    if (!a->workspace || a->workspace_bytes < nrl_readout_workspace_bytes(a->rows, a->V)) return NRL_E_WORKSPACE;
+    p.parts = (float*)a->workspace;
+    p.logits_out = (uint16_t*)a->logits_out;
+    CUtensorMap mx, mw;
+    int rc = encode_bf16_2d(&mx, a->hidden, a->d, a->rows, kRoBK, kRoBM);
+    if (rc) return rc;
+    rc = p.w_is_vd ? encode_bf16_2d(&mw, a->weights, a->d, a->V, kRoBK, kRoBN) : encode_bf16_2d(&mw, a->weights, a->V, a->d, 64, kRoBK);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned grid = (unsigned)(rb * p.nsplit);
+    if (p.round_bf16) {
+        e = cudaFuncSetAttribute(readout_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        readout_fwd_kernel<true><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+    } else {
+        e = cudaFuncSetAttribute(readout_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        readout_fwd_kernel<false><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+    }
+    rc = after_launch();
+    if (rc) return rc;
+    readout_finish_kernel<<<(unsigned)((a->rows + 127) / 128), 128, 0, st>>>(a->rows, p.nsplit, p.parts, p.tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats, (uint8_t*)a->status);
+    return after_launch();
 }

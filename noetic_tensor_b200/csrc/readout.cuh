@@ -1,0 +1,394 @@
+// Readout-fused row statistics: logits = hidden [rows, d] · W [d, V] on the tensor cores, reduced
+// to the per-row quantities of the row forward (maximum, log-sum-exp, entropy sum, the given
+// token's logit) while the accumulators are still in tensor memory. The [rows, V] logits are
+// never written (an optional bf16 copy exists for comparisons).
+//
+// What it replaces: `Decoder::head` (src/nn/decoder.rs:270-273, a `Linear` x · W with W held as
+// [in, out], src/nn/linear.rs:1-3, 51-58) run as `hgemm_bf16_f32acc` (src/tensor/cuda/half_gemm.rs:
+// 32-168: bf16 operands, f32 accumulators, 64×64 tiles of mma.sync.m16n8k16) followed by
+// token_log_probs / categorical_entropy on the logits it wrote (src/nn/rl.rs:134-141, 405-414).
+//
+// Shape of the kernel (sm_100a only):
+//   - a CTA owns 128 consecutive rows and a contiguous range of 256-column vocabulary tiles;
+//   - one thread issues TMA loads (cp.async.bulk.tensor.2d, 128-byte swizzle, no multicast) of a
+//     [128 × 64] tile of the hidden states and a [64 × 256] tile of W per pipeline stage, four
+//     stages deep, completion signalled on mbarriers by byte count;
+//   - one thread issues tcgen05.mma (M 128, N 256, K 16, bf16 → f32) from shared-memory
+//     descriptors into one of two 256-column accumulators in tensor memory, and
+//     tcgen05.commit hands finished stages back to the loader and finished tiles to the epilogue;
+//   - four epilogue warps read a finished accumulator with tcgen05.ld (thread = row, 32 columns
+//     at a time) and fold it into the row's running (m, S = Σe, W = Σe·(z − m)) in column order
+//     while the next tile's products run into the other accumulator.
+// A row's result over the CTA's column range goes to scratch; a second small kernel merges the
+// ranges in index order in f64 (the row kernels' finalisation) and writes the outputs. Every sum
+// has a fixed order: results are bitwise reproducible.
+//
+// Every wait (mbarrier) is bounded by a clock: after kWaitLimitNs without progress a role stops,
+// raises the CTA's abort flag (the other roles see it at their next wait), the loader waits,
+// again bounded, for its copies in flight, tensor memory is released and the rows of the CTA get
+// status bit 2 ("gave up"). Nothing spins forever.
+#pragma once
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace nrl {
+
+constexpr int kRoBM = 128;       // rows per CTA = lanes of tensor memory
+constexpr int kRoBN = 256;       // vocabulary columns per tile = N of one tcgen05.mma
+constexpr int kRoBK = 64;        // bf16 elements of K per stage = one 128-byte swizzle row
+constexpr int kRoStages = 4;
+constexpr int kRoThreads = 192;  // warp 0: loader, warp 1: mma + tensor-memory owner, warps 2-5: epilogue
+constexpr uint32_t kRoABytes = kRoBM * kRoBK * 2;  // 16 KB
+constexpr uint32_t kRoBBytes = kRoBN * kRoBK * 2;  // 32 KB
+constexpr uint32_t kRoStageBytes = kRoABytes + kRoBBytes;
+constexpr uint32_t kRoSmemBytes = kRoStages * kRoStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait here
+constexpr int kRoPartFloats = 4;  // (m, S, W, token logit) per row and column range
+
+struct ReadoutParams {
+    uint64_t rows;
+    uint32_t V, d;
+    uint32_t tiles;        // ceil(V / 256)
+    uint32_t nsplit;       // column ranges per row block
+    uint32_t row_blocks;   // ceil(rows / 128)
+    uint32_t w_is_vd;      // W given as [V, d] (K-major B) instead of [d, V] (N-major B)
+    uint32_t round_bf16;   // fold the logits after rounding them to bf16 (what a bf16 logits tensor would hold)
+    const int32_t* tokens; // [rows] or null
+    float* parts;          // scratch [rows, nsplit, 4]
+    uint16_t* logits_out;  // optional bf16 [rows, V]
+};
+
+// ---- raw PTX wrappers -----------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: false when the CTA aborted or the limit passed (then the abort flag is raised).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* abort_flag, unsigned long long limit_ns = kWaitLimitNs) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 1;; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 0u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > limit_ns) {
+                *abort_flag = 1u;
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) { asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// 32 consecutive f32 columns of this thread's lane
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t r[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
+          "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a 128-byte-swizzled tile (version 1, layout type 2), offsets in bytes.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) | ((uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ float round_through_bf16(float x) {
+    uint32_t u = __float_as_uint(x);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return x;  // NaN stays NaN
+    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;  // nearest, ties to even (src/tensor/half.rs:16-27)
+    return __uint_as_float(u);
+}
+
+// the range of vocabulary tiles of column range `split`
+__device__ __forceinline__ void readout_tile_range(const ReadoutParams& p, uint32_t split, uint32_t& t0, uint32_t& t1) {
+    const uint32_t per = (p.tiles + p.nsplit - 1) / p.nsplit;
+    t0 = min(split * per, p.tiles);
+    t1 = min(t0 + per, p.tiles);
+}
+
+template <bool ROUND>
+__global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ReadoutParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
+    const uint32_t a_base = smem_base, b_base = smem_base + kRoStages * kRoABytes;
+    const uint32_t bars = smem_base + kRoStages * kRoStageBytes;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * kRoStages, bar_acc_full = bars + 16 * kRoStages, bar_acc_empty = bar_acc_full + 16, bar_done = bar_acc_empty + 16;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t split = blockIdx.x / p.row_blocks, rb = blockIdx.x % p.row_blocks;
+    uint32_t t0, t1;
+    readout_tile_range(p, split, t0, t1);
+    const uint32_t kchunks = (p.d + kRoBK - 1) / kRoBK;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        for (int s = 0; s < kRoStages; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full + 8 * a, 1);
+            mbar_init(bar_acc_empty + 8 * a, 4);
+        }
+        mbar_init(bar_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {  // the whole warp allocates all 512 columns: two 256-column accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_addr(&tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        tc_fence_before();
+    }
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        // ---- loader ------------------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0, issued = 0;
+            bool ok = true;
+            for (uint32_t t = t0; t < t1 && ok; t++) {
+                for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
+                    const uint32_t s = it % kRoStages;
+                    if (!mbar_wait(bar_empty + 8 * s, ((it / kRoStages) & 1u) ^ 1u, &abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(bar_full + 8 * s, kRoStageBytes);
+                    tma_load_2d(a_base + s * kRoABytes, &map_x, (int32_t)(kc * kRoBK), (int32_t)(rb * kRoBM), bar_full + 8 * s);
+                    if (p.w_is_vd) {
+                        tma_load_2d(b_base + s * kRoBBytes, &map_w, (int32_t)(kc * kRoBK), (int32_t)(t * kRoBN), bar_full + 8 * s);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kRoBN / 64; j++)  // W [d, V]: four [64 k × 64 n] boxes, n contiguous
+                            tma_load_2d(b_base + s * kRoBBytes + j * (kRoBK * 128), &map_w, (int32_t)(t * kRoBN + j * 64), (int32_t)(kc * kRoBK), bar_full + 8 * s);
+                    }
+                    issued = it + 1;
+                }
+            }
+            if (!ok || abort_flag) {
+                // copies still in flight write this CTA's shared memory: wait for them (bounded) before the CTA may end
+                const uint32_t first = issued > (uint32_t)kRoStages ? issued - kRoStages : 0u;
+                for (uint32_t j = first; j < issued; j++) {
+                    volatile uint32_t never = 0u;
+                    mbar_wait(bar_full + 8 * (j % kRoStages), (j / kRoStages) & 1u, &never, 20000000ull);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue ---------------------------------------------------------------------
+        if (lane == 0) {
+            // instruction descriptor: D f32, A and B bf16, A K-major, B K-major ([V, d]) or N-major ([d, V]), N 256, M 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.w_is_vd ? 0u : 1u) << 16) | ((uint32_t)(kRoBN >> 3) << 17) | ((uint32_t)(kRoBM >> 4) << 24);
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t t = t0; t < t1 && ok; t++) {
+                const uint32_t n = t - t0, acc = n & 1u;
+                if (!mbar_wait(bar_acc_empty + 8 * acc, ((n >> 1) & 1u) ^ 1u, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + acc * kRoBN;
+                for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
+                    const uint32_t s = it % kRoStages;
+                    if (!mbar_wait(bar_full + 8 * s, (it / kRoStages) & 1u, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = a_base + s * kRoABytes, b_addr = b_base + s * kRoBBytes;
+#pragma unroll
+                    for (int k = 0; k < kRoBK / 16; k++) {
+                        // A, and B as [V, d]: K-major, rows of 128 bytes, groups of 8 rows 1024 bytes apart; 16 elements of K = 32 bytes along the row
+                        const uint64_t da = smem_desc_sw128(a_addr + k * 32, 16, 1024);
+                        // B as [d, V]: N-major, 64 columns contiguous, column blocks 8 KB apart, groups of 8 k-rows 1024 bytes apart; 16 k-rows = 2048 bytes
+                        const uint64_t db = p.w_is_vd ? smem_desc_sw128(b_addr + k * 32, 16, 1024) : smem_desc_sw128(b_addr + k * 2048, kRoBK * 128, 1024);
+                        tc_mma_bf16(d_tmem, da, db, idesc, (kc | (uint32_t)k) != 0u);
+                    }
+                    tc_commit(bar_empty + 8 * s);  // the stage is free once these products have read it
+                }
+                if (ok) tc_commit(bar_acc_full + 8 * acc);
+            }
+            // before tensor memory may be released every product issued above must have finished
+            tc_commit(bar_done);
+        }
+    } else {
+        // ---- epilogue: thread = row ------------------------------------------------------------------
+        const uint32_t quarter = (uint32_t)warp & 3u;  // the 32 lanes of tensor memory this warp may read
+        const uint32_t r_in_block = quarter * 32u + (uint32_t)lane;
+        const uint64_t row = (uint64_t)rb * kRoBM + r_in_block;
+        const bool live = row < p.rows;
+        const int32_t tok = (live && p.tokens) ? p.tokens[row] : -1;
+        float m = NRL_NEG_INF, S = 0.f, W = 0.f, ztok = __int_as_float(0x7fc00000);  // NaN: "the token is not in this range"
+        bool ok = true;
+        for (uint32_t t = t0; t < t1 && ok; t++) {
+            const uint32_t n = t - t0, acc = n & 1u;
+            if (!mbar_wait(bar_acc_full + 8 * acc, (n >> 1) & 1u, &abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem + ((quarter * 32u) << 16) + acc * kRoBN;
+            float ts = 0.f, tw = 0.f;  // this tile's sums at the running maximum
+#pragma unroll 1
+            for (int c = 0; c < kRoBN / 32; c++) {
+                uint32_t r[32];
+                tc_ld32(taddr + c * 32, r);
+                tc_wait_ld();
+                const uint32_t col0 = t * kRoBN + c * 32;
+                float z[32];
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float v = __uint_as_float(r[i]);
+                    if (ROUND) v = round_through_bf16(v);
+                    z[i] = v;
+                }
+                if (col0 + 32 > p.V) {  // past the vocabulary (TMA filled zeros there): exclude
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (col0 + i >= p.V) z[i] = -FLT_MAX;
+                }
+                if (p.logits_out && live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        if (col0 + i + 1 < p.V) {
+                            const uint32_t lo = __float_as_uint(round_through_bf16(z[i])) >> 16, hi = __float_as_uint(round_through_bf16(z[i + 1])) & 0xffff0000u;
+                            *reinterpret_cast<uint32_t*>(p.logits_out + row * p.V + col0 + i) = lo | hi;
+                        } else if (col0 + i < p.V) {
+                            p.logits_out[row * p.V + col0 + i] = (uint16_t)(__float_as_uint(round_through_bf16(z[i])) >> 16);
+                        }
+                    }
+                }
+                if (tok >= (int32_t)col0 && tok < (int32_t)(col0 + 32)) {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if ((int32_t)(col0 + i) == tok) ztok = z[i];
+                }
+                float cm = fmax3_nan(z[0], z[1], z[2]);
+#pragma unroll
+                for (int i = 3; i < 31; i += 2) cm = fmax3_nan(cm, z[i], z[i + 1]);
+                cm = fmax_nan(cm, z[31]);
+                cm = fmax_nan(cm, -FLT_MAX);  // a −inf logit is folded as −FLT_MAX: exp underflows to 0 either way and 0·inf cannot appear
+                if (!(cm <= m)) {  // a new maximum (or a NaN): move the sums
+                    if (m != NRL_NEG_INF) {
+                        const float dm = m - cm, sc = expf(dm);
+                        W = (W + S * dm) * sc;
+                        S *= sc;
+                        tw = (tw + ts * dm) * sc;
+                        ts *= sc;
+                    }
+                    m = cm;
+                }
+                // three levels of sums (32 columns, a tile, the range) keep the rounding of the long f32 sums small
+                float cs = 0.f, cw = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    const float tt = fmaxf(z[i], -FLT_MAX) - m;
+                    const float e = ex2_approx(tt * kLog2e);
+                    cs += e;
+                    cw = fmaf(e, tt, cw);
+                }
+                ts += cs;
+                tw += cw;
+            }
+            S += ts;
+            W += tw;
+            // this accumulator may be overwritten once all four epilogue warps are done with it
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty + 8 * acc);
+        }
+        if (live) {
+            float4 out = make_float4(m, S, W, ztok);
+            if (!ok || abort_flag) out = make_float4(0.f, -1.f, 0.f, 0.f);  // S = −1 marks "gave up" for the merge
+            reinterpret_cast<float4*>(p.parts)[row * p.nsplit + split] = out;
+        }
+    }
+
+    // ---- teardown ------------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (lane == 0) {
+            // all products have finished (on an aborted CTA the wait gives up after 20 ms)
+            volatile uint32_t never = 0u;
+            mbar_wait(bar_done, 0u, &never, 20000000ull);
+        }
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+}
+
+// Merge the column ranges of each row in index order (f64, as the row kernels finalise) and write
+// the outputs: rowstats (m, ln Z, 0, 0), entropy = ln Z − W / Z, logp = z_tok − m − ln Z.
+__global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const float* parts, const int32_t* tokens, float* logp, float* entropy, float* rowstats, uint8_t* status) {
+    const uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    const float4* pr = reinterpret_cast<const float4*>(parts) + row * nsplit;
+    float m = NRL_NEG_INF;
+    for (uint32_t s = 0; s < nsplit; s++) m = fmax_nan(m, pr[s].x);
+    double Z = 0.0, Wt = 0.0;
+    float ztok = __int_as_float(0x7fc00000);
+    for (uint32_t s = 0; s < nsplit; s++) {
+        const float4 a = pr[s];
+        if (a.x != NRL_NEG_INF && a.y > 0.f) {
+            const double dm = (double)a.x - (double)m, c = (double)expf(a.x - m);
+            Z += c * (double)a.y;
+            Wt += c * ((double)a.z + (double)a.y * dm);
+        }
+        if (a.w == a.w) ztok = a.w;
+    }
+    uint32_t st = 0u;
+    for (uint32_t s = 0; s < nsplit; s++)
+        if (pr[s].y < 0.f) st |= 4u;
+    if (m != m) st |= 2u;
+    else if (m == NRL_NEG_INF || m <= -FLT_MAX) st |= 1u;
+    const double lnZ = log(Z);
+    if (st) {
+        const float nan = __int_as_float(0x7fc00000);
+        if (logp) logp[row] = nan;
+        if (entropy) entropy[row] = nan;
+        if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(nan, nan, nan, nan);
+    } else {
+        if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(m, (float)lnZ, 0.f, 0.f);
+        if (entropy) entropy[row] = (float)(lnZ - Wt / Z);
+        if (logp && tokens) {
+            const int32_t tk = tokens[row];
+            // a token outside [0, V) has no logit: NaN; an excluded one (−inf logit) has log-prob −inf
+            logp[row] = (ztok != ztok) ? ztok : (ztok <= -FLT_MAX ? NRL_NEG_INF : (ztok - m) - (float)lnZ);
+            (void)tk;
+        }
+    }
+    if (status) status[row] = (uint8_t)st;
+}
+
+}  // namespace nrl

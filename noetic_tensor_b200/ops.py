@@ -375,6 +375,49 @@ def reduce_tokens_backward_pairs(reduction, S, B, T, seq_begin, n_seq, pairs, ma
     return d
 
 
+class Readout:
+    """Outputs of nrl_readout_fwd (fields are None when not requested)."""
+
+    __slots__ = ("logp", "entropy", "rowstats", "status", "logits")
+
+
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None):
+    """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
+    `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
+    `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
+    the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]."""
+    dev = hidden.device
+    if dev.type != "cuda":
+        raise ValueError("readout_forward needs CUDA tensors: this library has no CPU path")
+    rows, d = hidden.shape
+    V = weights.shape[0] if weights_are_vd else weights.shape[1]
+    _need(hidden, torch.bfloat16, (rows, d), "hidden", dev)
+    _need(weights, torch.bfloat16, (V, d) if weights_are_vd else (d, V), "weights", dev)
+    a = capi.ReadoutArgs()
+    a.struct_size = C.sizeof(a)
+    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0)
+    a.V, a.d, a.rows = V, d, rows
+    a.hidden, a.weights = _p(hidden), _p(weights)
+    out = Readout()
+    out.logp = None
+    if tokens is not None:
+        _need(tokens, torch.int32, (rows,), "tokens", dev)
+        a.tokens = _p(tokens)
+        out.logp = torch.empty(rows, dtype=torch.float32, device=dev)
+    out.entropy = torch.empty(rows, dtype=torch.float32, device=dev)
+    out.rowstats = torch.empty(rows, 4, dtype=torch.float32, device=dev)
+    out.status = torch.empty(rows, dtype=torch.uint8, device=dev)
+    out.logits = torch.empty(rows, V, dtype=torch.bfloat16, device=dev) if want_logits else None
+    a.logp, a.entropy, a.rowstats, a.status, a.logits_out = _p(out.logp), _p(out.entropy), _p(out.rowstats), _p(out.status), _p(out.logits)
+    need = capi.lib().nrl_readout_workspace_bytes(rows, V)
+    if workspace is None or workspace.numel() * workspace.element_size() < need:
+        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    a.workspace, a.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_readout_fwd(C.byref(a), _stream(dev)), "nrl_readout_fwd")
+    return out
+
+
 def row_sum(logits):
     """Σ_v logits[r, v] per row in f32 (nrl_row_sum)."""
     dev = logits.device
