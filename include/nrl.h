@@ -478,7 +478,7 @@ int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64
  * layout) or, with NRL_READOUT_W_VD, [V, d]; d and V multiples of 8, both 16-byte aligned.
  * `logits_out` (optional, bf16 [rows, V]) receives the rounded logits, for comparisons.
  * Needs compute capability 10.x (NRL_E_UNSUPPORTED otherwise) and
- * nrl_readout_workspace_bytes(rows, V) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
+ * nrl_readout_workspace_bytes(rows, V, d) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
  * a NaN, bit 2 the kernel gave up a bounded wait (an internal error: outputs of that row are NaN).
  * Results are bitwise reproducible run to run. */
 enum { NRL_READOUT_W_VD = 1u << 0, NRL_READOUT_ROUND_BF16 = 1u << 1 };
@@ -501,7 +501,7 @@ typedef struct nrl_readout_args {
     uint64_t workspace_bytes;
 } nrl_readout_args;
 
-uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V);
+uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d);
 int nrl_readout_fwd(const nrl_readout_args* args, nrl_stream stream);
 
 /* check_scored_finite (src/nn/rl.rs:204-211), the check the reference's losses run in debug

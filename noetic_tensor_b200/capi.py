@@ -127,7 +127,7 @@ SYMBOLS = {
     "nrl_host_pack_bits": (C.c_int, [u64, u32, C.c_void_p, C.c_void_p, u32]),
     "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
     "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
-    "nrl_readout_workspace_bytes": (u64, [u64, u32]),
+    "nrl_readout_workspace_bytes": (u64, [u64, u32, u32]),
     "nrl_readout_fwd": (C.c_int, [C.POINTER(ReadoutArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
     "nrl_check_scored_finite": (C.c_int, [ptr, ptr, u64, ptr, C.c_void_p, C.POINTER(u64), C.POINTER(f32)]),

@@ -52,6 +52,7 @@ struct ReadoutParams {
     uint32_t tiles;        // ceil(V / 256)
     uint32_t nsplit;       // column ranges per row block
     uint32_t row_blocks;   // ceil(rows / 128)
+    uint32_t group_blocks; // row blocks whose CTAs (all column ranges) are launched next to each other
     uint32_t w_is_vd;      // W given as [V, d] (K-major B) instead of [d, V] (N-major B)
     uint32_t round_bf16;   // fold the logits after rounding them to bf16 (what a bf16 logits tensor would hold)
     const int32_t* tokens; // [rows] or null
@@ -153,7 +154,13 @@ __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid
     __shared__ volatile uint32_t abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t split = blockIdx.x / p.row_blocks, rb = blockIdx.x % p.row_blocks;
+    // CTAs that run at the same time should share operands in L2: consecutive CTAs cover a group of
+    // row blocks (their hidden states stay in L2) times every column range (a range's W tiles are
+    // fetched once for the whole group).
+    const uint32_t group = blockIdx.x / (p.group_blocks * p.nsplit);
+    const uint32_t in_group = min(p.group_blocks, p.row_blocks - group * p.group_blocks);
+    const uint32_t within = blockIdx.x - group * p.group_blocks * p.nsplit;
+    const uint32_t split = within / in_group, rb = group * p.group_blocks + within % in_group;
     uint32_t t0, t1;
     readout_tile_range(p, split, t0, t1);
     const uint32_t kchunks = (p.d + kRoBK - 1) / kRoBK;

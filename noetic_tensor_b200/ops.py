@@ -409,9 +409,8 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     out.status = torch.empty(rows, dtype=torch.uint8, device=dev)
     out.logits = torch.empty(rows, V, dtype=torch.bfloat16, device=dev) if want_logits else None
     a.logp, a.entropy, a.rowstats, a.status, a.logits_out = _p(out.logp), _p(out.entropy), _p(out.rowstats), _p(out.status), _p(out.logits)
-    need = capi.lib().nrl_readout_workspace_bytes(rows, V)
-    if workspace is None or workspace.numel() * workspace.element_size() < need:
-        workspace = torch.empty(need, dtype=torch.uint8, device=dev)
+    if workspace is None:
+        workspace = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d), dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_readout_fwd(C.byref(a), _stream(dev)), "nrl_readout_fwd")

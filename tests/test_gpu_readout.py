@@ -1,0 +1,110 @@
+"""The readout-fused statistics (nrl_readout_fwd: tcgen05 product + online-softmax epilogue) through
+the C ABI.
+
+The product: the optional bf16 copy of the logits against an f64 product of the same bf16
+operands (a bf16 value may land on the neighbouring representable number: f32 accumulation order).
+The statistics: with NRL_READOUT_ROUND_BF16 the kernel folds exactly the logits it wrote, so
+log-prob, entropy and row statistics are held to the CPU oracle and to nrl_row_fwd on those logits
+at the path's tolerance (1e-5 relative or 1e-6 absolute); without rounding they are held to the f64
+statistics of the f64 product within 5e-5 relative, the spread an f32-accumulated product of
+d = 4096 terms leaves in a logit (the reference's own product, src/tensor/cuda/half_gemm.rs:32-168,
+accumulates in f32 in another order). What it replaces: src/nn/decoder.rs:270-279 followed by
+src/nn/rl.rs:134-141, 405-414."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def close(got, want, what, rel=1e-5, abs_=1e-6):
+    got, want = np.asarray(got, np.float64), np.asarray(want, np.float64)
+    err = np.abs(got - want)
+    ok = (err <= abs_) | (err <= rel * np.abs(want)) | (got == want)
+    assert ok.all(), f"{what}: {np.count_nonzero(~ok)} of {ok.size} outside tolerance, worst |Δ| {err.max():.3e}"
+
+
+def make(rows, d, V, seed):
+    g = torch.Generator(device=dev())
+    g.manual_seed(seed)
+    x = torch.randn(rows, d, generator=g, device=dev()).bfloat16()
+    w = (torch.randn(d, V, generator=g, device=dev()) * (3.0 / d ** 0.5)).bfloat16()
+    tok = torch.randint(0, V, (rows,), generator=g, device=dev(), dtype=torch.int32)
+    return x, w, tok
+
+
+CASES = [(128, 64, 256), (100, 72, 776), (37, 8, 8), (256, 256, 1024), (1000, 512, 4104), (129, 4096, 32000), (300, 4096, 128256), (2500, 1024, 16384)]
+
+
+@pytest.mark.parametrize("rows,d,V", CASES)
+@pytest.mark.parametrize("layout", ["dV", "Vd"])
+def test_readout_statistics_on_the_logits_it_wrote(oracle, rows, d, V, layout):
+    from noetic_tensor_b200 import ops
+
+    x, w, tok = make(rows, d, V, rows + V)
+    wa = w.t().contiguous() if layout == "Vd" else w
+    o = ops.readout_forward(x, wa, tokens=tok, weights_are_vd=(layout == "Vd"), round_bf16=True, want_logits=True)
+    assert (o.status == 0).all()
+    # the product
+    n = min(rows, 160)
+    ref = x[:n].double() @ w.double()
+    lg = o.logits[:n].double()
+    assert ((lg - ref).abs() <= 2.0 ** -7 * ref.abs() + 1e-4).all(), f"logits: worst |Δ| {(lg - ref).abs().max().item():.3e}"
+    # the statistics: the oracle on the very logits the kernel folded
+    idx = np.random.default_rng(rows).choice(rows, min(rows, 24), replace=False)
+    bits = o.logits[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    orc = oracle.sample_inverse_cdf(bits, 1.0, None, given_tokens=tok[idx].cpu().numpy().astype(np.int64))
+    close(o.logp[idx].cpu().numpy(), orc["logp"], "logp vs oracle")
+    close(o.entropy[idx].cpu().numpy(), orc["entropy"], "entropy vs oracle")
+    # and the row kernel on the same logits, every row
+    f = ops.row_forward(o.logits, tokens=tok)
+    close(o.logp.cpu().numpy(), f.logp.cpu().numpy(), "logp vs nrl_row_fwd")
+    close(o.entropy.cpu().numpy(), f.entropy.cpu().numpy(), "entropy vs nrl_row_fwd")
+    assert torch.equal(o.rowstats[:, 0], f.rowstats[:, 0]), "the row maximum is exact"
+    close(o.rowstats[:, 1].cpu().numpy(), f.rowstats[:, 1].cpu().numpy(), "ln Z vs nrl_row_fwd")
+    # run to run, and without the debug output
+    again = ops.readout_forward(x, wa, tokens=tok, weights_are_vd=(layout == "Vd"), round_bf16=True)
+    for name in ("logp", "entropy", "rowstats"):
+        assert torch.equal(getattr(o, name).view(torch.int32), getattr(again, name).view(torch.int32)), name
+
+
+@pytest.mark.parametrize("rows,d,V", [(256, 256, 1024), (200, 4096, 128256), (1500, 2048, 8192)])
+def test_readout_statistics_of_the_f32_accumulators(rows, d, V):
+    """Without rounding the logits are the f32 accumulators, as the reference's f32 logits tensor."""
+    from noetic_tensor_b200 import ops
+
+    x, w, tok = make(rows, d, V, 7 * rows + V)
+    o = ops.readout_forward(x, w, tokens=tok)
+    ovd = ops.readout_forward(x, w.t().contiguous(), tokens=tok, weights_are_vd=True)
+    n = min(rows, 128)
+    ref = x[:n].double() @ w.double()
+    lp = torch.log_softmax(ref, 1)
+    ent = -(lp.exp() * lp).sum(1)
+    lse = torch.logsumexp(ref, 1)
+    lpt = lp[torch.arange(n, device=dev()), tok[:n].long()]
+    close((o.rowstats[:n, 0].double() + o.rowstats[:n, 1].double()).cpu().numpy(), lse.cpu().numpy(), "m + ln Z", rel=5e-5, abs_=5e-6)
+    close(o.entropy[:n].cpu().numpy(), ent.cpu().numpy(), "entropy", rel=5e-5, abs_=5e-6)
+    close(o.logp[:n].cpu().numpy(), lpt.cpu().numpy(), "logp", rel=5e-5, abs_=5e-6)
+    # the two weight layouts feed the same products in the same order
+    for name in ("logp", "entropy", "rowstats"):
+        assert torch.equal(getattr(o, name).view(torch.int32), getattr(ovd, name).view(torch.int32)), name
+
+
+def test_readout_refusals_and_status():
+    from noetic_tensor_b200 import capi, ops
+
+    x, w, tok = make(140, 64, 512, 3)
+    x[5, 7] = float("nan")
+    tok[9] = 512  # no such token
+    o = ops.readout_forward(x, w, tokens=tok)
+    st = o.status.cpu().numpy()
+    assert st[5] == 2 and (np.delete(st, 5) == 0).all()
+    assert torch.isnan(o.logp[5]) and torch.isnan(o.entropy[5]) and torch.isnan(o.logp[9]) and torch.isfinite(o.entropy[9])
+    with pytest.raises(capi.NrlError):
+        ops.readout_forward(x[:, :60].contiguous(), w[:60].contiguous(), tokens=tok)  # d not a multiple of 8
+    with pytest.raises(capi.NrlError):
+        ops.readout_forward(x, w, tokens=tok, workspace=torch.empty(16, dtype=torch.uint8, device=dev()))
