@@ -415,7 +415,43 @@ def run_extras(dev, peak):
     seed = bytes(range(32))
     t_g = _time(lambda: ops.sample_gumbel(xs, seed, allow=ms_))
     res["reference_gumbel_sampler"] = entry(4096, t_g, 4096 * V * 3, "nrl_sample_gumbel on 4096 headline-shaped rows: tokens identical to the reference's sample_categorical for the same ChaCha20 seed (bytes = logits + mask; the kernel is bound by ChaCha20 and f64 logarithms, not by HBM)")
+    del xs, ms_
     res["masked_cross_entropy_fwd_bwd"] = entry(rows, _time(ce_step), rows * V * (2 + 2 + 4), "nn::loss masked_cross_entropy [2,4,1024,128256] bf16: forward (one read) + backward to f32 d(logits)")
+    del x, tg, mk
+    torch.cuda.empty_cache()
+
+    # the step before the path fused into it: logits = hidden · W on the tensor cores (tcgen05), folded to the row
+    # statistics out of tensor memory; against the two-step form (cuBLAS product writing bf16 logits, then nrl_row_fwd)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            pk = json.load(fh)
+        tf_sustained, tf_burst, tf_kind = float(pk["bf16_tflops_sustained"]), float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        tf_sustained, tf_burst, tf_kind = 1400.0, 1590.0, "fallback"
+    rows, d6 = 8192, 4096
+    hx = torch.randn(rows, d6, generator=gen, device=dev).to(torch.bfloat16)
+    wt = (torch.randn(d6, V, generator=gen, device=dev) * (3.0 / d6 ** 0.5)).to(torch.bfloat16)
+    tk = torch.randint(0, V, (rows,), generator=gen, device=dev, dtype=torch.int32)
+    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d6), dtype=torch.uint8, device=dev)
+    lg = torch.empty(rows, V, dtype=torch.bfloat16, device=dev)
+    t_fused = _time(lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws))
+    t_round = _time(lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws, round_bf16=True))
+    t_mm = _time(lambda: torch.matmul(hx, wt, out=lg))
+
+    def two_step():
+        torch.matmul(hx, wt, out=lg)
+        return ops.row_forward(lg, tokens=tk)
+
+    t_two = _time(two_step)
+    fl = 2.0 * rows * d6 * V
+    fo, f2 = ops.readout_forward(hx, wt, tokens=tk, workspace=ws, round_bf16=True, want_logits=True), None
+    f2 = ops.row_forward(fo.logits, tokens=tk)
+    res["readout_fused"] = {"what": "nrl_readout_fwd: logits = hidden [8192, 4096] x W [4096, 128256] (bf16, f32 accumulators in tensor memory) folded to log-prob of given tokens + entropy + row "
+                                    "statistics without writing the logits; two_step = torch.matmul (cuBLAS, bf16 logits written) + nrl_row_fwd on them",
+                            "rows": rows, "d": d6, "V": V, "ms": t_fused, "ms_round_bf16": t_round, "TFLOPs": fl / t_fused / 1e9, "frac_of_sustained_bf16_peak": fl / t_fused / 1e9 / tf_sustained,
+                            "frac_of_burst_bf16_peak": fl / t_fused / 1e9 / tf_burst, "peak_kind": tf_kind, "cublas_product_alone_ms": t_mm, "cublas_TFLOPs": fl / t_mm / 1e9,
+                            "two_step_ms": t_two, "speedup_vs_two_step": t_two / t_fused, "rows_per_s": rows / (t_fused * 1e-3),
+                            "values_outside_tolerance_vs_row_fwd_on_its_logits": close(fo.logp, f2.logp) + close(fo.entropy, f2.entropy)}
     return res
 
 

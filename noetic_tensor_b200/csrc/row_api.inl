@@ -157,9 +157,17 @@ static int launch_bwd(const BwdParams& p, cudaStream_t st) {
     // f32 logits, and bf16 logits alone (the cross-entropy backward): stores and loads that fill whole
     // sectors measured faster. With a mask or a reference stream the 8-element mapping, with its
     // fewer and wider loads, measured as fast or faster, so those stay on it.
-    if constexpr (VEC && !GENERAL && (DT == NRL_F32 || (!ALLOW && !REF))) {
+    if constexpr (VEC && !GENERAL && !ALLOW && (DT == NRL_F32 || !REF)) {
         if (!extra && aligned16((uint64_t)(uintptr_t)p.d_logits)) {
             row_bwd_split_kernel<DT, REF, ALLOW><<<grid, kBwdThreads, 0, st>>>(p);
+            return after_launch();
+        }
+    }
+    // byte- or bit-masked rows on the vectorised path: excluded vectors are zero-filled from the mask alone and the live
+    // ones are compacted (measured on the benchmark's grammar masks and on dense random masks)
+    if constexpr (VEC && !GENERAL && ALLOW) {
+        if (!extra && aligned16((uint64_t)(uintptr_t)p.d_logits)) {
+            row_bwd_compact_kernel<DT, REF><<<grid, kBwdThreads, 0, st>>>(p);
             return after_launch();
         }
     }

@@ -254,4 +254,141 @@ __global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_split_kernel(BwdParams
     }
 }
 
+// ---- rows under an allow-mask that excludes most of the vocabulary ------------------------------------
+//
+// Under a grammar mask most 8-element vectors are excluded whole, and the few live ones are
+// scattered: in the kernels above a warp runs the whole gradient arithmetic for the two or three
+// lanes that hold a live vector (9 of 32 threads active on the benchmark's masks) and waits for
+// the mask, then for the logits, one tile at a time. Here a warp works like the forward's
+// compacting loop: it scans its range's mask four tiles at a time (the next four in flight),
+// stores the zeros of excluded vectors at once — as 16-byte pieces laid out so that every
+// warp-wide store fills whole sectors — and queues the live vectors in shared memory; whenever 32
+// are queued every lane takes one, its loads fly while the previous batch's gradients are
+// computed, and each lane writes its 32 bytes. The values are the kernels' above, bit for bit
+// (the same expression per element).
+constexpr int kBwdQueue = 256;
+constexpr int kBwdAhead = 4;
+
+template <int DT, bool REF>
+__global__ void __launch_bounds__(kBwdThreads, 4) row_bwd_compact_kernel(BwdParams p) {
+    __shared__ uint32_t queues[kBwdThreads / 32][kBwdQueue];
+    const FwdParams& f = p.in;
+    const uint64_t row = blockIdx.x / p.chunks_per_row;
+    const uint32_t chunk = blockIdx.x % p.chunks_per_row;
+    const uint32_t V = f.V;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t lt = (1u << lane) - 1u;
+    // this warp's range of the row, in whole tiles
+    const uint32_t ntiles = (V + kTile - 1) / kTile;
+    const uint32_t nparts = p.chunks_per_row * (kBwdThreads / 32);
+    const uint32_t tiles_per = (ntiles + nparts - 1) / nparts;
+    const uint32_t part = chunk * (kBwdThreads / 32) + warp;
+    const uint32_t begin = min(part * tiles_per, ntiles) * kTile;
+    const uint32_t end = min(min((part + 1) * tiles_per, ntiles) * kTile, V);
+    float* out = p.d_logits + row * V;
+
+    const float glp = p.g_logp ? p.g_logp[row] : 0.f;
+    const float gkl = (REF && p.g_kl) ? p.g_kl[row] : 0.f;
+    const float gen = p.g_ent ? p.g_ent[row] : 0.f;
+    if (glp == 0.f && gkl == 0.f && gen == 0.f) {
+        // an unscored position: exact zeros, the inputs are not read
+        for (uint32_t t = begin; t < end; t += kTile) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint32_t e = t + h * (kTile / 2) + lane * 4;
+                if (e < end) stg_stream16(out + e, 0.f, 0.f, 0.f, 0.f);
+            }
+        }
+        return;
+    }
+    const float4 st = reinterpret_cast<const float4*>(p.rowstats)[row];
+    const float m = st.x, lnZ = st.y, mr = st.z, lnZr = st.w;
+    const float klv = (REF && p.kl && gkl != 0.f) ? p.kl[row] : 0.f;
+    const float hv = (p.entropy && gen != 0.f) ? p.entropy[row] : 0.f;
+    const int32_t tok = (p.tokens && glp != 0.f) ? p.tokens[row] : -1;
+
+    typedef VecLoader<DT, REF, true, false, true> Loader;
+    uint32_t* wq = queues[warp];
+    uint32_t head = 0, count = 0;  // warp-uniform ring state
+    Loader pend;
+    uint32_t pend_v = kNoEntry;
+    bool pend_any = false;
+
+#if NRL_MASK_BITS
+    const uint8_t* mp = f.allow + row * f.allow_stride + ((begin + lane * kVec) >> 3);
+    constexpr uint32_t kTileMask = kTile / 8;
+#else
+    const uint8_t* mp = f.allow + row * f.allow_stride + begin + lane * kVec;
+    constexpr uint32_t kTileMask = kTile;
+#endif
+    uint32_t v = begin + lane * kVec;  // this lane's vector of the tile at t0
+    uint32_t t0 = begin;
+    uint32_t mk[kBwdAhead];
+    MaskAny mn[kBwdAhead];
+#pragma unroll
+    for (int j = 0; j < kBwdAhead; j++) mk[j] = (v + j * kTile < end) ? mask_any_value(ldg_mask_any(mp + j * kTileMask, 0)) : 0u;
+
+    for (;;) {
+        const bool scanning = t0 < end;
+        if (scanning) {
+            const uint8_t* np = mp + kBwdAhead * kTileMask;
+            const uint32_t nv = v + kBwdAhead * kTile;
+#pragma unroll
+            for (int j = 0; j < kBwdAhead; j++) mn[j] = (nv + j * kTile < end) ? ldg_mask_any(np + j * kTileMask, 0) : mask_any_none();
+#pragma unroll
+            for (int j = 0; j < kBwdAhead; j++) {
+                const uint32_t vv = v + j * kTile;
+                // a vector is live when it allows a token, or holds the row's token (whose entry gets g_lp even if excluded)
+                const bool nz = vv < end && (mk[j] != 0u || (tok >= (int32_t)vv && tok < (int32_t)(vv + kVec)));
+                const uint32_t ball = __ballot_sync(0xffffffffu, nz);
+                if (nz) wq[(head + count + __popc(ball & lt)) & (kBwdQueue - 1)] = vv;
+                count += __popc(ball);
+                // zeros for the excluded vectors of this tile: lane l writes elements 4l.. of each half, which belong to vector 16h + l/2
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t e = t0 + j * kTile + h * (kTile / 2) + lane * 4;
+                    if (e < end && !((ball >> (h * 16 + (lane >> 1))) & 1u)) stg_stream16(out + e, 0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kBwdAhead; j++) mk[j] = mask_any_value(mn[j]);
+            mp = np;
+            v = nv;
+            t0 += kBwdAhead * kTile;
+            __syncwarp();
+        }
+        while (count >= 32 || (!scanning && (count > 0 || pend_any))) {
+            const uint32_t n = count < 32 ? count : 32;
+            Loader nxt;
+            const uint32_t nv_entry = ((uint32_t)lane < n) ? wq[(head + lane) & (kBwdQueue - 1)] : kNoEntry;
+            if (nv_entry != kNoEntry) nxt.load(f, row, nv_entry, end);
+            head = (head + n) & (kBwdQueue - 1);
+            count -= n;
+            if (pend_any && pend_v != kNoEntry) {
+                float z[8], zr[8], g[8];
+                pend.values(f, z, zr);
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float zc = fmaxf(z[i], -FLT_MAX);
+                    const float lp = (zc - m) - lnZ;
+                    const float pi = ex2_approx(lp * kLog2e);
+                    float c = -glp;                                          // d logp / dz_j = 1[j = tok] − π_j
+                    if (REF) c = fmaf(gkl, (lp - ((zr[i] - mr) - lnZr)) - klv, c);  // d KL / dz_j = π_j (log π_j − log ρ_j − KL)
+                    c = fmaf(-gen, lp + hv, c);                              // d H / dz_j = −π_j (log π_j + H)
+                    float d = pi > 0.f ? pi * c : 0.f;                       // a zero-probability token gets exactly 0
+                    if ((int32_t)(pend_v + i) == tok) d += glp;
+                    g[i] = d;
+                }
+                stg_stream16(out + pend_v, g[0], g[1], g[2], g[3]);
+                stg_stream16(out + pend_v + 4, g[4], g[5], g[6], g[7]);
+            }
+            pend = nxt;
+            pend_v = nv_entry;
+            pend_any = n > 0;
+        }
+        if (!scanning) break;
+        __syncwarp();  // the batch's entries are read before the next group's pushes can reuse slots
+    }
+}
+
 }  // namespace nrl
