@@ -387,7 +387,9 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
 #pragma unroll
     for (int s = 0; s < kSlots; s++) issue(s, v + s * kTile, xp + (size_t)s * kTile * kEsize, REF ? rp + (size_t)s * kTile * kEsize : nullptr);
     for (uint32_t t0 = begin; t0 < end; t0 += kSlots * kTile) {  // warp-uniform
-#pragma unroll
+        // not unrolled: one copy of the per-tile arithmetic keeps the loop inside the instruction cache
+        // (measured 4 % faster with a reference stream, 8 % without, than the loop unrolled over the slots)
+#pragma unroll 1
         for (int s = 0; s < kSlots; s++) {
             cp_async_wait<kSlots - 1>();  // the oldest tile has landed
             if (t0 + s * kTile < end) {  // warp-uniform: the tile exists
