@@ -343,19 +343,14 @@ def run_extras(dev, peak):
     up = torch.ones(S4, device=dev)
     launches0 = capi.lib().nrl_launch_count()
 
+    coef = [torch.ones(S4, device=dev), torch.full((S4,), 0.04, device=dev), torch.full((S4,), -0.01, device=dev)]
+
     def ppo_step():
         f = ops.row_forward(x, ref_logits=r, tokens=tok)
-        lp = f.logp.reshape(S4, B4, T4)
-        per, _ = ops.token_loss(capi.LOSS_PPO, lp, other=old, weights=adv, clip_low=0.2, clip_high=0.2, clamp=20.0, want_grad=False)
-        loss = ops.reduce_tokens(per, None, capi.REDUCE_TOKEN_MEAN)
-        kl = ops.reduce_tokens(f.kl.reshape(S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN)
-        ent = ops.reduce_tokens(f.entropy.reshape(S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN)
-        g_per = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, up)
-        _, g_lp = ops.token_loss(capi.LOSS_PPO, lp, other=old, weights=adv, clip_low=0.2, clip_high=0.2, clamp=20.0, upstream=g_per)
-        g_kl = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, 0.04 * up).reshape(-1)
-        g_en = ops.reduce_tokens_backward((S4, B4, T4), None, capi.REDUCE_TOKEN_MEAN, -0.01 * up).reshape(-1)
-        ops.row_backward(x, f, ref_logits=r, g_logp=g_lp.reshape(-1), g_kl=g_kl, g_ent=g_en, out=d)
-        return loss, kl, ent
+        o = ops.token_objective(capi.LOSS_PPO, f.logp.reshape(S4, B4, T4), capi.REDUCE_TOKEN_MEAN, other=old, weights=adv, clip_low=0.2, clip_high=0.2, clamp=20.0,
+                                kl=f.kl.reshape(S4, B4, T4), entropy=f.entropy.reshape(S4, B4, T4), up_policy=coef[0], up_kl=coef[1], up_entropy=coef[2])
+        ops.row_backward(x, f, ref_logits=r, g_logp=o.g_logp.reshape(-1), g_kl=o.g_kl.reshape(-1), g_ent=o.g_ent.reshape(-1), out=d)
+        return o.policy, o.kl, o.entropy
 
     ms = _time(ppo_step)
     res["ppo_step_config4"] = entry(rows, ms, rows * V4 * (4 + 4 + 4), "config 4 slice [1,32,256,151936] bf16 + reference: PPO-clip 0.2 + 0.04 KL − 0.01 entropy, forward + backward to f32 d(logits)")

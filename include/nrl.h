@@ -278,6 +278,32 @@ int nrl_reduce_tokens_fold(uint32_t reduction, uint64_t S, uint64_t B, nrl_devpt
 int nrl_reduce_tokens_bwd_pairs(uint32_t reduction, uint64_t S, uint64_t B, uint64_t T, uint64_t seq_begin, uint64_t n_seq, nrl_devptr pairs, nrl_devptr mask,
                                 nrl_devptr g_out, nrl_devptr d_per, nrl_stream stream);
 
+/* A whole token-level objective in one launch (no single counterpart in the reference, which
+ * composes it from the functions above): the token loss `policy` (any NRL_LOSS_* kind) of the
+ * log-probs, and the per-token exact KL and entropy that nrl_row_fwd left (either may be 0), all
+ * three under the same scoring mask and the same per-seed TokenReduction (SUM, TOKEN_MEAN or
+ * SEQUENCE_MEAN; the others: NRL_E_UNSUPPORTED), and at once the per-token upstream gradients
+ * nrl_row_bwd takes. It stands for nrl_token_loss + three nrl_reduce_tokens + three
+ * nrl_reduce_tokens_bwd + the backward nrl_token_loss — eight launches — and gives their bits:
+ *   out_policy[s] = reduce(token_loss(policy))        g_logp[i] = d_per_policy[i] · d loss_i / d logp_i
+ *   out_kl[s]     = reduce(zero_masked(kl))           g_kl[i]   = d_per_kl[i]
+ *   out_entropy[s]= reduce(zero_masked(entropy))      g_ent[i]  = d_per_entropy[i]
+ * where d_per_x is what nrl_reduce_tokens_bwd gives for the upstream gradient up_x [S] of the reduced
+ * value (0 = ones). A caller forms its objective from the three reduced values (for example
+ * policy + 0.04·kl − 0.01·entropy) and passes the matching upstream gradients (1, 0.04, −0.01). */
+typedef struct nrl_token_objective_args {
+    uint32_t struct_size;
+    uint32_t reduction;           /* NRL_REDUCE_SUM, NRL_REDUCE_TOKEN_MEAN or NRL_REDUCE_SEQUENCE_MEAN */
+    nrl_token_loss_args policy;   /* kind, S, B, T, logp, other, weights, mask, clip constants; its loss / upstream / dloss_dlogp / accumulate fields are ignored */
+    nrl_devptr kl;                /* f32 [S,B,T] per-token exact KL, or 0 */
+    nrl_devptr entropy;           /* f32 [S,B,T] per-token entropy, or 0 */
+    nrl_devptr up_policy, up_kl, up_entropy;    /* f32 [S] each, or 0 for ones */
+    nrl_devptr out_policy, out_kl, out_entropy; /* out f32 [S] each, or 0 */
+    nrl_devptr g_logp, g_kl, g_ent;             /* out f32 [S,B,T] each, or 0 */
+} nrl_token_objective_args;
+
+int nrl_token_objective(const nrl_token_objective_args* args, nrl_stream stream);
+
 /* ---------------------------------------------------------------------------------------------
  * The cross-entropy family of nn::loss over the same row kernels (src/nn/loss.rs:10-79):
  *   nll                    :10-16   −log_softmax(logits)[target]           = −logp of nrl_row_fwd(TOKENS_IN)

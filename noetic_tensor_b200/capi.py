@@ -48,6 +48,14 @@ class TokenLossArgs(C.Structure):
     ]
 
 
+class TokenObjectiveArgs(C.Structure):
+    _fields_ = [
+        ("struct_size", u32), ("reduction", u32), ("policy", TokenLossArgs), ("kl", ptr), ("entropy", ptr),
+        ("up_policy", ptr), ("up_kl", ptr), ("up_entropy", ptr), ("out_policy", ptr), ("out_kl", ptr), ("out_entropy", ptr),
+        ("g_logp", ptr), ("g_kl", ptr), ("g_ent", ptr),
+    ]
+
+
 class CeArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("V", u32), ("n", u64), ("smoothing", f64),
@@ -111,6 +119,7 @@ SYMBOLS = {
     "nrl_row_fwd_static": (C.c_int, [C.POINTER(RowFwdArgs), C.c_void_p]),
     "nrl_row_bwd": (C.c_int, [C.POINTER(RowBwdArgs), C.c_void_p]),
     "nrl_token_loss": (C.c_int, [C.POINTER(TokenLossArgs), C.c_void_p]),
+    "nrl_token_objective": (C.c_int, [C.POINTER(TokenObjectiveArgs), C.c_void_p]),
     "nrl_clip_fraction": (C.c_int, [C.POINTER(TokenLossArgs), ptr, C.c_void_p]),
     "nrl_reduce_tokens": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),
     "nrl_reduce_tokens_bwd": (C.c_int, [u32, u64, u64, u64, ptr, ptr, ptr, C.c_void_p]),

@@ -167,6 +167,36 @@ extern "C" int nrl_token_loss(const nrl_token_loss_args* a, nrl_stream stream) {
     return after_launch();
 }
 
+extern "C" int nrl_token_objective(const nrl_token_objective_args* a, nrl_stream stream) {
+    if (!a || a->struct_size != sizeof(nrl_token_objective_args)) return NRL_E_BAD_ARG;
+    ObjectiveParams p;
+    memset(&p, 0, sizeof p);
+    int rc = fill_tok(p.tok, &a->policy);
+    if (rc) return rc;
+    if (a->reduction != NRL_REDUCE_SUM && a->reduction != NRL_REDUCE_TOKEN_MEAN && a->reduction != NRL_REDUCE_SEQUENCE_MEAN) return NRL_E_UNSUPPORTED;
+    if (a->policy.S > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    if ((a->g_kl && !a->kl) || (a->g_ent && !a->entropy)) return NRL_E_BAD_ARG;
+    p.tok.loss = nullptr;
+    p.tok.upstream = nullptr;
+    p.tok.dloss = nullptr;
+    p.kl = (const float*)a->kl;
+    p.entropy = (const float*)a->entropy;
+    p.up_policy = (const float*)a->up_policy;
+    p.up_kl = (const float*)a->up_kl;
+    p.up_entropy = (const float*)a->up_entropy;
+    p.out_policy = (float*)a->out_policy;
+    p.out_kl = (float*)a->out_kl;
+    p.out_entropy = (float*)a->out_entropy;
+    p.g_logp = (float*)a->g_logp;
+    p.g_kl = (float*)a->g_kl;
+    p.g_ent = (float*)a->g_ent;
+    p.B = a->policy.B;
+    p.T = a->policy.T;
+    p.reduction = a->reduction;
+    token_objective_kernel<<<(unsigned)a->policy.S, kFoldThreads, 0, (cudaStream_t)stream>>>(p);
+    return after_launch();
+}
+
 extern "C" int nrl_clip_fraction(const nrl_token_loss_args* a, nrl_devptr out, nrl_stream stream) {
     TokParams p;
     int rc = fill_tok(p, a);

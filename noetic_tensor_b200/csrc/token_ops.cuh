@@ -34,12 +34,12 @@ __device__ __forceinline__ float clamp_sym(float x, float b, bool& pass) {
     return x;
 }
 
-__global__ void token_loss_kernel(TokParams p) {
-    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= p.n) return;
-    const bool scored = p.mask ? (p.mask[i] != 0.f) : true;
+// One position of a token-level loss: the value `per` and d per / d logp `dl` (both exactly 0 at
+// an unscored position: zero_masked is a select, so garbage there never leaks).
+__device__ __forceinline__ void token_loss_eval(const TokParams& p, uint64_t i, bool scored, float& per, float& dl) {
     const float lp = p.logp[i];
-    float per = 0.f, dl = 0.f;
+    per = 0.f;
+    dl = 0.f;
     if (p.kind == NRL_LOSS_PG) {
         float w = p.weights[p.w_per_seq ? i / p.T : i];
         per = -(lp * w);
@@ -92,7 +92,15 @@ __global__ void token_loss_kernel(TokParams p) {
         }
         dl = pass_d ? -g_d : 0.f;
     }
-    if (!scored) { per = 0.f; dl = 0.f; }  // zero_masked: a select, so garbage never leaks
+    if (!scored) { per = 0.f; dl = 0.f; }
+}
+
+__global__ void token_loss_kernel(TokParams p) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= p.n) return;
+    const bool scored = p.mask ? (p.mask[i] != 0.f) : true;
+    float per, dl;
+    token_loss_eval(p, i, scored, per, dl);
     if (p.loss) p.loss[i] = per;
     if (p.dloss) {
         float d = (p.upstream && scored) ? p.upstream[i] * dl : dl;
@@ -316,6 +324,108 @@ __global__ void __launch_bounds__(256) reduce_tokens_bwd_pairs_kernel(uint32_t r
         const bool scored = mask ? mask[base + t] != 0.f : true;
         const float gi = reduction == NRL_REDUCE_NONE ? g_out[base + t] : g;
         d_per[base + t] = scored ? gi : 0.f;
+    }
+}
+
+// ---- a whole token-level objective in one launch ---------------------------------------------------
+//
+// A PPO-style step reduces three per-token quantities with the same TokenReduction — the clipped
+// policy loss of the log-probs, the exact KL and the entropy the row forward left per token — and
+// then needs, per token, the upstream gradients the row backward takes. Done with the separate
+// entry points that is one token_loss, three reduce_tokens, three reduce_tokens_bwd and one more
+// token_loss launch. This kernel does all of it per seed (one block, warps taking the seed's
+// sequences side by side): step 1 sums each sequence of the three quantities and folds the
+// sequences in order — the very operations of reduce_tokens_kernel, so the reduced values have
+// its bits; step 2 writes g_logp = d_per · d loss / d logp, g_kl = d_per_kl and g_ent = d_per_ent,
+// with d_per the values reduce_tokens_bwd_kernel would write (same divisions).
+struct ObjectiveParams {
+    TokParams tok;            // the policy term (logp, other, weights, mask, clip constants); n = S·B·T
+    const float* kl;          // per-token exact KL [S,B,T] or null
+    const float* entropy;     // per-token entropy [S,B,T] or null
+    const float* up_policy;   // upstream gradients of the three reduced values, [S] each; null = ones
+    const float* up_kl;
+    const float* up_entropy;
+    float* out_policy;        // reduced values [S]
+    float* out_kl;
+    float* out_entropy;
+    float* g_logp;            // per-token gradients for nrl_row_bwd, [S,B,T]
+    float* g_kl;
+    float* g_ent;
+    uint64_t B, T;
+    uint32_t reduction;       // SUM, TOKEN_MEAN or SEQUENCE_MEAN
+};
+
+__global__ void __launch_bounds__(kFoldThreads) token_objective_kernel(ObjectiveParams p) {
+    __shared__ float sv[3][kSeqChunk], sc[kSeqChunk];
+    __shared__ float sh_scale;
+    const uint64_t s = blockIdx.x, B = p.B, T = p.T;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float* mask = p.tok.mask;
+    SeedFold f[3];
+    for (uint64_t b0 = 0; b0 < B; b0 += kSeqChunk) {
+        const int n = (int)(B - b0 < (uint64_t)kSeqChunk ? B - b0 : (uint64_t)kSeqChunk);
+        for (int j = warp; j < n; j += kFoldThreads / 32) {
+            const uint64_t base = (s * B + b0 + j) * T;
+            // seq_sum's order: lane l adds its elements l, l + 32, … then the butterfly
+            float v0 = 0.f, v1 = 0.f, v2 = 0.f, c = 0.f;
+            for (uint64_t t = lane; t < T; t += 32) {
+                const uint64_t i = base + t;
+                const bool scored = mask ? mask[i] != 0.f : true;
+                float per, dl;
+                token_loss_eval(p.tok, i, scored, per, dl);
+                v0 = __fadd_rn(v0, per);  // never contracted with the loss's last product: the sum of the stored values
+                if (p.kl) v1 += scored ? p.kl[i] : 0.f;          // zero_masked, then the reduction
+                if (p.entropy) v2 += scored ? p.entropy[i] : 0.f;
+                c += mask ? mask[i] : 1.f;
+            }
+#pragma unroll
+            for (int k = 16; k >= 1; k >>= 1) {
+                v0 += __shfl_xor_sync(0xffffffffu, v0, k);
+                v1 += __shfl_xor_sync(0xffffffffu, v1, k);
+                v2 += __shfl_xor_sync(0xffffffffu, v2, k);
+                c += __shfl_xor_sync(0xffffffffu, c, k);
+            }
+            if (lane == 0) { sv[0][j] = v0; sv[1][j] = v1; sv[2][j] = v2; sc[j] = c; }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int j = 0; j < n; j++) { f[0].add(sv[0][j], sc[j]); f[1].add(sv[1][j], sc[j]); f[2].add(sv[2][j], sc[j]); }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        if (p.out_policy) p.out_policy[s] = f[0].value(p.reduction);
+        if (p.kl && p.out_kl) p.out_kl[s] = f[1].value(p.reduction);
+        if (p.entropy && p.out_entropy) p.out_entropy[s] = f[2].value(p.reduction);
+        sh_scale = f[0].scale(p.reduction);
+    }
+    __syncthreads();
+    if (!p.g_logp && !p.g_kl && !p.g_ent) return;
+    const float seed_scale = sh_scale;
+    const float up0 = p.up_policy ? p.up_policy[s] : 1.f, up1 = p.up_kl ? p.up_kl[s] : 1.f, up2 = p.up_entropy ? p.up_entropy[s] : 1.f;
+    for (uint64_t b = warp; b < B; b += kFoldThreads / 32) {
+        const uint64_t base = (s * B + b) * T;
+        float seq_scale = 1.f;
+        if (p.reduction == NRL_REDUCE_SEQUENCE_MEAN) {
+            float v, c;
+            seq_sum(nullptr, mask, base, T, v, c);
+            seq_scale = fmaxf(c, 1.f);
+        }
+        // d_per of reduce_tokens_bwd_kernel for each of the three upstreams
+        float d0, d1, d2;
+        if (p.reduction == NRL_REDUCE_SEQUENCE_MEAN) { d0 = (up0 / seed_scale) / seq_scale; d1 = (up1 / seed_scale) / seq_scale; d2 = (up2 / seed_scale) / seq_scale; }
+        else if (p.reduction == NRL_REDUCE_TOKEN_MEAN) { d0 = up0 / seed_scale; d1 = up1 / seed_scale; d2 = up2 / seed_scale; }
+        else { d0 = up0; d1 = up1; d2 = up2; }
+        for (uint64_t t = lane; t < T; t += 32) {
+            const uint64_t i = base + t;
+            const bool scored = mask ? mask[i] != 0.f : true;
+            if (p.g_logp) {
+                float per, dl;
+                token_loss_eval(p.tok, i, scored, per, dl);
+                p.g_logp[i] = scored ? d0 * dl : dl;  // token_loss_kernel's `upstream · dl` (dl is 0 where unscored)
+            }
+            if (p.g_kl) p.g_kl[i] = scored ? d1 : 0.f;
+            if (p.g_ent) p.g_ent[i] = scored ? d2 : 0.f;
+        }
     }
 }
 

@@ -238,6 +238,46 @@ def token_loss(kind, logp, *, other=None, weights=None, mask=None, clip_low=0.0,
     return loss, dl
 
 
+class TokenObjective:
+    """Outputs of nrl_token_objective: reduced values [S] and per-token gradients [S,B,T] (None when not requested)."""
+
+    __slots__ = ("policy", "kl", "entropy", "g_logp", "g_kl", "g_ent")
+
+
+def token_objective(kind, logp, reduction, *, other=None, weights=None, mask=None, clip_low=0.0, clip_high=0.0, dual=None, clamp=None, kl=None, entropy=None,
+                    up_policy=None, up_kl=None, up_entropy=None, want_grads=True):
+    """A token loss of `logp` plus the per-token KL and entropy, all reduced per seed with one
+    TokenReduction, and the per-token upstream gradients of the row backward, in one launch
+    (nrl_token_objective). `up_*` are the upstream gradients [S] of the three reduced values (None = ones)."""
+    dev = logp.device
+    S, B, T = logp.shape
+    a = capi.TokenObjectiveArgs()
+    a.struct_size = C.sizeof(a)
+    a.reduction = reduction
+    a.policy = _tok_args(kind, logp, other, weights, mask, clip_low, clip_high, dual, clamp)
+    out = TokenObjective()
+    f32 = dict(dtype=torch.float32, device=dev)
+    for name, t in (("kl", kl), ("entropy", entropy)):
+        if t is not None:
+            _need(t, torch.float32, (S, B, T), name, dev)
+    for name, t in (("up_policy", up_policy), ("up_kl", up_kl), ("up_entropy", up_entropy)):
+        if t is not None:
+            _need(t, torch.float32, (S,), name, dev)
+    a.kl, a.entropy = _p(kl), _p(entropy)
+    a.up_policy, a.up_kl, a.up_entropy = _p(up_policy), _p(up_kl), _p(up_entropy)
+    out.policy = torch.empty(S, **f32)
+    out.kl = torch.empty(S, **f32) if kl is not None else None
+    out.entropy = torch.empty(S, **f32) if entropy is not None else None
+    out.g_logp = torch.empty(S, B, T, **f32) if want_grads else None
+    out.g_kl = torch.empty(S, B, T, **f32) if (want_grads and kl is not None) else None
+    out.g_ent = torch.empty(S, B, T, **f32) if (want_grads and entropy is not None) else None
+    a.out_policy, a.out_kl, a.out_entropy = _p(out.policy), _p(out.kl), _p(out.entropy)
+    a.g_logp, a.g_kl, a.g_ent = _p(out.g_logp), _p(out.g_kl), _p(out.g_ent)
+    with torch.cuda.device(dev):
+        capi.check(capi.lib().nrl_token_objective(C.byref(a), _stream(dev)), "nrl_token_objective")
+    return out
+
+
 def clip_fraction(logp, old_logp, advantages, *, mask=None, clip_low, clip_high, dual=None, clamp=None):
     dev = logp.device
     a = _tok_args(capi.LOSS_PPO, logp, old_logp, advantages, mask, clip_low, clip_high, dual, clamp)

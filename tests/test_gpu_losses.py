@@ -372,3 +372,35 @@ def test_token_reduction_bits_do_not_depend_on_the_number_of_gpus(S, B, T):
                     if e > b:
                         d = ops.reduce_tokens_backward_pairs(r, S, B, T, b, e - b, pairs, None if m is None else m.reshape(S * B, T)[b:e].contiguous(), up)
                         assert torch.equal(d.view(torch.int32), d_whole[b:e].view(torch.int32)), (r, world, rank, "backward")
+
+
+@pytest.mark.parametrize("S,B,T", [(2, 8, 12), (8, 64, 256), (4, 256, 128), (1, 1100, 33)])
+@pytest.mark.parametrize("reduction", [1, 2, 4])
+def test_token_objective_equals_the_separate_launches(S, B, T, reduction):
+    """nrl_token_objective (one launch) against the eight launches it stands for — token_loss,
+    three reduce_tokens, three reduce_tokens_bwd, the backward token_loss — bit for bit: the three
+    reduced values and the per-token gradients the row backward takes."""
+    from noetic_tensor_b200 import capi, ops
+
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev)
+    g.manual_seed(S * 100 + B + reduction)
+    lp = -torch.rand(S, B, T, generator=g, device=dev) * 6
+    old = lp + 0.3 * torch.randn(S, B, T, generator=g, device=dev)
+    adv = torch.randn(S, B, generator=g, device=dev)
+    kl = torch.rand(S, B, T, generator=g, device=dev)
+    ent = torch.rand(S, B, T, generator=g, device=dev) * 5
+    mask = (torch.rand(S, B, T, generator=g, device=dev) < 0.7).float()
+    mask[0, 0] = 0
+    ups = [torch.randn(S, generator=g, device=dev) for _ in range(3)]
+    for m in (mask, None):
+        for kind, kw in ((capi.LOSS_PPO, dict(other=old, weights=adv, clip_low=0.2, clip_high=0.3, dual=3.0, clamp=20.0)), (capi.LOSS_PG, dict(weights=adv)), (capi.LOSS_K3, dict(other=old, clamp=5.0))):
+            o = ops.token_objective(kind, lp, reduction, mask=m, kl=kl, entropy=ent, up_policy=ups[0], up_kl=ups[1], up_entropy=ups[2], **kw)
+            per, _ = ops.token_loss(kind, lp, mask=m, want_grad=False, **kw)
+            want = [ops.reduce_tokens(per, m, reduction), ops.reduce_tokens(ops.mask_rows(kl, m), m, reduction), ops.reduce_tokens(ops.mask_rows(ent, m), m, reduction)]
+            d = [ops.reduce_tokens_backward((S, B, T), m, reduction, u) for u in ups]
+            _, g_lp = ops.token_loss(kind, lp, mask=m, upstream=d[0], **kw)
+            for got, w, name in zip((o.policy, o.kl, o.entropy, o.g_logp, o.g_kl, o.g_ent), want + [g_lp, d[1], d[2]], ("policy", "kl", "entropy", "g_logp", "g_kl", "g_ent")):
+                assert torch.equal(got.view(torch.int32), w.view(torch.int32)), (kind, name, (got - w).abs().max().item())
+    with pytest.raises(capi.NrlError):
+        ops.token_objective(capi.LOSS_PG, lp, 3, weights=adv)
