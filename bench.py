@@ -450,7 +450,49 @@ def run_extras(dev, peak):
     return res
 
 
+def run_readout_variant(args):
+    """Profiling variant: a step is one nrl_readout_fwd launch pair (tcgen05 product + epilogue, then the
+    merge) over `--rows` rows (default 8192) of d = 4096 against V = 128256. Not the headline."""
+    import torch
+
+    from noetic_tensor_b200 import capi, ops
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    rows, d = args.rows or 8192, 4096
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(5)
+    hx = torch.randn(rows, d, generator=gen, device=dev).to(torch.bfloat16)
+    wt = (torch.randn(d, V, generator=gen, device=dev) * (3.0 / d ** 0.5)).to(torch.bfloat16)
+    tk = torch.randint(0, V, (rows,), generator=gen, device=dev, dtype=torch.int32)
+    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d), dtype=torch.uint8, device=dev)
+    for _ in range(max(1, args.warmup)):
+        ops.readout_forward(hx, wt, tokens=tk, workspace=ws)
+    torch.cuda.synchronize()
+    launches0 = capi.lib().nrl_launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        o = ops.readout_forward(hx, wt, tokens=tk, workspace=ws)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as fh:
+            peak, kind = float(json.load(fh)["bf16_tflops_sustained"]), "measured sustained cuBLAS bf16"
+    except Exception:
+        peak, kind = 1400.0, "fallback"
+    tf = 2.0 * rows * d * V / (ms * 1e-3) / 1e12
+    print(json.dumps({"metric": "rows/s readout-fused log-prob + entropy, d=4096, V=128256 bf16 (profiling variant, not the headline)", "value": rows / (ms * 1e-3), "unit": "rows/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "dtype": "bf16 operands, f32 accumulators",
+                      "config": {"workload": f"hidden [{rows}, {d}] x W [{d}, {V}] -> row statistics"}, "gpu_launches": int(capi.lib().nrl_launch_count() - launches0),
+                      "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_kind": kind, "kernel": "readout_fwd_kernel<false>", "traffic": None},
+                      "refused_rows": int((o.status != 0).sum().item())}))
+
+
 def run_ours(args):
+    if args.variant == "readout":
+        return run_readout_variant(args)
     # stdout carries the one JSON line and nothing else: libraries that write to it (NCCL prints
     # its version there when the communicator comes up) are sent to stderr until the line is printed
     sys.stdout.flush()
@@ -799,7 +841,7 @@ def main():
     ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
     ap.add_argument("--e2e-rows", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward", "bitmask"],
+    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward", "bitmask", "readout"],
                     help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; bitmask: the mask bit-packed; none of them is the headline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
