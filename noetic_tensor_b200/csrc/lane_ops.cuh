@@ -17,15 +17,46 @@ constexpr int kLaneThreads = 256;       // default block; long rows run 1024-thr
 constexpr int kLaneMaxThreads = 1024;
 constexpr int kLaneMaxWarps = kLaneMaxThreads / 32;
 
+// L2 eviction priorities for the rows the softmax family reads twice: the first read asks L2 to keep
+// the lines (evict_last), the second marks them as the first to go (evict_first), so that the rows
+// in flight, not the output being written, are what L2 holds.
+#ifndef NRL_SOFTMAX_HINT
+#define NRL_SOFTMAX_HINT 1
+#endif
+__device__ __forceinline__ uint64_t l2_policy_keep() {
+    uint64_t p;
+    asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_drop() {
+    uint64_t p;
+    asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint4 ldg_hint16(const void* p, uint64_t pol) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(pol));
+    return v;
+}
+
 // Eight consecutive elements of a row as floats; `n` of them exist. VEC: 16-byte loads (every row
 // starts on a 16-byte boundary and V is a multiple of 8).
 template <int DT, bool VEC>
-__device__ __forceinline__ int lane_load8(const void* base, uint64_t row0, uint32_t v, uint32_t V, float z[8]) {
+__device__ __forceinline__ int lane_load8(const void* base, uint64_t row0, uint32_t v, uint32_t V, float z[8], uint64_t policy = 0) {
     Raw<DT> raw;
     const uint32_t e0 = v * kVec;
     int n = kVec;
     if (VEC) {
-        raw.load(base, row0 + e0);
+        if (NRL_SOFTMAX_HINT && policy) {
+            if constexpr (DT == NRL_BF16) {
+                raw.q = ldg_hint16((const uint16_t*)base + row0 + e0, policy);
+            } else {
+                raw.a = ldg_hint16((const float*)base + row0 + e0, policy);
+                raw.b = ldg_hint16((const float*)base + row0 + e0 + 4, policy);
+            }
+        } else {
+            raw.load(base, row0 + e0);
+        }
     } else {
         n = (int)(V - e0 < (uint32_t)kVec ? V - e0 : (uint32_t)kVec);
         raw.load_scalar(base, row0 + e0, n);
@@ -109,14 +140,14 @@ __device__ __forceinline__ bool arg_better(float e, uint32_t i, float best, uint
 // (−inf − −inf); the first finite element resets it, so a lane of −inf alone ends as NaN, as the
 // reference's (x − max).exp() does.
 template <int DT, bool VEC>
-__device__ __forceinline__ MaxSum lane_thread_maxsum(const void* x, uint64_t row0, uint32_t V, uint32_t nvec) {
+__device__ __forceinline__ MaxSum lane_thread_maxsum(const void* x, uint64_t row0, uint32_t V, uint32_t nvec, uint64_t policy = 0) {
     MaxSum p;
     p.m = NRL_NEG_INF;
     p.S = 0.f;
 #pragma unroll 2
     for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
         float z[8];
-        lane_load8<DT, VEC>(x, row0, v, V, z);
+        lane_load8<DT, VEC>(x, row0, v, V, z, policy);
         const float vmax = fmax_nan(fmax3_nan(z[0], z[1], z[2]), fmax_nan(fmax3_nan(z[3], z[4], z[5]), fmax_nan(z[6], z[7])));
         const float mn = fmax_nan(p.m, vmax);
         if (mn != p.m) {
@@ -135,14 +166,15 @@ template <int DT, bool VEC, bool LOG>
 __global__ void __launch_bounds__(kLaneMaxThreads) lane_softmax_kernel(const void* __restrict__ x, float* __restrict__ out, uint64_t rows, uint32_t V) {
     __shared__ float sh[2 * kLaneMaxWarps];
     const uint32_t nvec = (V + kVec - 1) / kVec;
+    const uint64_t keep = l2_policy_keep(), drop = l2_policy_drop();
     for (uint64_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint64_t row0 = row * V;
-        const MaxSum p = block_maxsum(lane_thread_maxsum<DT, VEC>(x, row0, V, nvec), sh);
+        const MaxSum p = block_maxsum(lane_thread_maxsum<DT, VEC>(x, row0, V, nvec, keep), sh);
         const float m = p.m, lnS = logf(p.S), inv = 1.f / p.S;
 #pragma unroll 2
         for (uint32_t v = threadIdx.x; v < nvec; v += blockDim.x) {
             float z[8], y[8];
-            const int n = lane_load8<DT, VEC>(x, row0, v, V, z);
+            const int n = lane_load8<DT, VEC>(x, row0, v, V, z, drop);
 #pragma unroll
             for (int i = 0; i < 8; i++) y[i] = LOG ? (z[i] - m) - lnS : ex2_approx((z[i] - m) * kLog2e) * inv;
             lane_store8<VEC>(out, row0, v, n, y);
@@ -276,13 +308,30 @@ __global__ void __launch_bounds__(kLaneThreads) lane_sum_ordered_kernel(const vo
         float p = 0.f;
         uint32_t j = 0;
         if (live) {
-            for (; j + 32 <= full; j += 32) {
-                float t[32];
+            // Two batches of kSumDepth loads: the next batch is issued before the current one is added, so
+            // loads are in flight during the dependent adds too (eight threads per row leave an SM few
+            // warps; what hides the latency is the depth per thread).
+            constexpr int kSumDepth = 48;
+            float t[2][kSumDepth];
+            const uint32_t nb = full / kSumDepth;  // whole batches
+            auto load = [&](float* dst, uint32_t b) {
 #pragma unroll
-                for (int u = 0; u < 32; u++) t[u] = lane_elem<DT>(x, row0 + (uint64_t)(j + u) * 8 + k);
+                for (int u = 0; u < kSumDepth; u++) dst[u] = lane_elem<DT>(x, row0 + (uint64_t)(b * kSumDepth + u) * 8 + k);
+            };
+            auto add = [&](const float* src) {
 #pragma unroll
-                for (int u = 0; u < 32; u++) p = __fadd_rn(p, t[u]);
+                for (int u = 0; u < kSumDepth; u++) p = __fadd_rn(p, src[u]);
+            };
+            if (nb > 0) load(t[0], 0);
+            for (uint32_t b = 0; b < nb; b += 2) {
+                if (b + 1 < nb) load(t[1], b + 1);
+                add(t[0]);
+                if (b + 1 < nb) {
+                    if (b + 2 < nb) load(t[0], b + 2);
+                    add(t[1]);
+                }
             }
+            j = nb * kSumDepth;
             for (; j < full; j++) p = __fadd_rn(p, lane_elem<DT>(x, row0 + (uint64_t)j * 8 + k));
         }
         const float q = __fadd_rn(p, __shfl_down_sync(0xffffffffu, p, 4, 8));  // lanes 0..3 of the row: p_k + p_{k+4}

@@ -24,7 +24,7 @@
 //   src/tensor/autodiff.rs:141-215 run_backward: burn's traversal, gradients summed `new + old`
 //   src/tensor/activation.rs:30-42 log_softmax as one node, backward g − exp(y)·Σg
 //
-// Parity status: the Rust reference cannot be compiled on this machine (no rustc/cargo), so this
+// Parity status: the Rust reference was not compiled for this build (no Rust toolchain), so this
 // restatement is pinned against the hand-computed values and identities in the reference's own
 // tests (src/nn/tests/rl.rs), restated in tests/test_oracle_golden.py. Rust's f32::exp / ln call
 // the platform libm, as expf / logf do here; the build uses -ffp-contract=off and no fast-math
