@@ -507,7 +507,12 @@ int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64
  * nrl_readout_workspace_bytes(rows, V, d) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
  * a NaN, bit 2 the kernel gave up a bounded wait (an internal error: outputs of that row are NaN).
  * Results are bitwise reproducible run to run. */
-enum { NRL_READOUT_W_VD = 1u << 0, NRL_READOUT_ROUND_BF16 = 1u << 1 };
+enum {
+    NRL_READOUT_W_VD = 1u << 0,
+    NRL_READOUT_ROUND_BF16 = 1u << 1,
+    NRL_READOUT_ONE_CTA = 1u << 2 /* one CTA per 128-row block (tcgen05 cta_group::1) instead of CTA pairs on 256-row blocks
+                                    (cta_group::2, the default for more than 128 rows); the results are the same bits */
+};
 
 typedef struct nrl_readout_args {
     uint32_t struct_size;

@@ -504,38 +504,39 @@ extern "C" int nrl_check_scored_finite(nrl_devptr logp, nrl_devptr mask, uint64_
 
 // ---- readout-fused row statistics (tcgen05) ---------------------------------------------------------
 
-// Column ranges per row block. CTAs that run together (one wave of 148) are a group of row blocks
-// times every column range, and the group's hidden states (128 · d · 2 bytes per row block) must
-// stay in L2 while its CTAs walk the vocabulary: measured on B200 at d = 4096, 18 944 rows reach
-// 0.82 PFLOP/s with one range (148 MB of hidden states in flight) and 1.24 with four (37 MB).
-// When all the hidden states fit anyway, the count (at most 16, each range at least 8 tiles) that
-// fills the waves best is taken. A function of (rows, V, d) only.
-static uint32_t readout_nsplit(uint64_t rows, uint32_t V, uint32_t d) {
-    const uint64_t rb = (rows + kRoBM - 1) / kRoBM;
+// Column ranges per row block. Work is laid out in groups: a group is some row blocks times every
+// column range, at most one wave of CTAs (148) or CTA pairs (74), and runs as one wave, so that the
+// group's hidden states (rows · d · 2 bytes) stay in L2 while its CTAs walk the vocabulary and each W
+// tile is fetched once per group. Measured on B200 at d = 4096: 18 944 rows reach 0.82 PFLOP/s
+// with one range (148 MB of hidden states in flight) and 1.24 with four (37 MB). The count taken
+// (at most 16, each range at least 8 tiles) is the one that fills the waves best among those whose
+// group keeps at most 40 MB of hidden states in flight. A function of (rows, V, d) only.
+static uint32_t readout_nsplit(uint64_t rows, uint32_t V, uint32_t d, bool pairs) {
+    // the unit is a CTA (128 rows, 148 per wave) or a CTA pair (256 rows, 74 per wave)
+    const uint64_t unit_rows = pairs ? 2 * kRoBM : kRoBM, wave = pairs ? 74 : 148;
+    const uint64_t rb = (rows + unit_rows - 1) / unit_rows;
     const uint32_t tiles = (V + kRoBN - 1) / kRoBN;
-    const uint64_t block_bytes = (uint64_t)kRoBM * d * 2;
-    uint64_t fit = (40ull << 20) / block_bytes;  // row blocks whose hidden states may be in flight
-    if (fit < 1) fit = 1;
-    if (rb > fit + fit / 2) {
-        uint32_t s = (uint32_t)((148 + fit - 1) / fit);
-        if (s < 4) s = 4;
-        if (s > 16) s = 16;
-        while (s > 1 && tiles / s < 8) s--;
-        return s;
+    const uint64_t block_bytes = unit_rows * d * 2;
+    uint32_t best = 0;
+    double best_eff = -1.0;
+    for (int pass = 0; pass < 2 && !best; pass++) {  // second pass: no count meets the footprint, take the best anyway
+        for (uint32_t s = 1; s <= 16 && (s == 1 || tiles / s >= 8); s++) {
+            uint64_t gb = wave / s;
+            if (gb < 1) gb = 1;
+            if (gb > rb) gb = rb;
+            if (pass == 0 && gb * block_bytes > (40ull << 20)) continue;
+            const uint64_t ctas = rb * s;
+            const double eff = (double)ctas / (double)(wave * ((ctas + wave - 1) / wave));
+            if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+        }
     }
-    uint32_t best = 1;
-    double best_eff = 0.0;
-    for (uint32_t s = 1; s <= 16 && (s == 1 || tiles / s >= 8); s++) {
-        const uint64_t ctas = rb * s;
-        const double eff = (double)ctas / (148.0 * (double)((ctas + 147) / 148));
-        if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
-    }
-    return best;
+    return best ? best : 1;
 }
 
 extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d) {
     if (rows == 0 || V == 0 || d == 0) return 0;
-    return rows * readout_nsplit(rows, V, d) * kRoPartFloats * sizeof(float);
+    const uint32_t a = readout_nsplit(rows, V, d, false), b = readout_nsplit(rows, V, d, true);
+    return rows * (a > b ? a : b) * kRoPartFloats * sizeof(float);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -564,7 +565,7 @@ static int encode_bf16_2d(CUtensorMap* map, uint64_t base, uint64_t inner, uint6
 extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
-    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 )) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA)) return NRL_E_BAD_ARG;
     // TMA wants 16-byte aligned bases and row pitches
     if (a->V % 8 != 0 || a->d % 8 != 0 || ((a->hidden | a->weights) & 15u)) return NRL_E_UNSUPPORTED;
     if ((a->tokens & 3u) || (a->logp & 3u) || (a->entropy & 3u) || (a->rowstats & 15u) || (a->logits_out & 3u) || (a->workspace & 15u)) return NRL_E_BAD_ARG;
@@ -580,11 +581,19 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     p.V = a->V;
     p.d = a->d;
     p.tiles = (a->V + kRoBN - 1) / kRoBN;
-    p.nsplit = readout_nsplit(a->rows, a->V, a->d);
-    const uint64_t rb = (a->rows + kRoBM - 1) / kRoBM;
-    if (rb * p.nsplit > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+    // CTA pairs where they measured faster (B200, d = 4096, V = 128 256: 1.50 / 1.44 PFLOP/s against 1.22 / 1.27 at 8192 /
+    // 18 944 rows). Beyond a few waves one CTA per block is the faster and the safer choice (1.34 against 1.15 at 65 536
+    // rows): the W tiles are shared through L2 by the CTAs that walk a column range in step, a wave of 74 pairs does not
+    // divide into equal groups, and groups that straddle waves fall out of step (ncu: 200 GB of DRAM reads instead of 16).
+    const bool pairs = !(a->flags & NRL_READOUT_ONE_CTA) && a->rows > (uint64_t)kRoBM && a->rows <= 24576;
+    p.nsplit = readout_nsplit(a->rows, a->V, a->d, pairs);
+    const uint64_t unit_rows = pairs ? 2 * kRoBM : kRoBM;
+    const uint64_t rb = (a->rows + unit_rows - 1) / unit_rows;  // row blocks: CTAs or CTA pairs
+    if (rb * p.nsplit * 2 > 0x7fffffffull) return NRL_E_UNSUPPORTED;
     p.row_blocks = (uint32_t)rb;
-    p.group_blocks = (148u + p.nsplit - 1) / p.nsplit;
+    // a group (its row blocks x every column range) must not outgrow a wave, or waves would mix two groups' hidden states
+    p.group_blocks = (pairs ? 74u : 148u) / p.nsplit;
+    if (p.group_blocks < 1) p.group_blocks = 1;
     if (p.group_blocks > p.row_blocks) p.group_blocks = p.row_blocks;
     p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
     p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
@@ -595,18 +604,33 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     CUtensorMap mx, mw;
     int rc = encode_bf16_2d(&mx, a->hidden, a->d, a->rows, kRoBK, kRoBM);
     if (rc) return rc;
-    rc = p.w_is_vd ? encode_bf16_2d(&mw, a->weights, a->d, a->V, kRoBK, kRoBN) : encode_bf16_2d(&mw, a->weights, a->V, a->d, 64, kRoBK);
+    // W tiles: [V, d] as boxes of 64 k × 256 rows of W (128 for a pair: each CTA loads half a tile); [d, V] as boxes of 64 columns × 64 k
+    rc = p.w_is_vd ? encode_bf16_2d(&mw, a->weights, a->d, a->V, kRoBK, pairs ? kRoBN / 2 : kRoBN) : encode_bf16_2d(&mw, a->weights, a->V, a->d, 64, kRoBK);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
-    const unsigned grid = (unsigned)(rb * p.nsplit);
-    if (p.round_bf16) {
-        e = cudaFuncSetAttribute(readout_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        readout_fwd_kernel<true><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+    if (pairs) {
+        const uint64_t groups = (rb + p.group_blocks - 1) / p.group_blocks;
+        const unsigned grid = (unsigned)(groups * p.group_blocks * p.nsplit * 2);  // one cluster of two CTAs per work item
+        if (p.round_bf16) {
+            e = cudaFuncSetAttribute(readout_fwd_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes2);
+            if (e != cudaSuccess) return (int)e;
+            readout_fwd_pair_kernel<true><<<grid, kRoThreads, kRoSmemBytes2, st>>>(mx, mw, p);
+        } else {
+            e = cudaFuncSetAttribute(readout_fwd_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes2);
+            if (e != cudaSuccess) return (int)e;
+            readout_fwd_pair_kernel<false><<<grid, kRoThreads, kRoSmemBytes2, st>>>(mx, mw, p);
+        }
     } else {
-        e = cudaFuncSetAttribute(readout_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        readout_fwd_kernel<false><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+        const unsigned grid = (unsigned)(rb * p.nsplit);
+        if (p.round_bf16) {
+            e = cudaFuncSetAttribute(readout_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
+            if (e != cudaSuccess) return (int)e;
+            readout_fwd_kernel<true><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+        } else {
+            e = cudaFuncSetAttribute(readout_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
+            if (e != cudaSuccess) return (int)e;
+            readout_fwd_kernel<false><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
+        }
     }
     rc = after_launch();
     if (rc) return rc;

@@ -143,6 +143,77 @@ __device__ __forceinline__ void readout_tile_range(const ReadoutParams& p, uint3
     t1 = min(t0 + per, p.tiles);
 }
 
+// One finished 256-column tile of one row (this thread's lane of tensor memory at `taddr`) folded
+// into the row's running (m, S, W) at maximum m, and the given token's logit picked up if the
+// tile holds it. Columns are taken 32 at a time in index order.
+template <bool ROUND>
+__device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32_t taddr, uint32_t t, uint64_t row, bool live, int32_t tok, float& m, float& S, float& W, float& ztok) {
+    float ts = 0.f, tw = 0.f;  // this tile's sums at the running maximum
+#pragma unroll 1
+    for (int c = 0; c < kRoBN / 32; c++) {
+        uint32_t r[32];
+        tc_ld32(taddr + c * 32, r);
+        tc_wait_ld();
+        const uint32_t col0 = t * kRoBN + c * 32;
+        float z[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            float v = __uint_as_float(r[i]);
+            if (ROUND) v = round_through_bf16(v);
+            z[i] = v;
+        }
+        if (col0 + 32 > p.V) {  // past the vocabulary (TMA filled zeros there): exclude
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (col0 + i >= p.V) z[i] = -FLT_MAX;
+        }
+        if (p.logits_out && live) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                if (col0 + i + 1 < p.V) {
+                    const uint32_t lo = __float_as_uint(round_through_bf16(z[i])) >> 16, hi = __float_as_uint(round_through_bf16(z[i + 1])) & 0xffff0000u;
+                    *reinterpret_cast<uint32_t*>(p.logits_out + row * p.V + col0 + i) = lo | hi;
+                } else if (col0 + i < p.V) {
+                    p.logits_out[row * p.V + col0 + i] = (uint16_t)(__float_as_uint(round_through_bf16(z[i])) >> 16);
+                }
+            }
+        }
+        if (tok >= (int32_t)col0 && tok < (int32_t)(col0 + 32)) {
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if ((int32_t)(col0 + i) == tok) ztok = z[i];
+        }
+        float cm = fmax3_nan(z[0], z[1], z[2]);
+#pragma unroll
+        for (int i = 3; i < 31; i += 2) cm = fmax3_nan(cm, z[i], z[i + 1]);
+        cm = fmax_nan(cm, z[31]);
+        cm = fmax_nan(cm, -FLT_MAX);  // a −inf logit is folded as −FLT_MAX: exp underflows to 0 either way and 0·inf cannot appear
+        if (!(cm <= m)) {  // a new maximum (or a NaN): move the sums
+            if (m != NRL_NEG_INF) {
+                const float dm = m - cm, sc = expf(dm);
+                W = (W + S * dm) * sc;
+                S *= sc;
+                tw = (tw + ts * dm) * sc;
+                ts *= sc;
+            }
+            m = cm;
+        }
+        // three levels of sums (32 columns, a tile, the range) keep the rounding of the long f32 sums small
+        float cs = 0.f, cw = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+            const float tt = fmaxf(z[i], -FLT_MAX) - m;
+            const float e = ex2_approx(tt * kLog2e);
+            cs += e;
+            cw = fmaf(e, tt, cw);
+        }
+        ts += cs;
+        tw += cw;
+    }
+    S += ts;
+    W += tw;
+}
+
 template <bool ROUND>
 __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ReadoutParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -263,71 +334,7 @@ __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid
             const uint32_t n = t - t0, acc = n & 1u;
             if (!mbar_wait(bar_acc_full + 8 * acc, (n >> 1) & 1u, &abort_flag)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t taddr = tmem + ((quarter * 32u) << 16) + acc * kRoBN;
-            float ts = 0.f, tw = 0.f;  // this tile's sums at the running maximum
-#pragma unroll 1
-            for (int c = 0; c < kRoBN / 32; c++) {
-                uint32_t r[32];
-                tc_ld32(taddr + c * 32, r);
-                tc_wait_ld();
-                const uint32_t col0 = t * kRoBN + c * 32;
-                float z[32];
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float v = __uint_as_float(r[i]);
-                    if (ROUND) v = round_through_bf16(v);
-                    z[i] = v;
-                }
-                if (col0 + 32 > p.V) {  // past the vocabulary (TMA filled zeros there): exclude
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (col0 + i >= p.V) z[i] = -FLT_MAX;
-                }
-                if (p.logits_out && live) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        if (col0 + i + 1 < p.V) {
-                            const uint32_t lo = __float_as_uint(round_through_bf16(z[i])) >> 16, hi = __float_as_uint(round_through_bf16(z[i + 1])) & 0xffff0000u;
-                            *reinterpret_cast<uint32_t*>(p.logits_out + row * p.V + col0 + i) = lo | hi;
-                        } else if (col0 + i < p.V) {
-                            p.logits_out[row * p.V + col0 + i] = (uint16_t)(__float_as_uint(round_through_bf16(z[i])) >> 16);
-                        }
-                    }
-                }
-                if (tok >= (int32_t)col0 && tok < (int32_t)(col0 + 32)) {
-#pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if ((int32_t)(col0 + i) == tok) ztok = z[i];
-                }
-                float cm = fmax3_nan(z[0], z[1], z[2]);
-#pragma unroll
-                for (int i = 3; i < 31; i += 2) cm = fmax3_nan(cm, z[i], z[i + 1]);
-                cm = fmax_nan(cm, z[31]);
-                cm = fmax_nan(cm, -FLT_MAX);  // a −inf logit is folded as −FLT_MAX: exp underflows to 0 either way and 0·inf cannot appear
-                if (!(cm <= m)) {  // a new maximum (or a NaN): move the sums
-                    if (m != NRL_NEG_INF) {
-                        const float dm = m - cm, sc = expf(dm);
-                        W = (W + S * dm) * sc;
-                        S *= sc;
-                        tw = (tw + ts * dm) * sc;
-                        ts *= sc;
-                    }
-                    m = cm;
-                }
-                // three levels of sums (32 columns, a tile, the range) keep the rounding of the long f32 sums small
-                float cs = 0.f, cw = 0.f;
-#pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    const float tt = fmaxf(z[i], -FLT_MAX) - m;
-                    const float e = ex2_approx(tt * kLog2e);
-                    cs += e;
-                    cw = fmaf(e, tt, cw);
-                }
-                ts += cs;
-                tw += cw;
-            }
-            S += ts;
-            W += tw;
+            readout_fold_tile<ROUND>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
             // this accumulator may be overwritten once all four epilogue warps are done with it
             tc_fence_before();
             __syncwarp();
@@ -352,6 +359,227 @@ __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+}
+
+// ---- the same kernel on CTA pairs (cta_group::2) ---------------------------------------------------
+//
+// Two CTAs of a cluster, on two SMs, work on one 256-row block: CTA r of the pair owns rows
+// 128·r … of it (its hidden-state tiles, its 128 lanes of tensor memory, its epilogue) and loads
+// only HALF of each W tile (128 of the 256 columns); one thread of the pair's first CTA issues
+// tcgen05.mma.cta_group::2 (M 256, N 256), which reads both CTAs' shared memory and writes both
+// CTAs' accumulators. Per unit of tensor work an SM then takes 32 KB instead of 48 KB out of L2,
+// and the freed shared memory holds six stages instead of four.
+//   loads:     cp.async.bulk.tensor.2d.cta_group::2 (no multicast), every copy of the pair
+//              completing on the FIRST CTA's `full` barrier, which expects both CTAs' bytes;
+//   hand-back: tcgen05.commit.cta_group::2 … multicast::cluster to the `empty` barriers of both
+//              CTAs (each CTA's loader waits on its own) and to both `accumulator full` barriers;
+//   epilogue:  both CTAs' epilogue warps arrive on the first CTA's `accumulator empty` barrier
+//              (a remote mbarrier arrive for the second CTA).
+// Waits are bounded as above; the pair meets at a cluster barrier before either CTA exits.
+constexpr int kRoStages2 = 6;
+constexpr uint32_t kRoBBytes2 = kRoBBytes / 2;                 // 16 KB: this CTA's half of the W tile
+constexpr uint32_t kRoStageBytes2 = kRoABytes + kRoBBytes2;    // 32 KB
+constexpr uint32_t kRoSmemBytes2 = kRoStages2 * kRoStageBytes2 + 1024 + 256;
+// a shared-memory address of this CTA -> the address of the same offset in the cluster's first CTA
+__device__ __forceinline__ uint32_t in_first_cta(uint32_t addr) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(0u));
+    return r;
+}
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int32_t x, int32_t y, uint32_t bar_in_first_cta) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map), "r"(x), "r"(y),
+                 "r"(bar_in_first_cta)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {  // arrives on `bar` in both CTAs of the pair
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Work items are (256-row block, column range) pairs laid out in groups as above; the grid holds
+// `gridDim.x / 2 / (group_blocks · nsplit)` groups' worth of clusters and a cluster walks the groups
+// with that stride (one cluster per item when the grid covers every group).
+template <bool ROUND>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kRoThreads, 1)
+    readout_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ReadoutParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base = smem_base, b_base = smem_base + kRoStages2 * kRoABytes;
+    const uint32_t bars = smem_base + kRoStages2 * kRoStageBytes2;
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * kRoStages2, bar_acc_full = bars + 16 * kRoStages2, bar_acc_empty = bar_acc_full + 16, bar_done = bar_acc_empty + 16;
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();  // 0: issues the products; both load and fold
+    const uint32_t per_group = p.group_blocks * p.nsplit;  // row_blocks, group_blocks: in 256-row blocks
+    const uint32_t cluster = (blockIdx.x >> 1) % per_group, group0 = (blockIdx.x >> 1) / per_group, gstride = max(1u, (gridDim.x >> 1) / per_group);
+    const uint32_t ngroups = (p.row_blocks + p.group_blocks - 1) / p.group_blocks;
+    const uint32_t kchunks = (p.d + kRoBK - 1) / kRoBK;
+    // work item of this cluster in group g: false when the group has fewer items than the wave has clusters
+    auto item = [&](uint32_t g, uint32_t& split, uint32_t& rb, uint32_t& t0, uint32_t& t1) -> bool {
+        const uint32_t in_group = min(p.group_blocks, p.row_blocks - g * p.group_blocks);
+        if (cluster >= in_group * p.nsplit) return false;
+        split = cluster / in_group;
+        rb = (g * p.group_blocks + cluster % in_group) * 2 + rank;  // this CTA's 128-row block
+        readout_tile_range(p, split, t0, t1);
+        return true;
+    };
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0u;
+        for (int s = 0; s < kRoStages2; s++) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(bar_acc_full + 8 * a, 1);
+            mbar_init(bar_acc_empty + 8 * a, 8);  // four epilogue warps of each CTA
+        }
+        mbar_init(bar_done, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_addr(&tmem_slot)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        tc_fence_before();
+    }
+    __syncthreads();
+    cluster_sync_all();  // both CTAs' barriers exist before anything crosses between them
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+
+    if (warp == 0) {
+        // ---- loader (both CTAs) -------------------------------------------------------------------
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (uint32_t g = group0; g < ngroups && ok; g += gstride) {
+                uint32_t split, rb, t0, t1;
+                if (!item(g, split, rb, t0, t1)) continue;
+                for (uint32_t t = t0; t < t1 && ok; t++) {
+                    for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
+                        const uint32_t s = it % kRoStages2;
+                        if (!mbar_wait(bar_empty + 8 * s, ((it / kRoStages2) & 1u) ^ 1u, &abort_flag)) { ok = false; break; }
+                        const uint32_t full_first = in_first_cta(bar_full + 8 * s);
+                        if (rank == 0) mbar_expect_tx(bar_full + 8 * s, 2 * kRoStageBytes2);  // both CTAs' copies land on this barrier
+                        tma_load_2d_pair(a_base + s * kRoABytes, &map_x, (int32_t)(kc * kRoBK), (int32_t)(rb * kRoBM), full_first);
+                        const uint32_t n0 = t * kRoBN + rank * (kRoBN / 2);  // this CTA's half of the tile's columns
+                        if (p.w_is_vd) {
+                            tma_load_2d_pair(b_base + s * kRoBBytes2, &map_w, (int32_t)(kc * kRoBK), (int32_t)n0, full_first);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < kRoBN / 128; j++)
+                                tma_load_2d_pair(b_base + s * kRoBBytes2 + j * (kRoBK * 128), &map_w, (int32_t)(n0 + j * 64), (int32_t)(kc * kRoBK), full_first);
+                        }
+                    }
+                }
+            }
+            if ((!ok || abort_flag) && it) {
+                // give this CTA's copies in flight time to land before the pair may end (their completion is
+                // counted on the first CTA's barrier, which this CTA cannot wait on by phase: a bounded sleep)
+                const unsigned long long t_start = global_ns();
+                while (global_ns() - t_start < 2000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue (first CTA only) -------------------------------------------------------
+        if (rank == 0 && lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((p.w_is_vd ? 0u : 1u) << 16) | ((uint32_t)(kRoBN >> 3) << 17) | ((uint32_t)((2 * kRoBM) >> 4) << 24);
+            uint32_t it = 0, n = 0;
+            bool ok = true;
+            for (uint32_t g = group0; g < ngroups && ok; g += gstride) {
+                uint32_t split, rb, t0, t1;
+                if (!item(g, split, rb, t0, t1)) continue;
+                for (uint32_t t = t0; t < t1 && ok; t++, n++) {
+                    const uint32_t acc = n & 1u;
+                    if (!mbar_wait(bar_acc_empty + 8 * acc, ((n >> 1) & 1u) ^ 1u, &abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem + acc * kRoBN;
+                    for (uint32_t kc = 0; kc < kchunks; kc++, it++) {
+                        const uint32_t s = it % kRoStages2;
+                        if (!mbar_wait(bar_full + 8 * s, (it / kRoStages2) & 1u, &abort_flag)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t a_addr = a_base + s * kRoABytes, b_addr = b_base + s * kRoBBytes2;
+#pragma unroll
+                        for (int k = 0; k < kRoBK / 16; k++) {
+                            const uint64_t da = smem_desc_sw128(a_addr + k * 32, 16, 1024);
+                            const uint64_t db = p.w_is_vd ? smem_desc_sw128(b_addr + k * 32, 16, 1024) : smem_desc_sw128(b_addr + k * 2048, kRoBK * 128, 1024);
+                            tc_mma_bf16_pair(d_tmem, da, db, idesc, (kc | (uint32_t)k) != 0u);
+                        }
+                        tc_commit_pair(bar_empty + 8 * s);
+                    }
+                    if (ok) tc_commit_pair(bar_acc_full + 8 * acc);
+                }
+            }
+            tc_commit_pair(bar_done);
+        }
+    } else {
+        // ---- epilogue (both CTAs): thread = row ----------------------------------------------------------
+        const uint32_t quarter = (uint32_t)warp & 3u;
+        const uint32_t r_in_block = quarter * 32u + (uint32_t)lane;
+        uint32_t n = 0;
+        bool ok = true;
+        for (uint32_t g = group0; g < ngroups; g += gstride) {
+            uint32_t split, rb, t0, t1;
+            if (!item(g, split, rb, t0, t1)) continue;
+            const uint64_t row = (uint64_t)rb * kRoBM + r_in_block;
+            const bool live = row < p.rows;
+            const int32_t tok = (live && p.tokens) ? p.tokens[row] : -1;
+            float m = NRL_NEG_INF, S = 0.f, W = 0.f, ztok = __int_as_float(0x7fc00000);
+            for (uint32_t t = t0; t < t1 && ok; t++, n++) {
+                const uint32_t acc = n & 1u;
+                if (!mbar_wait(bar_acc_full + 8 * acc, (n >> 1) & 1u, &abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                readout_fold_tile<ROUND>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(in_first_cta(bar_acc_empty + 8 * acc));
+            }
+            if (live) {
+                float4 out = make_float4(m, S, W, ztok);
+                if (!ok || abort_flag) out = make_float4(0.f, -1.f, 0.f, 0.f);  // "gave up": also for the items not reached
+                reinterpret_cast<float4*>(p.parts)[row * p.nsplit + split] = out;
+            }
+        }
+    }
+
+    // ---- teardown ------------------------------------------------------------------------------------
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        if (lane == 0) {
+            volatile uint32_t never = 0u;
+            mbar_wait(bar_done, 0u, &never, 20000000ull);  // every product has finished (multicast to both CTAs)
+        }
+        __syncwarp();
+    }
+    cluster_sync_all();  // neither CTA leaves while the other may still reach into its shared or tensor memory
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
     }
 }
 

@@ -421,7 +421,7 @@ class Readout:
     __slots__ = ("logp", "entropy", "rowstats", "status", "logits")
 
 
-def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None):
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False):
     """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
     `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
     `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
@@ -435,7 +435,7 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     _need(weights, torch.bfloat16, (V, d) if weights_are_vd else (d, V), "weights", dev)
     a = capi.ReadoutArgs()
     a.struct_size = C.sizeof(a)
-    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0)
+    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0)
     a.V, a.d, a.rows = V, d, rows
     a.hidden, a.weights = _p(hidden), _p(weights)
     out = Readout()

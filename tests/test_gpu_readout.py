@@ -108,3 +108,22 @@ def test_readout_refusals_and_status():
         ops.readout_forward(x[:, :60].contiguous(), w[:60].contiguous(), tokens=tok)  # d not a multiple of 8
     with pytest.raises(capi.NrlError):
         ops.readout_forward(x, w, tokens=tok, workspace=torch.empty(16, dtype=torch.uint8, device=dev()))
+
+
+@pytest.mark.parametrize("rows,d,V", [(129, 64, 512), (300, 4096, 128256), (2500, 1024, 16384), (513, 72, 776)])
+@pytest.mark.parametrize("layout", ["dV", "Vd"])
+def test_readout_cta_pairs_give_the_single_cta_bits(rows, d, V, layout):
+    """More than 128 rows run on CTA pairs (tcgen05 cta_group::2: one product over two SMs, each
+    loading half of every W tile); NRL_READOUT_ONE_CTA keeps one CTA per 128 rows. The products and
+    the fold are the same operations in the same order: the same bits."""
+    from noetic_tensor_b200 import ops
+
+    x, w, tok = make(rows, d, V, 11 * rows + V)
+    wa = w.t().contiguous() if layout == "Vd" else w
+    for rnd in (False, True):
+        a = ops.readout_forward(x, wa, tokens=tok, weights_are_vd=(layout == "Vd"), round_bf16=rnd, want_logits=True)
+        b = ops.readout_forward(x, wa, tokens=tok, weights_are_vd=(layout == "Vd"), round_bf16=rnd, want_logits=True, one_cta=True)
+        assert (a.status == 0).all() and (b.status == 0).all()
+        assert torch.equal(a.logits.view(torch.int16), b.logits.view(torch.int16))
+        for name in ("logp", "entropy", "rowstats"):
+            assert torch.equal(getattr(a, name).view(torch.int32), getattr(b, name).view(torch.int32)), (name, rnd)
