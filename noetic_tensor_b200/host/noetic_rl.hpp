@@ -540,6 +540,44 @@ inline Tensor token_log_probs(const Tensor& logits, const IntTensor& tokens) {
     return logp;
 }
 
+// `token_log_probs(head(x), tokens)` and `categorical_entropy(head(x))` per position without the
+// [.., V] logits in between (src/nn/decoder.rs:270-279 followed by src/nn/rl.rs:134-141, 405-414):
+// `hidden` BF16 [.., d], `weight` BF16 [d, V] (the Linear's [in, out] layout, src/nn/linear.rs:1-3),
+// tokens [..]. Returns the log-probabilities [..] and, if asked, the per-position entropies.
+// Untracked: the backward of the fused form (d hidden, d weight) is not built; needs a
+// compute-capability-10 device (tcgen05). `round_bf16`: statistics of the logits rounded to bf16.
+inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, const IntTensor& tokens, Tensor* entropy = nullptr, bool round_bf16 = false) {
+    if (hidden.dtype() != DType::BF16 || weight.dtype() != DType::BF16) throw std::runtime_error("head_token_log_probs: BF16 hidden states and weight");
+    if (hidden.rank() < 1 || weight.rank() != 2 || weight.shape()[0] != hidden.shape().back()) throw std::runtime_error("head_token_log_probs: hidden [.., d], weight [d, V]");
+    const Shape lead(hidden.shape().begin(), hidden.shape().end() - 1);
+    if (tokens.shape != lead) throw std::runtime_error("token_log_probs: tokens shape (the logits' without the vocabulary axis)");
+    const uint64_t d = weight.shape()[0], V = weight.shape()[1], rows = numel(lead);
+    std::vector<int32_t> h(tokens.data.begin(), tokens.data.end());
+    for (int64_t t : tokens.data)
+        if (t < 0 || (uint64_t)t >= V) throw std::runtime_error("gather index out of range");
+    Tensor tok = Tensor::empty(Shape{(size_t)rows}, DType::I32, hidden.device());
+    cu(cudaMemcpy(tok.ptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice), "upload tokens");
+    Tensor logp = Tensor::empty(lead, DType::F32, hidden.device());
+    Tensor status = Tensor::empty(Shape{(size_t)rows}, DType::U8, hidden.device());
+    const uint64_t need = nrl_readout_workspace_bytes(rows, (uint32_t)V, (uint32_t)d);
+    Tensor ws = Tensor::empty(Shape{(size_t)need}, DType::U8, hidden.device());
+    nrl_readout_args a;
+    std::memset(&a, 0, sizeof a);
+    a.struct_size = sizeof a;
+    a.flags = round_bf16 ? NRL_READOUT_ROUND_BF16 : 0u;
+    a.V = (uint32_t)V; a.d = (uint32_t)d; a.rows = rows;
+    a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev();
+    a.logp = logp.dev(); a.status = status.dev();
+    if (entropy) {
+        *entropy = Tensor::empty(lead, DType::F32, hidden.device());
+        a.entropy = entropy->dev();
+    }
+    a.workspace = ws.dev(); a.workspace_bytes = need;
+    nrl(nrl_readout_fwd(&a, detail::stream()), "readout_fwd");
+    cu(cudaStreamSynchronize(detail::stream()), "sync");  // the workspace goes out of scope here
+    return logp;
+}
+
 // src/nn/rl.rs:204-211: every scored log-probability (mask != 0; no mask: all) is finite. Returns
 // an empty string, or the reference's error text naming the first flat position. A host read.
 inline std::string check_scored_finite(const std::string& what, const Tensor& logp, const Tensor* mask) {

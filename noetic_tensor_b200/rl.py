@@ -257,3 +257,14 @@ def reference_kl(logits, ref_logits, temperature, vocab_mask=None, mask=None, re
 def categorical_entropy(logits, mask=None, reduction=TOKEN_MEAN):
     """categorical_entropy (src/nn/rl.rs:405-414)."""
     return _row_level("entropy", logits, None, mask, reduction)
+
+
+def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
+    """`token_log_probs(head(x), tokens)` and `categorical_entropy(head(x))` per position without the
+    logits in between (src/nn/decoder.rs:270-279, then src/nn/rl.rs:134-141, 405-414): `hidden`
+    bf16 [..., d], `weight` bf16 [d, V] (the Linear's [in, out] layout), tokens [...]. Returns
+    (log-probs [...], entropies [...]). Untracked; needs a compute-capability-10 device."""
+    lead = hidden.shape[:-1]
+    o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, tokens=tokens.reshape(-1).to(torch.int32).contiguous(), round_bf16=round_bf16)
+    ops.check_status(o.status)
+    return o.logp.reshape(lead), o.entropy.reshape(lead)

@@ -522,6 +522,47 @@ static void test_group_advantages() {
     CHECK(throws([] { rl::group_advantages_tensor(Tensor::from_f32({1, 2}, {2, 1}, dev), rl::GroupNorm::Std(0.0, true)); }, "at least 2"), "tensor n = 1 unbiased");
 }
 
+// ---- Decoder::head fused with token_log_probs / categorical_entropy (tcgen05) -------------------------
+static void test_head_token_log_probs() {
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, 0);
+    if (prop.major != 10) {
+        std::printf("    (skipped: needs compute capability 10.x, this device is %d.%d)\n", prop.major, prop.minor);
+        return;
+    }
+    const size_t S = 2, B = 3, T = 50, d = 72, V = 776;  // 300 rows: CTA pairs, a ragged last block, a ragged last tile
+    std::mt19937 gen(7);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::vector<float> x(S * B * T * d), w(d * V);
+    for (auto& v : x) v = through_bf16(nd(gen));
+    for (auto& v : w) v = through_bf16(nd(gen) * 0.35f);
+    std::vector<int64_t> tok(S * B * T);
+    for (size_t i = 0; i < tok.size(); i++) tok[i] = (int64_t)(gen() % V);
+    Tensor hx = Tensor::from_f32(x, {S, B, T, d}, dev, DType::BF16), hw = Tensor::from_f32(w, {d, V}, dev, DType::BF16);
+    IntTensor it = IntTensor::from_data(tok, Shape{S, B, T});
+    Tensor ent;
+    const std::vector<float> lp = rl::head_token_log_probs(hx, hw, it, &ent).to_vec(), en = ent.to_vec();
+    // f64 on the host: logits = x · w, then log-softmax and entropy
+    std::vector<double> want_lp(tok.size()), want_en(tok.size());
+    for (size_t r = 0; r < tok.size(); r++) {
+        std::vector<double> z(V, 0.0);
+        for (size_t k = 0; k < d; k++)
+            for (size_t v = 0; v < V; v++) z[v] += (double)x[r * d + k] * (double)w[k * V + v];
+        double m = z[0];
+        for (double v : z) m = std::max(m, v);
+        double Z = 0.0;
+        for (double v : z) Z += std::exp(v - m);
+        const double lse = m + std::log(Z);
+        double h = 0.0;
+        for (double v : z) h -= std::exp(v - lse) * (v - lse);
+        want_lp[r] = z[tok[r]] - lse;
+        want_en[r] = h;
+    }
+    close_all(lp, want_lp, 2e-5, "head_token_log_probs");
+    close_all(en, want_en, 2e-5, "head entropy");
+    CHECK(throws([&] { rl::head_token_log_probs(Tensor::from_f32(x, {S, B, T, d}, dev), hw, it); }, "BF16"), "f32 hidden states are refused");
+}
+
 // ---- check_scored_finite (src/nn/tests/rl.rs:837-855) -------------------------------------------
 static void test_check_scored_finite() {
     const float ninf = -std::numeric_limits<float>::infinity();
@@ -755,7 +796,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"sample_categorical (reference noise)", test_sample_categorical_reference},
-        {"group_advantages", test_group_advantages}, {"check_scored_finite", test_check_scored_finite}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
+        {"group_advantages", test_group_advantages}, {"check_scored_finite", test_check_scored_finite}, {"head + token_log_probs (readout-fused)", test_head_token_log_probs}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {
