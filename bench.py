@@ -490,9 +490,40 @@ def run_readout_variant(args):
                       "refused_rows": int((o.status != 0).sum().item())}))
 
 
+def run_gumbel_variant(args):
+    """Profiling variant: a step is one nrl_sample_gumbel launch (the reference's own Gumbel-max sampler on
+    the device) over `--rows` headline-shaped rows (default 4096). Not the headline."""
+    import torch
+
+    from noetic_tensor_b200 import capi, ops, synth
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    rows = args.rows or 4096
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(6)
+    x = synth.normal_logits(rows, V, 3.0, torch.bfloat16, gen, dev)
+    m = synth.grammar_masks(rows, V, gen, dev)
+    seed = bytes(range(32))
+    for _ in range(max(1, args.warmup)):
+        ops.sample_gumbel(x, seed, allow=m)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ops.sample_gumbel(x, seed, allow=m)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"metric": "rows/s Gumbel-max sampling with the reference's ChaCha20 noise, V=128256 bf16 (profiling variant, not the headline)", "value": rows / (ms * 1e-3), "unit": "rows/s",
+                      "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "config": {"workload": f"[{rows}, {V}] bf16 + U8 grammar masks"}, "gpu_launches": args.steps}))
+
+
 def run_ours(args):
     if args.variant == "readout":
         return run_readout_variant(args)
+    if args.variant == "gumbel":
+        return run_gumbel_variant(args)
     # stdout carries the one JSON line and nothing else: libraries that write to it (NCCL prints
     # its version there when the communicator comes up) are sent to stderr until the line is printed
     sys.stdout.flush()
@@ -841,7 +872,7 @@ def main():
     ap.add_argument("--seeds", type=int, default=0, help="cap the resident seeds per GPU (default: as many of the 8 as fit)")
     ap.add_argument("--e2e-rows", type=int, default=8192)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward", "bitmask", "readout"],
+    ap.add_argument("--variant", default="headline", choices=["headline", "unmasked", "backward", "bitmask", "readout", "gumbel"],
                     help="unmasked: drop the mask (for profiling the every-byte-read path); backward: time the d(logits) kernel alone; bitmask: the mask bit-packed; none of them is the headline")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
