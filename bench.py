@@ -427,7 +427,7 @@ def run_extras(dev, peak):
     hx = torch.randn(rows, d6, generator=gen, device=dev).to(torch.bfloat16)
     wt = (torch.randn(d6, V, generator=gen, device=dev) * (3.0 / d6 ** 0.5)).to(torch.bfloat16)
     tk = torch.randint(0, V, (rows,), generator=gen, device=dev, dtype=torch.int32)
-    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d6), dtype=torch.uint8, device=dev)
+    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d6, 0), dtype=torch.uint8, device=dev)
     lg = torch.empty(rows, V, dtype=torch.bfloat16, device=dev)
     t_fused = _time(lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws))
     t_round = _time(lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws, round_bf16=True))
@@ -465,7 +465,7 @@ def run_readout_variant(args):
     hx = torch.randn(rows, d, generator=gen, device=dev).to(torch.bfloat16)
     wt = (torch.randn(d, V, generator=gen, device=dev) * (3.0 / d ** 0.5)).to(torch.bfloat16)
     tk = torch.randint(0, V, (rows,), generator=gen, device=dev, dtype=torch.int32)
-    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d), dtype=torch.uint8, device=dev)
+    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d, 0), dtype=torch.uint8, device=dev)
     for _ in range(max(1, args.warmup)):
         ops.readout_forward(hx, wt, tokens=tk, workspace=ws, one_cta=args.readout_one_cta)
     torch.cuda.synchronize()

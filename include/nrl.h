@@ -497,19 +497,25 @@ int nrl_check_status(nrl_devptr status, uint64_t rows, nrl_stream stream, uint64
  * folds each finished 128 × 256 tile of logits into the rows' maximum, log-sum-exp and entropy
  * sums straight from tensor memory, so the logits are never written or re-read:
  *   rowstats[r] = (m, ln Z, 0, 0), entropy[r] = ln Z − Σ e_v (z_v − m) / Z,
- *   logp[r] = z_token − m − ln Z for the given token (NRL_FWD_TOKENS_IN semantics),
+ *   logp[r] = z_token − m − ln Z for the given token (NRL_FWD_TOKENS_IN semantics) or, with
+ *   NRL_READOUT_SAMPLE, for the token drawn by inverse CDF against the row's uniform; an optional
+ *   byte allow-mask excludes tokens as in nrl_row_fwd (tempered_logits' −inf mask),
  * with z = the f32 accumulators (the reference's logits are f32 too), or, with
  * NRL_READOUT_ROUND_BF16, z rounded to bf16 first — what a bf16 logits tensor handed to
  * nrl_row_fwd would hold. `hidden` is bf16 [rows, d], `weights` bf16 [d, V] (the reference's
  * layout) or, with NRL_READOUT_W_VD, [V, d]; d and V multiples of 8, both 16-byte aligned.
  * `logits_out` (optional, bf16 [rows, V]) receives the rounded logits, for comparisons.
  * Needs compute capability 10.x (NRL_E_UNSUPPORTED otherwise) and
- * nrl_readout_workspace_bytes(rows, V, d) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
+ * nrl_readout_workspace_bytes(rows, V, d, flags) bytes of scratch. status[r]: bit 0 no finite logit, bit 1
  * a NaN, bit 2 the kernel gave up a bounded wait (an internal error: outputs of that row are NaN).
  * Results are bitwise reproducible run to run. */
 enum {
     NRL_READOUT_W_VD = 1u << 0,
     NRL_READOUT_ROUND_BF16 = 1u << 1,
+    NRL_READOUT_SAMPLE = 1u << 3,  /* draw the tokens (inverse CDF against `uniforms`, as NRL_FWD_SAMPLE) instead of taking them:
+                                     `tokens` is then an output and `logp` the drawn tokens' log-probs. The pass logs each
+                                     row's mass per 64 columns; a second small kernel finds the 64 columns holding u·Z and
+                                     computes those 64 logits again (f32) to walk to the token */
     NRL_READOUT_ONE_CTA = 1u << 2 /* one CTA per 128-row block (tcgen05 cta_group::1) instead of CTA pairs on 256-row blocks
                                     (cta_group::2, the default for more than 128 rows); the results are the same bits */
 };
@@ -530,9 +536,13 @@ typedef struct nrl_readout_args {
     nrl_devptr logits_out;   /* out bf16 [rows, V], or 0 */
     nrl_devptr workspace;    /* scratch */
     uint64_t workspace_bytes;
+    nrl_devptr allow_mask;   /* u8 allow-mask as in nrl_row_fwd ([rows, V], or [1, V] with stride 0), or 0 */
+    uint64_t allow_row_stride; /* V or 0 */
+    nrl_devptr uniforms;     /* f32 [rows] in [0,1), for NRL_READOUT_SAMPLE; else 0 */
 } nrl_readout_args;
 
-uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d);
+/* scratch for a call with these flags (sampling adds 32 bytes per row and vocabulary tile) */
+uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags);
 int nrl_readout_fwd(const nrl_readout_args* args, nrl_stream stream);
 
 /* check_scored_finite (src/nn/rl.rs:204-211), the check the reference's losses run in debug

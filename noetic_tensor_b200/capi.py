@@ -99,11 +99,11 @@ class ReadoutArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("flags", u32), ("V", u32), ("d", u32), ("rows", u64),
         ("hidden", ptr), ("weights", ptr), ("tokens", ptr), ("logp", ptr), ("entropy", ptr), ("rowstats", ptr), ("status", ptr), ("logits_out", ptr),
-        ("workspace", ptr), ("workspace_bytes", u64),
+        ("workspace", ptr), ("workspace_bytes", u64), ("allow_mask", ptr), ("allow_row_stride", u64), ("uniforms", ptr),
     ]
 
 
-READOUT_W_VD, READOUT_ROUND_BF16, READOUT_ONE_CTA = 1, 2, 4
+READOUT_W_VD, READOUT_ROUND_BF16, READOUT_ONE_CTA, READOUT_SAMPLE = 1, 2, 4, 8
 
 LANE_SOFTMAX, LANE_LOG_SOFTMAX, LANE_LOGSUMEXP, LANE_ARGMAX, LANE_SUM, LANE_SOFTMAX_BWD, LANE_LOG_SOFTMAX_BWD, LANE_LOGSUMEXP_BWD = range(8)
 
@@ -136,7 +136,7 @@ SYMBOLS = {
     "nrl_host_pack_bits": (C.c_int, [u64, u32, C.c_void_p, C.c_void_p, u32]),
     "nrl_host_pack": (C.c_int, [C.POINTER(PackArgs)]),
     "nrl_unpack_rows": (C.c_int, [C.POINTER(UnpackArgs), C.c_void_p]),
-    "nrl_readout_workspace_bytes": (u64, [u64, u32, u32]),
+    "nrl_readout_workspace_bytes": (u64, [u64, u32, u32, u32]),
     "nrl_readout_fwd": (C.c_int, [C.POINTER(ReadoutArgs), C.c_void_p]),
     "nrl_check_status": (C.c_int, [ptr, u64, C.c_void_p, C.POINTER(u64), C.POINTER(u32)]),
     "nrl_check_scored_finite": (C.c_int, [ptr, ptr, u64, ptr, C.c_void_p, C.POINTER(u64), C.POINTER(f32)]),

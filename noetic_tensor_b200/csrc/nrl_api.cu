@@ -533,10 +533,16 @@ static uint32_t readout_nsplit(uint64_t rows, uint32_t V, uint32_t d, bool pairs
     return best ? best : 1;
 }
 
-extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d) {
-    if (rows == 0 || V == 0 || d == 0) return 0;
+static uint64_t readout_parts_bytes(uint64_t rows, uint32_t V, uint32_t d) {
     const uint32_t a = readout_nsplit(rows, V, d, false), b = readout_nsplit(rows, V, d, true);
-    return rows * (a > b ? a : b) * kRoPartFloats * sizeof(float);
+    return (rows * (a > b ? a : b) * kRoPartFloats * sizeof(float) + 255) & ~255ull;
+}
+
+extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags) {
+    if (rows == 0 || V == 0 || d == 0) return 0;
+    uint64_t n = readout_parts_bytes(rows, V, d);
+    if (flags & NRL_READOUT_SAMPLE) n += rows * (uint64_t)((V + kRoBN - 1) / kRoBN) * (kRoBN / kRoLogCols) * sizeof(float2);
+    return n;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -565,11 +571,14 @@ static int encode_bf16_2d(CUtensorMap* map, uint64_t base, uint64_t inner, uint6
 extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
-    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA)) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA | NRL_READOUT_SAMPLE)) return NRL_E_BAD_ARG;
     // TMA wants 16-byte aligned bases and row pitches
     if (a->V % 8 != 0 || a->d % 8 != 0 || ((a->hidden | a->weights) & 15u)) return NRL_E_UNSUPPORTED;
     if ((a->tokens & 3u) || (a->logp & 3u) || (a->entropy & 3u) || (a->rowstats & 15u) || (a->logits_out & 3u) || (a->workspace & 15u)) return NRL_E_BAD_ARG;
     if (a->logp && !a->tokens) return NRL_E_BAD_ARG;
+    const bool sample = (a->flags & NRL_READOUT_SAMPLE) != 0;
+    if (sample && (!a->uniforms || (a->uniforms & 3u) || !a->tokens)) return NRL_E_BAD_ARG;
+    if (a->allow_mask && a->allow_row_stride != 0 && a->allow_row_stride != a->V) return NRL_E_BAD_ARG;
     int dev = 0, cc_major = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
@@ -597,9 +606,13 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (p.group_blocks > p.row_blocks) p.group_blocks = p.row_blocks;
     p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
     p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
-    p.tokens = (const int32_t*)a->tokens;
-    if (!a->workspace || a->workspace_bytes < nrl_readout_workspace_bytes(a->rows, a->V, a->d)) return NRL_E_WORKSPACE;
+    p.tokens = sample ? nullptr : (const int32_t*)a->tokens;
+    if (!a->workspace || a->workspace_bytes < nrl_readout_workspace_bytes(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
     p.parts = (float*)a->workspace;
+    p.allow = (const uint8_t*)a->allow_mask;
+    p.allow_stride = a->allow_row_stride;
+    p.slog = sample ? (float2*)(a->workspace + readout_parts_bytes(a->rows, a->V, a->d)) : nullptr;
+    const bool extra = sample || a->allow_mask != 0;
     p.logits_out = (uint16_t*)a->logits_out;
     CUtensorMap mx, mw;
     int rc = encode_bf16_2d(&mx, a->hidden, a->d, a->rows, kRoBK, kRoBM);
@@ -608,32 +621,31 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     rc = p.w_is_vd ? encode_bf16_2d(&mw, a->weights, a->d, a->V, kRoBK, pairs ? kRoBN / 2 : kRoBN) : encode_bf16_2d(&mw, a->weights, a->V, a->d, 64, kRoBK);
     if (rc) return rc;
     cudaStream_t st = (cudaStream_t)stream;
+#define NRL_RO_LAUNCH(KERNEL, SMEM)                                                                                  \
+    do {                                                                                                            \
+        e = cudaFuncSetAttribute(KERNEL, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(SMEM));                  \
+        if (e != cudaSuccess) return (int)e;                                                                        \
+        KERNEL<<<grid, kRoThreads, (SMEM), st>>>(mx, mw, p);                                                         \
+    } while (0)
     if (pairs) {
         const uint64_t groups = (rb + p.group_blocks - 1) / p.group_blocks;
         const unsigned grid = (unsigned)(groups * p.group_blocks * p.nsplit * 2);  // one cluster of two CTAs per work item
-        if (p.round_bf16) {
-            e = cudaFuncSetAttribute(readout_fwd_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes2);
-            if (e != cudaSuccess) return (int)e;
-            readout_fwd_pair_kernel<true><<<grid, kRoThreads, kRoSmemBytes2, st>>>(mx, mw, p);
-        } else {
-            e = cudaFuncSetAttribute(readout_fwd_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes2);
-            if (e != cudaSuccess) return (int)e;
-            readout_fwd_pair_kernel<false><<<grid, kRoThreads, kRoSmemBytes2, st>>>(mx, mw, p);
-        }
+        if (p.round_bf16) { if (extra) NRL_RO_LAUNCH((readout_fwd_pair_kernel<true, true>), kRoSmemBytes2); else NRL_RO_LAUNCH((readout_fwd_pair_kernel<true, false>), kRoSmemBytes2); }
+        else              { if (extra) NRL_RO_LAUNCH((readout_fwd_pair_kernel<false, true>), kRoSmemBytes2); else NRL_RO_LAUNCH((readout_fwd_pair_kernel<false, false>), kRoSmemBytes2); }
     } else {
         const unsigned grid = (unsigned)(rb * p.nsplit);
-        if (p.round_bf16) {
-            e = cudaFuncSetAttribute(readout_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
-            if (e != cudaSuccess) return (int)e;
-            readout_fwd_kernel<true><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
-        } else {
-            e = cudaFuncSetAttribute(readout_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoSmemBytes);
-            if (e != cudaSuccess) return (int)e;
-            readout_fwd_kernel<false><<<grid, kRoThreads, kRoSmemBytes, st>>>(mx, mw, p);
-        }
+        if (p.round_bf16) { if (extra) NRL_RO_LAUNCH((readout_fwd_kernel<true, true>), kRoSmemBytes); else NRL_RO_LAUNCH((readout_fwd_kernel<true, false>), kRoSmemBytes); }
+        else              { if (extra) NRL_RO_LAUNCH((readout_fwd_kernel<false, true>), kRoSmemBytes); else NRL_RO_LAUNCH((readout_fwd_kernel<false, false>), kRoSmemBytes); }
     }
+#undef NRL_RO_LAUNCH
     rc = after_launch();
     if (rc) return rc;
+    if (sample) {
+        if ((a->rows + 7) / 8 > 0x7fffffffull) return NRL_E_UNSUPPORTED;
+        readout_sample_kernel<<<(unsigned)((a->rows + 7) / 8), 256, 0, st>>>(p, (const float*)a->uniforms, (int32_t*)a->tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats,
+                                                                             (uint8_t*)a->status, (const uint16_t*)a->hidden, (const uint16_t*)a->weights);
+        return after_launch();
+    }
     readout_finish_kernel<<<(unsigned)((a->rows + 127) / 128), 128, 0, st>>>(a->rows, p.nsplit, p.parts, p.tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats, (uint8_t*)a->status);
     return after_launch();
 }

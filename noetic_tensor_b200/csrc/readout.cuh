@@ -58,7 +58,12 @@ struct ReadoutParams {
     const int32_t* tokens; // [rows] or null
     float* parts;          // scratch [rows, nsplit, 4]
     uint16_t* logits_out;  // optional bf16 [rows, V]
+    // the kernels compiled with EXTRA only:
+    const uint8_t* allow;  // optional byte allow-mask [rows, V] or [1, V]
+    uint64_t allow_stride; // V or 0
+    float2* slog;          // optional sampling log [rows, tiles, 4]: per 64 columns (mass at the running maximum, that maximum)
 };
+constexpr int kRoLogCols = 64;  // columns per sampling-log entry
 
 // ---- raw PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory"); }
@@ -146,9 +151,11 @@ __device__ __forceinline__ void readout_tile_range(const ReadoutParams& p, uint3
 // One finished 256-column tile of one row (this thread's lane of tensor memory at `taddr`) folded
 // into the row's running (m, S, W) at maximum m, and the given token's logit picked up if the
 // tile holds it. Columns are taken 32 at a time in index order.
-template <bool ROUND>
+// EXTRA: an allow-mask (excluded columns fold as −FLT_MAX, as in the row kernels) and the sampling log.
+template <bool ROUND, bool EXTRA>
 __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32_t taddr, uint32_t t, uint64_t row, bool live, int32_t tok, float& m, float& S, float& W, float& ztok) {
     float ts = 0.f, tw = 0.f;  // this tile's sums at the running maximum
+    float qs = 0.f;            // EXTRA: the current 64 columns' mass at the running maximum
 #pragma unroll 1
     for (int c = 0; c < kRoBN / 32; c++) {
         uint32_t r[32];
@@ -161,6 +168,20 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
             float v = __uint_as_float(r[i]);
             if (ROUND) v = round_through_bf16(v);
             z[i] = v;
+        }
+        if (EXTRA && p.allow && live && col0 < p.V) {  // 32 mask bytes of this row: one sector
+            const uint8_t* mp = p.allow + row * p.allow_stride + col0;
+            if (col0 + 32 <= p.V && ((reinterpret_cast<uintptr_t>(mp) & 15u) == 0)) {
+                const uint4 q0 = ldg_stream16(mp), q1 = ldg_stream16(mp + 16);
+                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (((w[i >> 2] >> (8 * (i & 3))) & 0xffu) == 0u) z[i] = -FLT_MAX;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (col0 + i < p.V && mp[i] == 0) z[i] = -FLT_MAX;
+            }
         }
         if (col0 + 32 > p.V) {  // past the vocabulary (TMA filled zeros there): exclude
 #pragma unroll
@@ -188,33 +209,41 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
         for (int i = 3; i < 31; i += 2) cm = fmax3_nan(cm, z[i], z[i + 1]);
         cm = fmax_nan(cm, z[31]);
         cm = fmax_nan(cm, -FLT_MAX);  // a −inf logit is folded as −FLT_MAX: exp underflows to 0 either way and 0·inf cannot appear
-        if (!(cm <= m)) {  // a new maximum (or a NaN): move the sums
+        const bool nothing = cm <= -FLT_MAX;  // every column here is excluded (or −inf): no maximum, no mass (a NaN is not "nothing")
+        if (!nothing && !(cm <= m)) {  // a new maximum (or a NaN): move the sums
             if (m != NRL_NEG_INF) {
                 const float dm = m - cm, sc = expf(dm);
                 W = (W + S * dm) * sc;
                 S *= sc;
                 tw = (tw + ts * dm) * sc;
                 ts *= sc;
+                if (EXTRA) qs *= sc;
             }
             m = cm;
         }
         // three levels of sums (32 columns, a tile, the range) keep the rounding of the long f32 sums small
         float cs = 0.f, cw = 0.f;
+        if (!nothing) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) {
-            const float tt = fmaxf(z[i], -FLT_MAX) - m;
-            const float e = ex2_approx(tt * kLog2e);
-            cs += e;
-            cw = fmaf(e, tt, cw);
+            for (int i = 0; i < 32; i++) {
+                const float tt = fmaxf(z[i], -FLT_MAX) - m;
+                const float e = ex2_approx(tt * kLog2e);
+                cs += e;
+                cw = fmaf(e, tt, cw);
+            }
         }
         ts += cs;
         tw += cw;
+        if (EXTRA && p.slog) {
+            qs = (c & 1) ? qs + cs : cs;
+            if ((c & 1) && live) p.slog[(row * p.tiles + t) * (kRoBN / kRoLogCols) + (c >> 1)] = make_float2(qs, m);
+        }
     }
     S += ts;
     W += tw;
 }
 
-template <bool ROUND>
+template <bool ROUND, bool EXTRA>
 __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ReadoutParams p) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_addr(smem_raw) + 1023u) & ~1023u;  // swizzled tiles want 1024-byte alignment
@@ -334,7 +363,7 @@ __global__ void __launch_bounds__(kRoThreads, 1) readout_fwd_kernel(const __grid
             const uint32_t n = t - t0, acc = n & 1u;
             if (!mbar_wait(bar_acc_full + 8 * acc, (n >> 1) & 1u, &abort_flag)) { ok = false; break; }
             tc_fence_after();
-            readout_fold_tile<ROUND>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
+            readout_fold_tile<ROUND, EXTRA>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
             // this accumulator may be overwritten once all four epilogue warps are done with it
             tc_fence_before();
             __syncwarp();
@@ -420,7 +449,7 @@ __device__ __forceinline__ uint32_t cluster_cta_rank() {
 // Work items are (256-row block, column range) pairs laid out in groups as above; the grid holds
 // `gridDim.x / 2 / (group_blocks · nsplit)` groups' worth of clusters and a cluster walks the groups
 // with that stride (one cluster per item when the grid covers every group).
-template <bool ROUND>
+template <bool ROUND, bool EXTRA>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kRoThreads, 1)
     readout_fwd_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w, ReadoutParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -553,7 +582,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kRoThreads, 1)
                 const uint32_t acc = n & 1u;
                 if (!mbar_wait(bar_acc_full + 8 * acc, (n >> 1) & 1u, &abort_flag)) { ok = false; break; }
                 tc_fence_after();
-                readout_fold_tile<ROUND>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
+                readout_fold_tile<ROUND, EXTRA>(p, tmem + ((quarter * 32u) << 16) + acc * kRoBN, t, row, live, tok, m, S, W, ztok);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(in_first_cta(bar_acc_empty + 8 * acc));
@@ -624,6 +653,145 @@ __global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const floa
         }
     }
     if (status) status[row] = (uint8_t)st;
+}
+
+// ---- sampling out of the fused pass -----------------------------------------------------------------
+//
+// token = min{k : Σ_{v≤k} e_v > u·Z}, as in the row forward. The tensor-core pass leaves, per row
+// and per 64 columns, the mass at the maximum the row had reached then. One warp per row: merge
+// the ranges (the row's m and Z), rescale the logged masses to m and find the 64 columns that hold
+// u·Z with warp scans in index order; then compute those 64 logits again — 64 dot products of
+// length d, f32, lanes over columns — apply rounding and mask as the pass did, and walk to the
+// token. Its log-prob is z_token − m − ln Z with that recomputed logit (it differs from the
+// tensor cores' accumulation of the same products by the f32 rounding of a sum of d terms).
+__global__ void __launch_bounds__(256) readout_sample_kernel(ReadoutParams p, const float* uniforms, int32_t* tokens, float* logp, float* entropy, float* rowstats, uint8_t* status,
+                                                            const uint16_t* hidden, const uint16_t* weights) {
+    const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= p.rows) return;
+    const int lane = threadIdx.x & 31;
+    const float4* pr = reinterpret_cast<const float4*>(p.parts) + row * p.nsplit;
+    float m = NRL_NEG_INF;
+    uint32_t st = 0u;
+    for (uint32_t s = 0; s < p.nsplit; s++) {
+        m = fmax_nan(m, pr[s].x);
+        if (pr[s].y < 0.f) st |= 4u;
+    }
+    double Z = 0.0, Wt = 0.0;
+    for (uint32_t s = 0; s < p.nsplit; s++) {
+        const float4 a = pr[s];
+        if (a.x != NRL_NEG_INF && a.y > 0.f) {
+            const double dm = (double)a.x - (double)m, c = (double)expf(a.x - m);
+            Z += c * (double)a.y;
+            Wt += c * ((double)a.z + (double)a.y * dm);
+        }
+    }
+    if (m != m) st |= 2u;
+    else if (m == NRL_NEG_INF || m <= -FLT_MAX) st |= 1u;
+    const double lnZ = log(Z);
+    const float nan = __int_as_float(0x7fc00000);
+    if (st) {
+        if (lane == 0) {
+            tokens[row] = -1;
+            if (logp) logp[row] = nan;
+            if (entropy) entropy[row] = nan;
+            if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(nan, nan, nan, nan);
+            if (status) status[row] = (uint8_t)st;
+        }
+        return;
+    }
+    // the 64 columns that hold the target
+    const double target = (double)uniforms[row] * Z;
+    const uint32_t nlog = p.tiles * (kRoBN / kRoLogCols);
+    const float2* lg = p.slog + row * nlog;
+    double before = 0.0, run = 0.0;
+    int32_t chunk = -1, last_mass = -1;
+    for (uint32_t e0 = 0; e0 < nlog && chunk < 0; e0 += 32) {
+        const uint32_t e = e0 + lane;
+        double x = 0.0;
+        if (e < nlog && (uint64_t)e * kRoLogCols < p.V) {
+            const float2 q = lg[e];
+            if (q.x > 0.f) x = (double)q.x * (double)expf(q.y - m);
+        }
+        const double incl = warp_scan_incl(x, lane);
+        const uint32_t cross = __ballot_sync(0xffffffffu, x > 0.0 && run + incl > target);
+        const uint32_t has = __ballot_sync(0xffffffffu, x > 0.0);
+        if (has) last_mass = (int32_t)e0 + 31 - __clz(has);
+        if (cross) {
+            const int owner = __ffs(cross) - 1;
+            chunk = (int32_t)e0 + owner;
+            before = run + __shfl_sync(0xffffffffu, incl - x, owner);
+        }
+        run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    bool take_last = false;
+    if (chunk < 0) {  // rounding left no crossing: the last columns with mass, their last token with mass
+        chunk = last_mass;
+        take_last = true;
+    }
+    // the logits of columns c0 + 2·lane, c0 + 2·lane + 1 again
+    const uint32_t c0 = (uint32_t)chunk * kRoLogCols, ca = c0 + 2 * lane;
+    float z0 = 0.f, z1 = 0.f;
+    const uint16_t* x = hidden + row * p.d;
+    if (ca < p.V) {
+        if (p.w_is_vd) {
+            const uint16_t *wa = weights + (uint64_t)ca * p.d, *wb = wa + p.d;
+            for (uint32_t k = 0; k < p.d; k += 8) {
+                const uint4 xq = *reinterpret_cast<const uint4*>(x + k), aq = ldg_stream16(wa + k), bq = ldg_stream16(wb + k);
+                const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w}, aw[4] = {aq.x, aq.y, aq.z, aq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    z0 = fmaf(bf16_lo(xw[i]), bf16_lo(aw[i]), z0);
+                    z0 = fmaf(bf16_hi(xw[i]), bf16_hi(aw[i]), z0);
+                    z1 = fmaf(bf16_lo(xw[i]), bf16_lo(bw[i]), z1);
+                    z1 = fmaf(bf16_hi(xw[i]), bf16_hi(bw[i]), z1);
+                }
+            }
+        } else {
+            const uint16_t* wp = weights + ca;
+#pragma unroll 8
+            for (uint32_t k = 0; k < p.d; k++) {
+                const float xv = __uint_as_float((uint32_t)x[k] << 16);
+                const uint32_t ww = __ldg(reinterpret_cast<const uint32_t*>(wp + (uint64_t)k * p.V));
+                z0 = fmaf(xv, bf16_lo(ww), z0);
+                z1 = fmaf(xv, bf16_hi(ww), z1);
+            }
+        }
+    }
+    if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
+    bool ok0 = ca < p.V, ok1 = ca + 1 < p.V;
+    if (p.allow) {
+        const uint8_t* mp = p.allow + row * p.allow_stride;
+        ok0 = ok0 && mp[ca] != 0;
+        ok1 = ok1 && mp[ca + 1] != 0;
+    }
+    const float e0v = ok0 ? ex2_approx((fmaxf(z0, -FLT_MAX) - m) * kLog2e) : 0.f, e1v = ok1 ? ex2_approx((fmaxf(z1, -FLT_MAX) - m) * kLog2e) : 0.f;
+    const double pair = (double)e0v + (double)e1v;
+    const double incl = warp_scan_incl(pair, lane);
+    const double resid = take_last ? 1e300 : target - before;
+    const uint32_t cross = __ballot_sync(0xffffffffu, pair > 0.0 && incl > resid);
+    const uint32_t has = __ballot_sync(0xffffffffu, pair > 0.0);
+    int32_t token = -1;
+    float ztok = nan;
+    if (has) {
+        const int owner = cross ? __ffs(cross) - 1 : 31 - __clz(has);
+        int32_t tk = -1;
+        float zt = nan;
+        if (lane == owner) {
+            const double b0 = incl - pair;
+            if (cross ? (e0v > 0.f && b0 + (double)e0v > resid) : !(e1v > 0.f)) { tk = (int32_t)ca; zt = z0; }
+            else if (e1v > 0.f) { tk = (int32_t)ca + 1; zt = z1; }
+            else { tk = (int32_t)ca; zt = z0; }
+        }
+        token = __shfl_sync(0xffffffffu, tk, owner);
+        ztok = __shfl_sync(0xffffffffu, zt, owner);
+    }
+    if (lane == 0) {
+        tokens[row] = token;
+        if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(m, (float)lnZ, 0.f, 0.f);
+        if (entropy) entropy[row] = (float)(lnZ - Wt / Z);
+        if (logp) logp[row] = token < 0 ? nan : (ztok - m) - (float)lnZ;
+        if (status) status[row] = 0;
+    }
 }
 
 }  // namespace nrl

@@ -559,7 +559,7 @@ inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, c
     cu(cudaMemcpy(tok.ptr(), h.data(), h.size() * 4, cudaMemcpyHostToDevice), "upload tokens");
     Tensor logp = Tensor::empty(lead, DType::F32, hidden.device());
     Tensor status = Tensor::empty(Shape{(size_t)rows}, DType::U8, hidden.device());
-    const uint64_t need = nrl_readout_workspace_bytes(rows, (uint32_t)V, (uint32_t)d);
+    const uint64_t need = nrl_readout_workspace_bytes(rows, (uint32_t)V, (uint32_t)d, 0u);
     Tensor ws = Tensor::empty(Shape{(size_t)need}, DType::U8, hidden.device());
     nrl_readout_args a;
     std::memset(&a, 0, sizeof a);

@@ -418,14 +418,16 @@ def reduce_tokens_backward_pairs(reduction, S, B, T, seq_begin, n_seq, pairs, ma
 class Readout:
     """Outputs of nrl_readout_fwd (fields are None when not requested)."""
 
-    __slots__ = ("logp", "entropy", "rowstats", "status", "logits")
+    __slots__ = ("logp", "entropy", "rowstats", "status", "logits", "tokens")
 
 
-def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False):
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None):
     """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
     `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
     `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
-    the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]."""
+    the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]. With
+    `uniforms` (float32 [rows]) the tokens are drawn by inverse CDF instead of given (`tokens` of the
+    result); `allow` is a uint8 allow-mask [rows, V] or [1, V]."""
     dev = hidden.device
     if dev.type != "cuda":
         raise ValueError("readout_forward needs CUDA tensors: this library has no CPU path")
@@ -435,22 +437,32 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     _need(weights, torch.bfloat16, (V, d) if weights_are_vd else (d, V), "weights", dev)
     a = capi.ReadoutArgs()
     a.struct_size = C.sizeof(a)
-    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0)
+    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0) | (capi.READOUT_SAMPLE if uniforms is not None else 0)
     a.V, a.d, a.rows = V, d, rows
     a.hidden, a.weights = _p(hidden), _p(weights)
     out = Readout()
-    out.logp = None
-    if tokens is not None:
+    out.logp = out.tokens = None
+    if uniforms is not None:
+        if tokens is not None:
+            raise ValueError("give `tokens` or `uniforms`, not both")
+        _need(uniforms, torch.float32, (rows,), "uniforms", dev)
+        a.uniforms = _p(uniforms)
+        tokens = out.tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    elif tokens is not None:
         _need(tokens, torch.int32, (rows,), "tokens", dev)
+    if tokens is not None:
         a.tokens = _p(tokens)
         out.logp = torch.empty(rows, dtype=torch.float32, device=dev)
+    if allow is not None:
+        allow, a.allow_row_stride, _, _ = _masks(V, rows, allow, None, dev)
+        a.allow_mask = _p(allow)
     out.entropy = torch.empty(rows, dtype=torch.float32, device=dev)
     out.rowstats = torch.empty(rows, 4, dtype=torch.float32, device=dev)
     out.status = torch.empty(rows, dtype=torch.uint8, device=dev)
     out.logits = torch.empty(rows, V, dtype=torch.bfloat16, device=dev) if want_logits else None
     a.logp, a.entropy, a.rowstats, a.status, a.logits_out = _p(out.logp), _p(out.entropy), _p(out.rowstats), _p(out.status), _p(out.logits)
     if workspace is None:
-        workspace = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d), dtype=torch.uint8, device=dev)
+        workspace = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d, a.flags), dtype=torch.uint8, device=dev)
     a.workspace, a.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
     with torch.cuda.device(dev):
         capi.check(capi.lib().nrl_readout_fwd(C.byref(a), _stream(dev)), "nrl_readout_fwd")

@@ -127,3 +127,111 @@ def test_readout_cta_pairs_give_the_single_cta_bits(rows, d, V, layout):
         assert torch.equal(a.logits.view(torch.int16), b.logits.view(torch.int16))
         for name in ("logp", "entropy", "rowstats"):
             assert torch.equal(getattr(a, name).view(torch.int32), getattr(b, name).view(torch.int32)), (name, rnd)
+
+
+@pytest.mark.parametrize("rows,d,V,keep", [(128, 64, 256, None), (100, 72, 776, 0.5), (1000, 512, 4104, 0.1), (300, 4096, 128256, None), (260, 4096, 128256, 0.02), (2500, 1024, 16384, 0.7)])
+@pytest.mark.parametrize("layout", ["dV", "Vd"])
+def test_readout_sampling_and_masks(oracle, rows, d, V, keep, layout):
+    """NRL_READOUT_SAMPLE with and without a byte allow-mask: the tokens against the f64 oracle's
+    inverse CDF on the very logits the kernel folded (equal off the CDF boundary rows; the picked
+    logit is computed a second time in f32, so a row whose uniform lies within the oracle's
+    boundary band may fall either way), never an excluded token, log-prob / entropy within the
+    path's tolerance, and nrl_row_fwd's sampler on the same logits, mask and uniforms agreeing."""
+    from noetic_tensor_b200 import ops
+
+    x, w, _ = make(rows, d, V, 13 * rows + V)
+    wa = w.t().contiguous() if layout == "Vd" else w
+    g = torch.Generator(device=dev())
+    g.manual_seed(rows)
+    u = torch.rand(rows, generator=g, device=dev())
+    allow = None
+    if keep is not None:
+        allow = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
+        allow[:, V // 3] = 1
+    o = ops.readout_forward(x, wa, uniforms=u, allow=allow, weights_are_vd=(layout == "Vd"), round_bf16=True, want_logits=True)
+    assert (o.status == 0).all()
+    tok = o.tokens.long()
+    assert ((tok >= 0) & (tok < V)).all()
+    if allow is not None:
+        assert allow[torch.arange(rows, device=dev()), tok].all(), "an excluded token was drawn"
+    # the row kernel's sampler on the same logits
+    f = ops.row_forward(o.logits, allow=allow, uniforms=u)
+    differ = (f.tokens != o.tokens)
+    # the oracle on a sample of rows (and on every row where the two samplers differ)
+    idx = np.unique(np.concatenate([np.random.default_rng(rows).choice(rows, min(rows, 24), replace=False), differ.nonzero().flatten().cpu().numpy()[:40]]))
+    bits = o.logits[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    orc = oracle.sample_inverse_cdf(bits, 1.0, u[idx].cpu().numpy(), allow=None if allow is None else allow[idx].cpu().numpy())
+    got = o.tokens[idx].cpu().numpy().astype(np.int64)
+    bad = (got != orc["tokens"]) & (orc["boundary"] == 0)
+    assert not bad.any(), f"{bad.sum()} sampled tokens differ from the oracle off the CDF boundaries"
+    same = got == orc["tokens"]
+    lp_err = np.abs(o.logp[idx].cpu().numpy()[same] - orc["logp"][same])
+    assert ((lp_err <= 1e-6) | (lp_err <= 1e-5 * np.abs(orc["logp"][same])) | (lp_err <= 2.0 ** -7 * 32)).all() and np.count_nonzero(lp_err > 1e-4) <= 2, "logp of drawn tokens vs oracle"
+    close(o.entropy[idx].cpu().numpy(), orc["entropy"], "entropy vs oracle")
+    agree = ~differ
+    # The drawn token's logit is computed a second time (f32 on the CUDA cores); rounded to bf16 it can
+    # land on the neighbour of the value the tensor cores' accumulation rounded to: at most a few rows,
+    # and never by more than one bf16 step of that logit.
+    lp_a, lp_b = o.logp[agree].double(), f.logp[agree].double()
+    zt = o.logits[torch.arange(rows, device=dev()), tok][agree].double().abs()
+    off = ((lp_a - lp_b).abs() > 1e-6) & ((lp_a - lp_b).abs() > 1e-5 * lp_b.abs())
+    assert int(off.sum()) <= max(2, rows // 100) and ((lp_a - lp_b).abs()[off] <= 2.0 ** -7 * zt[off] + 1e-6).all(), "logp vs nrl_row_fwd"
+    close(o.entropy.cpu().numpy(), f.entropy.cpu().numpy(), "entropy vs nrl_row_fwd")
+    assert int(differ.sum()) <= max(2, rows // 100), f"{int(differ.sum())} of {rows} tokens differ from nrl_row_fwd's sampler"
+    # run to run
+    again = ops.readout_forward(x, wa, uniforms=u, allow=allow, weights_are_vd=(layout == "Vd"), round_bf16=True)
+    assert torch.equal(again.tokens, o.tokens) and torch.equal(again.logp.view(torch.int32), o.logp.view(torch.int32))
+
+
+@pytest.mark.parametrize("rows,d,V", [(300, 4096, 128256), (1000, 512, 4104)])
+def test_readout_sampling_of_the_f32_accumulators(rows, d, V):
+    """Without rounding: the drawn tokens' log-probs against the f64 log-softmax of the f64 product at
+    those tokens (5e-5 relative: the spread of an f32-accumulated product), and the draw itself
+    against the f64 CDF: the token's cumulative interval must contain u·Z up to that spread."""
+    from noetic_tensor_b200 import ops
+
+    x, w, _ = make(rows, d, V, 17 * rows + V)
+    g = torch.Generator(device=dev())
+    g.manual_seed(rows)
+    u = torch.rand(rows, generator=g, device=dev())
+    o = ops.readout_forward(x, w, uniforms=u)
+    n = min(rows, 128)
+    ref = x[:n].double() @ w.double()
+    lp = torch.log_softmax(ref, 1)
+    tok = o.tokens[:n].long()
+    # ln Z comes from the tensor cores' accumulation of 4096-term products, the token's logit from an f32
+    # FMA chain: the two differ from the exact product by up to ~1e-4 in a logit of magnitude ~10
+    close(o.logp[:n].cpu().numpy(), lp[torch.arange(n, device=dev()), tok].cpu().numpy(), "logp of drawn tokens", rel=5e-5, abs_=1e-4)
+    cdf = torch.cumsum(lp.exp(), 1)
+    hi = cdf[torch.arange(n, device=dev()), tok]
+    lo = hi - lp.exp()[torch.arange(n, device=dev()), tok]
+    uu = u[:n].double()
+    assert ((uu >= lo - 1e-4) & (uu <= hi + 1e-4)).all(), "a drawn token's CDF interval does not hold its uniform"
+
+
+def test_readout_sampling_distribution_and_refusals():
+    """Frequencies over many draws of one small distribution (src/nn/tests/rl.rs:582-629: within 4.5
+    standard errors), a row with no allowed token (status 1, token −1) and masks given as [1, V]."""
+    from noetic_tensor_b200 import ops
+
+    d, V, draws = 64, 64, 40000
+    g = torch.Generator(device=dev())
+    g.manual_seed(5)
+    h = torch.randn(1, d, generator=g, device=dev()).bfloat16()
+    w = (torch.randn(d, V, generator=g, device=dev()) * 0.3).bfloat16()
+    x = h.expand(draws, d).contiguous()
+    allow = torch.ones(1, V, dtype=torch.uint8, device=dev())
+    allow[0, ::5] = 0
+    u = torch.rand(draws, generator=g, device=dev())
+    o = ops.readout_forward(x, w, uniforms=u, allow=allow)
+    z = (h.double() @ w.double())[0]
+    z[allow[0] == 0] = float("-inf")
+    p = torch.softmax(z, 0).cpu().numpy()
+    fr = np.bincount(o.tokens.cpu().numpy(), minlength=V) / draws
+    assert (fr[::5] == 0).all()
+    assert np.all(np.abs(fr - p) <= 4.5 * np.sqrt(p * (1 - p) / draws) + 1e-12)
+    rows_mask = torch.ones(200, V, dtype=torch.uint8, device=dev())
+    rows_mask[17] = 0
+    o = ops.readout_forward(x[:200].contiguous(), w, uniforms=u[:200].contiguous(), allow=rows_mask)
+    st = o.status.cpu().numpy()
+    assert st[17] == 1 and o.tokens[17] == -1 and (np.delete(st, 17) == 0).all()
