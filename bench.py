@@ -438,6 +438,17 @@ def run_extras(dev, peak):
         return ops.row_forward(lg, tokens=tk)
 
     t_two = _time(two_step)
+    # the headline's own operation fused with the product: masked sampling + log-prob + entropy
+    am = synth.grammar_masks(rows, V, gen, dev)
+    un = synth.uniforms(rows, gen, dev)
+    ws2 = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d6, capi.READOUT_SAMPLE), dtype=torch.uint8, device=dev)
+    t_sample = _time(lambda: ops.readout_forward(hx, wt, uniforms=un, allow=am, workspace=ws2))
+
+    def two_step_sample():
+        torch.matmul(hx, wt, out=lg)
+        return ops.row_forward(lg, allow=am, uniforms=un)
+
+    t_two_sample = _time(two_step_sample)
     fl = 2.0 * rows * d6 * V
     fo, f2 = ops.readout_forward(hx, wt, tokens=tk, workspace=ws, round_bf16=True, want_logits=True), None
     f2 = ops.row_forward(fo.logits, tokens=tk)
@@ -446,7 +457,10 @@ def run_extras(dev, peak):
                             "rows": rows, "d": d6, "V": V, "ms": t_fused, "ms_round_bf16": t_round, "TFLOPs": fl / t_fused / 1e9, "frac_of_sustained_bf16_peak": fl / t_fused / 1e9 / tf_sustained,
                             "frac_of_burst_bf16_peak": fl / t_fused / 1e9 / tf_burst, "peak_kind": tf_kind, "cublas_product_alone_ms": t_mm, "cublas_TFLOPs": fl / t_mm / 1e9,
                             "two_step_ms": t_two, "speedup_vs_two_step": t_two / t_fused, "rows_per_s": rows / (t_fused * 1e-3),
-                            "values_outside_tolerance_vs_row_fwd_on_its_logits": close(fo.logp, f2.logp) + close(fo.entropy, f2.entropy)}
+                            "values_outside_tolerance_vs_row_fwd_on_its_logits": close(fo.logp, f2.logp) + close(fo.entropy, f2.entropy),
+                            "masked_sampling": {"what": "the same product with U8 grammar masks and inverse-CDF sampling fused (NRL_READOUT_SAMPLE): tokens + log-probs + entropy; two_step = cuBLAS + nrl_row_fwd "
+                                                        "(masked sampling) on the bf16 logits it wrote", "ms": t_sample, "TFLOPs": fl / t_sample / 1e9, "two_step_ms": t_two_sample,
+                                                "speedup_vs_two_step": t_two_sample / t_sample, "rows_per_s": rows / (t_sample * 1e-3)}}
     return res
 
 

@@ -541,7 +541,13 @@ static uint64_t readout_parts_bytes(uint64_t rows, uint32_t V, uint32_t d) {
 extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags) {
     if (rows == 0 || V == 0 || d == 0) return 0;
     uint64_t n = readout_parts_bytes(rows, V, d);
-    if (flags & NRL_READOUT_SAMPLE) n += rows * (uint64_t)((V + kRoBN - 1) / kRoBN) * (kRoBN / kRoLogCols) * sizeof(float2);
+    if (flags & NRL_READOUT_SAMPLE) {
+        const uint64_t nslabs = (uint64_t)((V + kRoBN - 1) / kRoBN) * (kRoBN / kRoLogCols);
+        n += (rows * nslabs * sizeof(float2) + 255) & ~255ull;      // the mass log
+        n += (rows * sizeof(ReadoutPick) + 255) & ~255ull;          // each row's slab and residual
+        n += ((nslabs + 1) * sizeof(uint32_t) + 255) & ~255ull;     // rows grouped by slab: starts
+        n += (rows * sizeof(uint32_t) + 255) & ~255ull;             //                       and order
+    }
     return n;
 }
 
@@ -641,9 +647,23 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     rc = after_launch();
     if (rc) return rc;
     if (sample) {
-        if ((a->rows + 7) / 8 > 0x7fffffffull) return NRL_E_UNSUPPORTED;
-        readout_sample_kernel<<<(unsigned)((a->rows + 7) / 8), 256, 0, st>>>(p, (const float*)a->uniforms, (int32_t*)a->tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats,
-                                                                             (uint8_t*)a->status, (const uint16_t*)a->hidden, (const uint16_t*)a->weights);
+        const uint64_t nslabs = (uint64_t)p.tiles * (kRoBN / kRoLogCols);
+        uint64_t off = readout_parts_bytes(a->rows, a->V, a->d) + ((a->rows * nslabs * sizeof(float2) + 255) & ~255ull);
+        ReadoutPick* picks = (ReadoutPick*)(a->workspace + off);
+        off += (a->rows * sizeof(ReadoutPick) + 255) & ~255ull;
+        uint32_t* bucket_start = (uint32_t*)(a->workspace + off);
+        off += ((nslabs + 1) * sizeof(uint32_t) + 255) & ~255ull;
+        uint32_t* order = (uint32_t*)(a->workspace + off);
+        if ((a->rows + 7) / 8 > 0x7fffffffull || a->rows > 0xffffffffull) return NRL_E_UNSUPPORTED;
+        if (nslabs > (uint64_t)kRoMaxSlabs) return NRL_E_UNSUPPORTED;  // V beyond 524 288 with sampling
+        readout_pick_kernel<<<(unsigned)((a->rows + 7) / 8), 256, 0, st>>>(p, (const float*)a->uniforms, picks, (int32_t*)a->tokens, (float*)a->logp, (float*)a->entropy,
+                                                                           (float*)a->rowstats, (uint8_t*)a->status);
+        rc = after_launch();
+        if (rc) return rc;
+        readout_bucket_kernel<<<1, 1024, 0, st>>>(a->rows, (uint32_t)nslabs, picks, bucket_start, order);
+        rc = after_launch();
+        if (rc) return rc;
+        readout_draw_kernel<<<dim3(kRoDrawParts, (unsigned)nslabs), 256, 0, st>>>(p, picks, bucket_start, order, (int32_t*)a->tokens, (float*)a->logp, (const uint16_t*)a->hidden, (const uint16_t*)a->weights);
         return after_launch();
     }
     readout_finish_kernel<<<(unsigned)((a->rows + 127) / 128), 128, 0, st>>>(a->rows, p.nsplit, p.parts, p.tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats, (uint8_t*)a->status);

@@ -156,6 +156,17 @@ template <bool ROUND, bool EXTRA>
 __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32_t taddr, uint32_t t, uint64_t row, bool live, int32_t tok, float& m, float& S, float& W, float& ztok) {
     float ts = 0.f, tw = 0.f;  // this tile's sums at the running maximum
     float qs = 0.f;            // EXTRA: the current 64 columns' mass at the running maximum
+    // EXTRA: the mask bytes of a whole tile inside the vocabulary, 16-byte aligned, are fetched one chunk ahead
+    uint4 mq[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+    bool mask_fast = false;
+    if (EXTRA && p.allow && live) {
+        const uint8_t* mp0 = p.allow + row * p.allow_stride + (uint64_t)t * kRoBN;
+        mask_fast = (uint64_t)(t + 1) * kRoBN <= p.V && (reinterpret_cast<uintptr_t>(mp0) & 15u) == 0;
+        if (mask_fast) {
+            mq[0] = ldg_stream16(mp0);
+            mq[1] = ldg_stream16(mp0 + 16);
+        }
+    }
 #pragma unroll 1
     for (int c = 0; c < kRoBN / 32; c++) {
         uint32_t r[32];
@@ -171,9 +182,13 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
         }
         if (EXTRA && p.allow && live && col0 < p.V) {  // 32 mask bytes of this row: one sector
             const uint8_t* mp = p.allow + row * p.allow_stride + col0;
-            if (col0 + 32 <= p.V && ((reinterpret_cast<uintptr_t>(mp) & 15u) == 0)) {
-                const uint4 q0 = ldg_stream16(mp), q1 = ldg_stream16(mp + 16);
-                const uint32_t w[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            if (mask_fast) {
+                // this chunk's bytes were loaded one chunk ahead; the next chunk's go out now
+                const uint32_t w[8] = {mq[0].x, mq[0].y, mq[0].z, mq[0].w, mq[1].x, mq[1].y, mq[1].z, mq[1].w};
+                if (c + 1 < kRoBN / 32) {
+                    mq[0] = ldg_stream16(mp + 32);
+                    mq[1] = ldg_stream16(mp + 48);
+                }
 #pragma unroll
                 for (int i = 0; i < 32; i++)
                     if (((w[i >> 2] >> (8 * (i & 3))) & 0xffu) == 0u) z[i] = -FLT_MAX;
@@ -658,14 +673,28 @@ __global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const floa
 // ---- sampling out of the fused pass -----------------------------------------------------------------
 //
 // token = min{k : Σ_{v≤k} e_v > u·Z}, as in the row forward. The tensor-core pass leaves, per row
-// and per 64 columns, the mass at the maximum the row had reached then. One warp per row: merge
-// the ranges (the row's m and Z), rescale the logged masses to m and find the 64 columns that hold
-// u·Z with warp scans in index order; then compute those 64 logits again — 64 dot products of
-// length d, f32, lanes over columns — apply rounding and mask as the pass did, and walk to the
-// token. Its log-prob is z_token − m − ln Z with that recomputed logit (it differs from the
-// tensor cores' accumulation of the same products by the f32 rounding of a sum of d terms).
-__global__ void __launch_bounds__(256) readout_sample_kernel(ReadoutParams p, const float* uniforms, int32_t* tokens, float* logp, float* entropy, float* rowstats, uint8_t* status,
-                                                            const uint16_t* hidden, const uint16_t* weights) {
+// and per 64 columns, the mass at the maximum the row had reached then. Three small kernels follow:
+//   readout_pick_kernel    one warp per row: merge the ranges (the row's m, Z, entropy), rescale the
+//                          logged masses to m and find the 64 columns that hold u·Z with warp scans
+//                          in index order;
+//   readout_bucket_kernel  one block: rows grouped by the 64-column slab they picked (a counting
+//                          sort; the order inside a group does not enter any result), so that
+//   readout_draw_kernel    one block per slab computes the slab's 64 logits again for every row
+//                          that picked it — 64 dot products of length d in f32, lanes over columns —
+//                          with the slab of W (64 · d · 2 bytes) coming from HBM once instead of once
+//                          per row, applies rounding and mask as the pass did, and walks to the
+//                          token. Its log-prob is z_token − m − ln Z with that recomputed logit (it
+//                          differs from the tensor cores' accumulation of the same products by the
+//                          f32 rounding of a sum of d terms).
+struct ReadoutPick {
+    double resid;    // u·Z minus the mass before the slab; 1e300: take the slab's last token with mass
+    float m, lnZ;
+    int32_t slab;    // index of the 64-column slab, −1 for a refused row
+    uint32_t pad;
+};
+
+__global__ void __launch_bounds__(256) readout_pick_kernel(ReadoutParams p, const float* uniforms, ReadoutPick* picks, int32_t* tokens, float* logp, float* entropy, float* rowstats,
+                                                          uint8_t* status) {
     const uint64_t row = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= p.rows) return;
     const int lane = threadIdx.x & 31;
@@ -689,6 +718,8 @@ __global__ void __launch_bounds__(256) readout_sample_kernel(ReadoutParams p, co
     else if (m == NRL_NEG_INF || m <= -FLT_MAX) st |= 1u;
     const double lnZ = log(Z);
     const float nan = __int_as_float(0x7fc00000);
+    ReadoutPick pk;
+    pk.resid = 0.0; pk.m = m; pk.lnZ = (float)lnZ; pk.slab = -1; pk.pad = 0u;
     if (st) {
         if (lane == 0) {
             tokens[row] = -1;
@@ -696,16 +727,16 @@ __global__ void __launch_bounds__(256) readout_sample_kernel(ReadoutParams p, co
             if (entropy) entropy[row] = nan;
             if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(nan, nan, nan, nan);
             if (status) status[row] = (uint8_t)st;
+            picks[row] = pk;
         }
         return;
     }
-    // the 64 columns that hold the target
     const double target = (double)uniforms[row] * Z;
     const uint32_t nlog = p.tiles * (kRoBN / kRoLogCols);
     const float2* lg = p.slog + row * nlog;
     double before = 0.0, run = 0.0;
-    int32_t chunk = -1, last_mass = -1;
-    for (uint32_t e0 = 0; e0 < nlog && chunk < 0; e0 += 32) {
+    int32_t slab = -1, last_mass = -1;
+    for (uint32_t e0 = 0; e0 < nlog && slab < 0; e0 += 32) {
         const uint32_t e = e0 + lane;
         double x = 0.0;
         if (e < nlog && (uint64_t)e * kRoLogCols < p.V) {
@@ -718,79 +749,171 @@ __global__ void __launch_bounds__(256) readout_sample_kernel(ReadoutParams p, co
         if (has) last_mass = (int32_t)e0 + 31 - __clz(has);
         if (cross) {
             const int owner = __ffs(cross) - 1;
-            chunk = (int32_t)e0 + owner;
+            slab = (int32_t)e0 + owner;
             before = run + __shfl_sync(0xffffffffu, incl - x, owner);
         }
         run += __shfl_sync(0xffffffffu, incl, 31);
     }
-    bool take_last = false;
-    if (chunk < 0) {  // rounding left no crossing: the last columns with mass, their last token with mass
-        chunk = last_mass;
-        take_last = true;
+    pk.resid = target - before;
+    if (slab < 0) {  // rounding left no crossing: the last slab with mass, its last token with mass
+        slab = last_mass;
+        pk.resid = 1e300;
     }
-    // the logits of columns c0 + 2·lane, c0 + 2·lane + 1 again
-    const uint32_t c0 = (uint32_t)chunk * kRoLogCols, ca = c0 + 2 * lane;
-    float z0 = 0.f, z1 = 0.f;
-    const uint16_t* x = hidden + row * p.d;
-    if (ca < p.V) {
-        if (p.w_is_vd) {
-            const uint16_t *wa = weights + (uint64_t)ca * p.d, *wb = wa + p.d;
-            for (uint32_t k = 0; k < p.d; k += 8) {
-                const uint4 xq = *reinterpret_cast<const uint4*>(x + k), aq = ldg_stream16(wa + k), bq = ldg_stream16(wb + k);
-                const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w}, aw[4] = {aq.x, aq.y, aq.z, aq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    z0 = fmaf(bf16_lo(xw[i]), bf16_lo(aw[i]), z0);
-                    z0 = fmaf(bf16_hi(xw[i]), bf16_hi(aw[i]), z0);
-                    z1 = fmaf(bf16_lo(xw[i]), bf16_lo(bw[i]), z1);
-                    z1 = fmaf(bf16_hi(xw[i]), bf16_hi(bw[i]), z1);
-                }
-            }
-        } else {
-            const uint16_t* wp = weights + ca;
-#pragma unroll 8
-            for (uint32_t k = 0; k < p.d; k++) {
-                const float xv = __uint_as_float((uint32_t)x[k] << 16);
-                const uint32_t ww = __ldg(reinterpret_cast<const uint32_t*>(wp + (uint64_t)k * p.V));
-                z0 = fmaf(xv, bf16_lo(ww), z0);
-                z1 = fmaf(xv, bf16_hi(ww), z1);
-            }
-        }
-    }
-    if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
-    bool ok0 = ca < p.V, ok1 = ca + 1 < p.V;
-    if (p.allow) {
-        const uint8_t* mp = p.allow + row * p.allow_stride;
-        ok0 = ok0 && mp[ca] != 0;
-        ok1 = ok1 && mp[ca + 1] != 0;
-    }
-    const float e0v = ok0 ? ex2_approx((fmaxf(z0, -FLT_MAX) - m) * kLog2e) : 0.f, e1v = ok1 ? ex2_approx((fmaxf(z1, -FLT_MAX) - m) * kLog2e) : 0.f;
-    const double pair = (double)e0v + (double)e1v;
-    const double incl = warp_scan_incl(pair, lane);
-    const double resid = take_last ? 1e300 : target - before;
-    const uint32_t cross = __ballot_sync(0xffffffffu, pair > 0.0 && incl > resid);
-    const uint32_t has = __ballot_sync(0xffffffffu, pair > 0.0);
-    int32_t token = -1;
-    float ztok = nan;
-    if (has) {
-        const int owner = cross ? __ffs(cross) - 1 : 31 - __clz(has);
-        int32_t tk = -1;
-        float zt = nan;
-        if (lane == owner) {
-            const double b0 = incl - pair;
-            if (cross ? (e0v > 0.f && b0 + (double)e0v > resid) : !(e1v > 0.f)) { tk = (int32_t)ca; zt = z0; }
-            else if (e1v > 0.f) { tk = (int32_t)ca + 1; zt = z1; }
-            else { tk = (int32_t)ca; zt = z0; }
-        }
-        token = __shfl_sync(0xffffffffu, tk, owner);
-        ztok = __shfl_sync(0xffffffffu, zt, owner);
-    }
+    pk.slab = slab;
     if (lane == 0) {
-        tokens[row] = token;
+        picks[row] = pk;
         if (rowstats) reinterpret_cast<float4*>(rowstats)[row] = make_float4(m, (float)lnZ, 0.f, 0.f);
         if (entropy) entropy[row] = (float)(lnZ - Wt / Z);
-        if (logp) logp[row] = token < 0 ? nan : (ztok - m) - (float)lnZ;
         if (status) status[row] = 0;
+    }
+}
+
+// Rows grouped by slab: order[bucket_start[s] .. bucket_start[s + 1]) are the rows that picked slab s.
+constexpr int kRoMaxSlabs = 8192;  // slabs a single block can count in shared memory (V ≤ 524 288)
+__global__ void __launch_bounds__(1024) readout_bucket_kernel(uint64_t rows, uint32_t nslabs, const ReadoutPick* picks, uint32_t* bucket_start, uint32_t* order) {
+    __shared__ uint32_t cnt[kRoMaxSlabs];
+    __shared__ uint32_t carry;
+    for (uint32_t i = threadIdx.x; i < nslabs; i += blockDim.x) cnt[i] = 0u;
+    __syncthreads();
+    for (uint64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+        const int32_t s = picks[r].slab;
+        if (s >= 0) atomicAdd(&cnt[s], 1u);  // a count of work items: no result depends on the order of these additions
+    }
+    __syncthreads();
+    // exclusive scan of the counts, 1024 slabs at a time
+    if (threadIdx.x == 0) carry = 0u;
+    __syncthreads();
+    for (uint32_t base = 0; base < nslabs; base += blockDim.x) {
+        const uint32_t i = base + threadIdx.x;
+        const uint32_t c = i < nslabs ? cnt[i] : 0u;
+        // block-wide inclusive scan through shared memory (Hillis-Steele on the warp, then the warps' totals)
+        uint32_t x = c;
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+        for (int k = 1; k < 32; k <<= 1) {
+            const uint32_t y = __shfl_up_sync(0xffffffffu, x, k);
+            if (lane >= k) x += y;
+        }
+        __shared__ uint32_t wsum[32];
+        if (lane == 31) wsum[warp] = x;
+        __syncthreads();
+        if (warp == 0) {
+            uint32_t w = wsum[lane];
+#pragma unroll
+            for (int k = 1; k < 32; k <<= 1) {
+                const uint32_t y = __shfl_up_sync(0xffffffffu, w, k);
+                if (lane >= k) w += y;
+            }
+            wsum[lane] = w;
+        }
+        __syncthreads();
+        const uint32_t incl = x + (warp ? wsum[warp - 1] : 0u) + carry;
+        if (i < nslabs) {
+            bucket_start[i] = incl - c;
+            cnt[i] = incl - c;  // becomes the slab's fill cursor
+        }
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry = incl;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) bucket_start[nslabs] = carry;
+    __syncthreads();
+    for (uint64_t r = threadIdx.x; r < rows; r += blockDim.x) {
+        const int32_t s = picks[r].slab;
+        if (s >= 0) order[atomicAdd(&cnt[s], 1u)] = (uint32_t)r;
+    }
+}
+
+// grid (kRoDrawParts, slabs) — the parts of a slab next to each other in launch order, so that they run
+// together and share the slab of W through L2: block (y, s) takes the rows y, y + kRoDrawParts, … of slab s's group;
+// its eight warps split the d terms of a row's 64 dot products (each warp a contiguous eighth,
+// loads 16 deep), the partial sums meet in shared memory and are added in warp order.
+constexpr int kRoDrawParts = 4;
+__global__ void __launch_bounds__(256) readout_draw_kernel(ReadoutParams p, const ReadoutPick* picks, const uint32_t* bucket_start, const uint32_t* order, int32_t* tokens, float* logp,
+                                                          const uint16_t* hidden, const uint16_t* weights) {
+    __shared__ float part[8][kRoLogCols];
+    const uint32_t slab = blockIdx.y;
+    const uint32_t r0 = bucket_start[slab], r1 = bucket_start[slab + 1];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const float nan = __int_as_float(0x7fc00000);
+    const uint32_t c0 = slab * kRoLogCols, ca = c0 + 2 * lane;  // this lane's two columns
+    const uint32_t kper = ((p.d + 63) / 64) * 8;                // terms per warp, a multiple of 8
+    const uint32_t k0 = min((uint32_t)warp * kper, p.d), k1 = min(k0 + kper, p.d);
+    for (uint32_t j = r0 + blockIdx.x; j < r1; j += kRoDrawParts) {
+        const uint64_t row = order[j];
+        float z0 = 0.f, z1 = 0.f;
+        const uint16_t* x = hidden + row * p.d;
+        if (ca < p.V) {
+            if (p.w_is_vd) {
+                const uint16_t *wa = weights + (uint64_t)ca * p.d, *wb = wa + p.d;
+#pragma unroll 2
+                for (uint32_t k = k0; k < k1; k += 8) {
+                    const uint4 xq = *reinterpret_cast<const uint4*>(x + k), aq = *reinterpret_cast<const uint4*>(wa + k), bq = *reinterpret_cast<const uint4*>(wb + k);
+                    const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w}, aw[4] = {aq.x, aq.y, aq.z, aq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        z0 = fmaf(bf16_lo(xw[i]), bf16_lo(aw[i]), z0);
+                        z0 = fmaf(bf16_hi(xw[i]), bf16_hi(aw[i]), z0);
+                        z1 = fmaf(bf16_lo(xw[i]), bf16_lo(bw[i]), z1);
+                        z1 = fmaf(bf16_hi(xw[i]), bf16_hi(bw[i]), z1);
+                    }
+                }
+            } else {
+                const uint16_t* wp = weights + ca;
+#pragma unroll 16
+                for (uint32_t k = k0; k < k1; k++) {
+                    const float xv = __uint_as_float((uint32_t)x[k] << 16);
+                    const uint32_t ww = *reinterpret_cast<const uint32_t*>(wp + (uint64_t)k * p.V);
+                    z0 = fmaf(xv, bf16_lo(ww), z0);
+                    z1 = fmaf(xv, bf16_hi(ww), z1);
+                }
+            }
+        }
+        __syncthreads();  // the previous row's readers of `part` are done
+        part[warp][2 * lane] = z0;
+        part[warp][2 * lane + 1] = z1;
+        __syncthreads();
+        if (warp != 0) continue;
+        z0 = part[0][2 * lane];
+        z1 = part[0][2 * lane + 1];
+#pragma unroll
+        for (int w = 1; w < 8; w++) {
+            z0 += part[w][2 * lane];
+            z1 += part[w][2 * lane + 1];
+        }
+        const ReadoutPick pk = picks[row];
+        if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
+        bool ok0 = ca < p.V, ok1 = ca + 1 < p.V;
+        if (p.allow) {
+            const uint8_t* mp = p.allow + row * p.allow_stride;
+            ok0 = ok0 && mp[ca] != 0;
+            ok1 = ok1 && mp[ca + 1] != 0;
+        }
+        const float m = pk.m;
+        const float e0v = ok0 ? ex2_approx((fmaxf(z0, -FLT_MAX) - m) * kLog2e) : 0.f, e1v = ok1 ? ex2_approx((fmaxf(z1, -FLT_MAX) - m) * kLog2e) : 0.f;
+        const double pair = (double)e0v + (double)e1v;
+        const double incl = warp_scan_incl(pair, lane);
+        const uint32_t cross = __ballot_sync(0xffffffffu, pair > 0.0 && incl > pk.resid);
+        const uint32_t has = __ballot_sync(0xffffffffu, pair > 0.0);
+        int32_t token = -1;
+        float ztok = nan;
+        if (has) {
+            const int owner = cross ? __ffs(cross) - 1 : 31 - __clz(has);
+            int32_t tk = -1;
+            float zt = nan;
+            if (lane == owner) {
+                const double b0 = incl - pair;
+                if (cross ? (e0v > 0.f && b0 + (double)e0v > pk.resid) : !(e1v > 0.f)) { tk = (int32_t)ca; zt = z0; }
+                else if (e1v > 0.f) { tk = (int32_t)ca + 1; zt = z1; }
+                else { tk = (int32_t)ca; zt = z0; }
+            }
+            token = __shfl_sync(0xffffffffu, tk, owner);
+            ztok = __shfl_sync(0xffffffffu, zt, owner);
+        }
+        if (lane == 0) {
+            tokens[row] = token;
+            if (logp) logp[row] = token < 0 ? nan : (ztok - m) - pk.lnZ;
+        }
     }
 }
 

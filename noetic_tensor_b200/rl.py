@@ -268,3 +268,19 @@ def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
     o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, tokens=tokens.reshape(-1).to(torch.int32).contiguous(), round_bf16=round_bf16)
     ops.check_status(o.status)
     return o.logp.reshape(lead), o.entropy.reshape(lead)
+
+
+def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None):
+    """`sample_categorical(head(x), 1.0, mask, ·)` by inverse CDF against `uniforms` (one per
+    position) without the logits in between: tokens [...] (int32), their log-probs and the
+    per-position entropies. `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
+    position with no allowed token with the reference's message (src/nn/rl.rs:516-519)."""
+    lead = hidden.shape[:-1]
+    V = weight.shape[1]
+    allow = None
+    if vocab_mask is not None:
+        allow = vocab_mask.reshape(-1, V)
+        allow = (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous()
+    o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow)
+    ops.check_status(o.status)
+    return o.tokens.reshape(lead), o.logp.reshape(lead), o.entropy.reshape(lead)
