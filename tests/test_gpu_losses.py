@@ -281,7 +281,7 @@ def test_all_masked_and_one_token(oracle):
 
 def test_check_scored_finite_names_the_first_position(oracle):
     """check_scored_finite (src/nn/rl.rs:204-211; its test src/nn/tests/rl.rs:837-846) through the C
-    ABI: the same verdict and message as the oracle's restatement, on the reference's hand cases
+    ABI: the same result and message as the oracle's restatement, on the reference's hand cases
     and on random placements of −inf / NaN / +inf under random scoring masks."""
     from noetic_tensor_b200 import ops, rl
 
