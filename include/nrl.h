@@ -517,7 +517,8 @@ enum {
                                      row's mass per 64 columns; a second small kernel finds the 64 columns holding u·Z and
                                      computes those 64 logits again (f32) to walk to the token */
     NRL_READOUT_ONE_CTA = 1u << 2 /* one CTA per 128-row block (tcgen05 cta_group::1) instead of CTA pairs on 256-row blocks
-                                    (cta_group::2, the default for more than 128 rows); the results are the same bits */
+                                    (cta_group::2, the default for more than 128 rows), and one launch however many rows: the same bits up to
+                                    24 576 rows; beyond, the count of column ranges, and with it the last bits of the sums, may differ */
 };
 
 typedef struct nrl_readout_args {
@@ -541,7 +542,9 @@ typedef struct nrl_readout_args {
     nrl_devptr uniforms;     /* f32 [rows] in [0,1), for NRL_READOUT_SAMPLE; else 0 */
 } nrl_readout_args;
 
-/* scratch for a call with these flags (sampling adds 32 bytes per row and vocabulary tile) */
+/* scratch for a call with these flags (sampling adds 32 bytes per row and vocabulary tile). More than
+ * 24 576 rows run as several launches of at most that many rows in stream order over the same scratch,
+ * so it stops growing there. */
 uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags);
 int nrl_readout_fwd(const nrl_readout_args* args, nrl_stream stream);
 

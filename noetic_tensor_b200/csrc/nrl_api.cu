@@ -538,8 +538,39 @@ static uint64_t readout_parts_bytes(uint64_t rows, uint32_t V, uint32_t d) {
     return (rows * (a > b ? a : b) * kRoPartFloats * sizeof(float) + 255) & ~255ull;
 }
 
+// Rows per launch. Every CTA of a launch has the same amount of work and the CTAs that walk one column range share its W
+// tiles through L2 only while they stay in step; over tens of waves they drift apart (B200, d = 4096, V = 128 256: 1.34
+// PFLOP/s at 65 536 rows, 1.24 at 131 072, 1.13 at 262 144 in one launch). So a large batch goes out as launches of 8192 to
+// 24 576 rows, each on CTA pairs and each a whole number of full waves: the count of 256-row blocks b that wastes the
+// fewest of its waves' 74 pair slots, the larger b on a tie.
+static uint64_t readout_chunk_rows(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags) {
+    if ((flags & NRL_READOUT_ONE_CTA) || rows <= 24576) return rows;
+    uint64_t best = 64;
+    double best_eff = -1.0;
+    for (uint64_t b = 32; b <= 96; b++) {
+        const uint32_t s = readout_nsplit(b * 2 * kRoBM, V, d, true);
+        uint64_t gb = 74 / s;
+        if (gb < 1) gb = 1;
+        if (gb > b) gb = b;
+        const uint64_t slots = ((b + gb - 1) / gb * gb * s + 73) / 74 * 74;  // the launch pads its last group
+        const double eff = (double)(b * s) / (double)slots;
+        if (eff >= best_eff) { best_eff = eff; best = b; }
+    }
+    return best * 2 * kRoBM;
+}
+
+static uint64_t readout_workspace_one(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags);
+
 extern "C" uint64_t nrl_readout_workspace_bytes(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags) {
     if (rows == 0 || V == 0 || d == 0) return 0;
+    const uint64_t chunk = readout_chunk_rows(rows, V, d, flags);
+    if (chunk >= rows) return readout_workspace_one(rows, V, d, flags);
+    const uint64_t a = readout_workspace_one(chunk, V, d, flags), tail = rows % chunk;
+    const uint64_t b = tail ? readout_workspace_one(tail, V, d, flags) : 0;
+    return a > b ? a : b;
+}
+
+static uint64_t readout_workspace_one(uint64_t rows, uint32_t V, uint32_t d, uint32_t flags) {
     uint64_t n = readout_parts_bytes(rows, V, d);
     if (flags & NRL_READOUT_SAMPLE) {
         const uint64_t nslabs = (uint64_t)((V + kRoBN - 1) / kRoBN) * (kRoBN / kRoLogCols);
@@ -574,6 +605,8 @@ static int encode_bf16_2d(CUtensorMap* map, uint64_t base, uint64_t inner, uint6
     return r == CUDA_SUCCESS ? NRL_OK : NRL_E_BAD_ARG;
 }
 
+static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream);
+
 extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
@@ -590,6 +623,32 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
     if (e != cudaSuccess) return (int)e;
     if (cc_major != 10) return NRL_E_UNSUPPORTED;  // tcgen05 / tensor memory
+    const uint64_t chunk = readout_chunk_rows(a->rows, a->V, a->d, a->flags);
+    if (chunk >= a->rows) return readout_fwd_one(a, stream);
+    if (!a->workspace || a->workspace_bytes < nrl_readout_workspace_bytes(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
+    // launches in stream order share the workspace: one launch's last kernel has read it before the next one's first writes
+    for (uint64_t r0 = 0; r0 < a->rows; r0 += chunk) {
+        nrl_readout_args c = *a;
+        c.rows = a->rows - r0 < chunk ? a->rows - r0 : chunk;
+        c.hidden = a->hidden + r0 * a->d * 2;
+        if (a->tokens) c.tokens = a->tokens + r0 * 4;
+        if (a->logp) c.logp = a->logp + r0 * 4;
+        if (a->entropy) c.entropy = a->entropy + r0 * 4;
+        if (a->rowstats) c.rowstats = a->rowstats + r0 * 16;
+        if (a->status) c.status = a->status + r0;
+        if (a->logits_out) c.logits_out = a->logits_out + r0 * a->V * 2;
+        if (a->allow_mask) c.allow_mask = a->allow_mask + r0 * a->allow_row_stride;
+        if (a->uniforms) c.uniforms = a->uniforms + r0 * 4;
+        const int rc = readout_fwd_one(&c, stream);
+        if (rc) return rc;
+    }
+    return NRL_OK;
+}
+
+// One launch of the readout kernel (and the kernels that finish or sample its rows) over arguments already checked.
+static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream) {
+    cudaError_t e = cudaSuccess;
+    const bool sample = (a->flags & NRL_READOUT_SAMPLE) != 0;
     ReadoutParams p;
     memset(&p, 0, sizeof p);
     p.rows = a->rows;
@@ -613,7 +672,7 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
     p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
     p.tokens = sample ? nullptr : (const int32_t*)a->tokens;
-    if (!a->workspace || a->workspace_bytes < nrl_readout_workspace_bytes(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
+    if (!a->workspace || a->workspace_bytes < readout_workspace_one(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
     p.parts = (float*)a->workspace;
     p.allow = (const uint8_t*)a->allow_mask;
     p.allow_stride = a->allow_row_stride;

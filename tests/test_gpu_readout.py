@@ -235,3 +235,39 @@ def test_readout_sampling_distribution_and_refusals():
     o = ops.readout_forward(x[:200].contiguous(), w, uniforms=u[:200].contiguous(), allow=rows_mask)
     st = o.status.cpu().numpy()
     assert st[17] == 1 and o.tokens[17] == -1 and (np.delete(st, 17) == 0).all()
+
+
+def test_readout_batches_beyond_one_launch():
+    """More than 24 576 rows go out as several launches over one workspace (each a whole number of
+    waves of CTA pairs): every output row against nrl_row_fwd on the logits the call wrote, given
+    tokens and drawn ones, with per-row masks, and against the single launch of NRL_READOUT_ONE_CTA."""
+    from noetic_tensor_b200 import capi, ops
+
+    rows, d, V = 60077, 64, 1000
+    x, w, tok = make(rows, d, V, 99)
+    assert capi.lib().nrl_readout_workspace_bytes(rows, V, d, 0) < capi.lib().nrl_readout_workspace_bytes(rows, V, d, capi.READOUT_ONE_CTA)
+    o = ops.readout_forward(x, w, tokens=tok, round_bf16=True, want_logits=True)
+    assert (o.status == 0).all()
+    f = ops.row_forward(o.logits, tokens=tok)
+    close(o.logp.cpu().numpy(), f.logp.cpu().numpy(), "logp vs nrl_row_fwd")
+    close(o.entropy.cpu().numpy(), f.entropy.cpu().numpy(), "entropy vs nrl_row_fwd")
+    assert torch.equal(o.rowstats[:, 0], f.rowstats[:, 0])
+    one = ops.readout_forward(x, w, tokens=tok, round_bf16=True, want_logits=True, one_cta=True)
+    assert torch.equal(one.logits.view(torch.int16), o.logits.view(torch.int16))
+    close(o.logp.cpu().numpy(), one.logp.cpu().numpy(), "logp vs one launch")
+    g = torch.Generator(device=dev())
+    g.manual_seed(4)
+    u = torch.rand(rows, generator=g, device=dev())
+    allow = (torch.rand(rows, V, generator=g, device=dev()) < 0.3).to(torch.uint8)
+    allow[:, 5] = 1
+    allow[40000] = 0
+    s = ops.readout_forward(x, w, uniforms=u, allow=allow, round_bf16=True, want_logits=True)
+    st = s.status.cpu().numpy()
+    assert st[40000] == 1 and s.tokens[40000] == -1 and (np.delete(st, 40000) == 0).all()
+    fs = ops.row_forward(s.logits, allow=allow, uniforms=u)
+    keep = torch.ones(rows, dtype=torch.bool, device=dev())
+    keep[40000] = False
+    differ = (fs.tokens != s.tokens) & keep
+    assert int(differ.sum()) <= rows // 100, f"{int(differ.sum())} of {rows} tokens differ from nrl_row_fwd's sampler"
+    assert allow[torch.arange(rows, device=dev())[keep], s.tokens.long()[keep]].all()
+    close(s.entropy[keep].cpu().numpy(), fs.entropy[keep].cpu().numpy(), "entropy vs nrl_row_fwd")
