@@ -376,6 +376,45 @@ static void launch_lane(const nrl_lane_args* a, bool vec, unsigned grid, unsigne
     }
 }
 
+// softmax / log_softmax on clusters of `csize` CTAs, each holding `per` vectors of a row
+template <int DT, bool LOG>
+static int launch_lane_cluster_as(const nrl_lane_args* a, uint32_t csize, uint32_t per, uint32_t vec_bytes, cudaStream_t st) {
+    auto kernel = lane_softmax_cluster_kernel<DT, LOG>;
+    const uint32_t smem = per * vec_bytes;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = csize;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.gridDim = dim3(csize, 1, 1);
+    cfg.blockDim = dim3(kLaneClusterThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int resident = 0;
+    e = cudaOccupancyMaxActiveClusters(&resident, kernel, &cfg);
+    if (e != cudaSuccess || resident < 1) {
+        (void)cudaGetLastError();
+        return NRL_E_UNSUPPORTED;  // the caller falls back to the kernel that reads the row twice
+    }
+    const uint64_t clusters = a->rows < (uint64_t)resident ? a->rows : (uint64_t)resident;
+    cfg.gridDim = dim3((unsigned)(clusters * csize), 1, 1);
+    e = cudaLaunchKernelEx(&cfg, kernel, (const void*)a->x, (float*)a->out, (uint64_t)a->rows, (uint32_t)a->V, per);
+    if (e != cudaSuccess) return (int)e;
+    return after_launch();
+}
+
+static int launch_lane_cluster(const nrl_lane_args* a, uint32_t csize, uint32_t per, uint32_t vec_bytes, cudaStream_t st) {
+    const bool log = a->op == NRL_LANE_LOG_SOFTMAX;
+    if (a->dtype == NRL_F32) return log ? launch_lane_cluster_as<NRL_F32, true>(a, csize, per, vec_bytes, st) : launch_lane_cluster_as<NRL_F32, false>(a, csize, per, vec_bytes, st);
+    return log ? launch_lane_cluster_as<NRL_BF16, true>(a, csize, per, vec_bytes, st) : launch_lane_cluster_as<NRL_BF16, false>(a, csize, per, vec_bytes, st);
+}
+
 extern "C" int nrl_lane_op(const nrl_lane_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_lane_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || !a->x || a->op > NRL_LANE_LOGSUMEXP_BWD) return NRL_E_BAD_ARG;
@@ -401,6 +440,16 @@ extern "C" int nrl_lane_op(const nrl_lane_args* a, nrl_stream stream) {
     const uint64_t cap = wide ? 148ull : 148ull * 8ull;
     const unsigned grid = (unsigned)(a->rows < cap ? a->rows : cap);
     cudaStream_t st = (cudaStream_t)stream;
+    if (fwd_full && vec && row_bytes * 1184ull > (96ull << 20)) {
+        // rows that L2 would not keep until their second read: a cluster holds the row in shared memory
+        const uint32_t nvec = a->V / kVec, vec_bytes = (uint32_t)(kVec * esize);
+        uint32_t csize = (uint32_t)(((uint64_t)nvec * vec_bytes + kLaneSliceBytes - 1) / kLaneSliceBytes);
+        while (csize <= kLaneMaxCluster && (uint64_t)((nvec + csize - 1) / csize) * vec_bytes > kLaneSliceBytes) csize++;
+        if (csize <= kLaneMaxCluster) {
+            const int rc = launch_lane_cluster(a, csize, (nvec + csize - 1) / csize, vec_bytes, st);
+            if (rc != NRL_E_UNSUPPORTED) return rc;
+        }
+    }
     if (bwd_y) {
         const float *y = (const float*)a->x, *g = (const float*)a->g;
         float* dx = (float*)a->out;
