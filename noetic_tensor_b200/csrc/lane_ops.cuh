@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(kLaneClusterThreads) lane_softmax_cluster_kern
     bool failed = false;
     for (uint64_t row = cluster; row < rows; row += nclusters, parity ^= 1u) {
         cp_async_wait<0>();
-        __syncthreads();
+        __syncthreads();  // the row's slice is complete, and everyone is done with the previous row
         // this thread's pieces q, q + blockDim (consecutive lanes read consecutive pieces: no bank conflicts), two per step
         MaxSum p;
         p.m = NRL_NEG_INF;
@@ -355,16 +355,28 @@ __global__ void __launch_bounds__(kLaneClusterThreads) lane_softmax_cluster_kern
         // 16-byte stores would each fill half of every 32-byte sector)
         float* dst = out + row * V + (uint64_t)v0 * kVec;
         const float m = t.m, lnS = logf(t.S), inv = 1.f / t.S;
+        // f32 rows: as soon as a piece has been read for the last time, the same thread requests the next row's 16
+        // bytes for that place, so the copy of row r + 1 is in flight while row r is still being written (+4 %). A
+        // 16-byte copy is two bf16 pieces, read by two lanes; pairing them up cost more than it gained: bf16 rows
+        // request the next slice after the pass.
+        constexpr bool kEarly = DT == NRL_F32;
+        const bool more = row + nclusters < rows;
+        const unsigned char* next = (const unsigned char*)x + ((row + nclusters) * V + (uint64_t)v0 * kVec) * (kVecBytes / kVec);
 #pragma unroll 4
         for (uint32_t q = threadIdx.x; q < pieces; q += blockDim.x) {
             float z[4], y[4];
             lane_piece4<DT>(slice, q, z);
+            if (kEarly && more) cp_async16(slice + q * 16u, next + (uint64_t)q * 16u);
 #pragma unroll
             for (int i = 0; i < 4; i++) y[i] = LOG ? (z[i] - m) - lnS : ex2_approx((z[i] - m) * kLog2e) * inv;
             stg_stream16(dst + (uint64_t)q * 4, y[0], y[1], y[2], y[3]);
         }
-        __syncthreads();  // the slice is free for the next row
-        fetch(row + nclusters);
+        if constexpr (kEarly) {
+            cp_async_commit();
+        } else {
+            __syncthreads();  // the slice is free for the next row
+            fetch(row + nclusters);
+        }
     }
     cluster_sync_all();  // no CTA leaves while a peer may still send to it
 }
