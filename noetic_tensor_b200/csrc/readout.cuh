@@ -794,62 +794,95 @@ __global__ void __launch_bounds__(1024) readout_bucket_kernel(uint64_t rows, uin
     }
 }
 
-// grid (kRoDrawParts, slabs) — the parts of a slab next to each other in launch order, so that they run
-// together and share the slab of W through L2: block (y, s) takes the rows y, y + kRoDrawParts, … of slab s's group;
-// its eight warps split the d terms of a row's 64 dot products (each warp a contiguous eighth,
-// loads 16 deep), the partial sums meet in shared memory and are added in warp order.
-constexpr int kRoDrawParts = 4;
+// grid (kRoDrawParts, slabs): the rows that picked slab s are taken kRoDrawRows at a time, block (y, s) taking the
+// groups y, y + kRoDrawParts, …; the rows of a group share one pass over the slab of W (64 · d · 2 bytes: with one row
+// per pass the kernel was bound by what an SM can pull out of L2). The eight warps split the d terms of the dot
+// products (each warp a contiguous eighth, 16 loads of W deep), the partial sums meet in shared memory and are added
+// in warp order: a row's recomputed logits do not depend on which rows share its pass. Warp i then walks row i.
+constexpr int kRoDrawParts = 8;
+constexpr int kRoDrawRows = 4;
 __global__ void __launch_bounds__(256) readout_draw_kernel(ReadoutParams p, const ReadoutPick* picks, const uint32_t* bucket_start, const uint32_t* order, int32_t* tokens, float* logp,
                                                           const uint16_t* hidden, const uint16_t* weights) {
-    __shared__ float part[8][kRoLogCols];
+    constexpr int R = kRoDrawRows;
+    __shared__ float part[8][R][kRoLogCols];
     const uint32_t slab = blockIdx.y;
-    const uint32_t r0 = bucket_start[slab], r1 = bucket_start[slab + 1];
+    const uint32_t r0 = bucket_start[slab], n = bucket_start[slab + 1] - r0;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const float nan = __int_as_float(0x7fc00000);
     const uint32_t c0 = slab * kRoLogCols, ca = c0 + 2 * lane;  // this lane's two columns
-    const uint32_t kper = ((p.d + 63) / 64) * 8;                // terms per warp, a multiple of 8
+    const uint32_t kper = ((p.d + 63) / 64) * 8;                // terms per warp, a multiple of 8 (as d is)
     const uint32_t k0 = min((uint32_t)warp * kper, p.d), k1 = min(k0 + kper, p.d);
-    for (uint32_t j = r0 + blockIdx.x; j < r1; j += kRoDrawParts) {
-        const uint64_t row = order[j];
-        float z0 = 0.f, z1 = 0.f;
-        const uint16_t* x = hidden + row * p.d;
+    for (uint32_t g = blockIdx.x * R; g < n; g += gridDim.x * R) {
+        const uint32_t cnt = min((uint32_t)R, n - g);
+        uint64_t rows[R];
+        const uint16_t* x[R];
+        float z[R][2];
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            rows[i] = order[r0 + g + min((uint32_t)i, cnt - 1)];  // a short group repeats its last row: computed, not used
+            x[i] = hidden + rows[i] * p.d;
+            z[i][0] = z[i][1] = 0.f;
+        }
         if (ca < p.V) {
             if (p.w_is_vd) {
                 const uint16_t *wa = weights + (uint64_t)ca * p.d, *wb = wa + p.d;
 #pragma unroll 2
                 for (uint32_t k = k0; k < k1; k += 8) {
-                    const uint4 xq = *reinterpret_cast<const uint4*>(x + k), aq = *reinterpret_cast<const uint4*>(wa + k), bq = *reinterpret_cast<const uint4*>(wb + k);
-                    const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w}, aw[4] = {aq.x, aq.y, aq.z, aq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
+                    const uint4 aq = *reinterpret_cast<const uint4*>(wa + k), bq = *reinterpret_cast<const uint4*>(wb + k);
+                    const uint32_t aw[4] = {aq.x, aq.y, aq.z, aq.w}, bw[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        z0 = fmaf(bf16_lo(xw[i]), bf16_lo(aw[i]), z0);
-                        z0 = fmaf(bf16_hi(xw[i]), bf16_hi(aw[i]), z0);
-                        z1 = fmaf(bf16_lo(xw[i]), bf16_lo(bw[i]), z1);
-                        z1 = fmaf(bf16_hi(xw[i]), bf16_hi(bw[i]), z1);
+                    for (int i = 0; i < R; i++) {
+                        const uint4 xq = *reinterpret_cast<const uint4*>(x[i] + k);
+                        const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w};
+#pragma unroll
+                        for (int t = 0; t < 4; t++) {
+                            z[i][0] = fmaf(bf16_lo(xw[t]), bf16_lo(aw[t]), z[i][0]);
+                            z[i][0] = fmaf(bf16_hi(xw[t]), bf16_hi(aw[t]), z[i][0]);
+                            z[i][1] = fmaf(bf16_lo(xw[t]), bf16_lo(bw[t]), z[i][1]);
+                            z[i][1] = fmaf(bf16_hi(xw[t]), bf16_hi(bw[t]), z[i][1]);
+                        }
                     }
                 }
             } else {
                 const uint16_t* wp = weights + ca;
-#pragma unroll 16
-                for (uint32_t k = k0; k < k1; k++) {
-                    const float xv = __uint_as_float((uint32_t)x[k] << 16);
-                    const uint32_t ww = *reinterpret_cast<const uint32_t*>(wp + (uint64_t)k * p.V);
-                    z0 = fmaf(xv, bf16_lo(ww), z0);
-                    z1 = fmaf(xv, bf16_hi(ww), z1);
+#pragma unroll 2
+                for (uint32_t k = k0; k < k1; k += 8) {
+                    uint32_t ww[8];
+#pragma unroll
+                    for (int t = 0; t < 8; t++) ww[t] = *reinterpret_cast<const uint32_t*>(wp + (uint64_t)(k + t) * p.V);
+#pragma unroll
+                    for (int i = 0; i < R; i++) {
+                        const uint4 xq = *reinterpret_cast<const uint4*>(x[i] + k);  // the same address in every lane: one fetch
+                        const uint32_t xw[4] = {xq.x, xq.y, xq.z, xq.w};
+#pragma unroll
+                        for (int t = 0; t < 4; t++) {
+                            const float xl = bf16_lo(xw[t]), xh = bf16_hi(xw[t]);
+                            z[i][0] = fmaf(xl, bf16_lo(ww[2 * t]), z[i][0]);
+                            z[i][1] = fmaf(xl, bf16_hi(ww[2 * t]), z[i][1]);
+                            z[i][0] = fmaf(xh, bf16_lo(ww[2 * t + 1]), z[i][0]);
+                            z[i][1] = fmaf(xh, bf16_hi(ww[2 * t + 1]), z[i][1]);
+                        }
+                    }
                 }
             }
         }
-        __syncthreads();  // the previous row's readers of `part` are done
-        part[warp][2 * lane] = z0;
-        part[warp][2 * lane + 1] = z1;
+        __syncthreads();  // the previous group's readers of `part` are done
+#pragma unroll
+        for (int i = 0; i < R; i++) {
+            part[warp][i][2 * lane] = z[i][0];
+            part[warp][i][2 * lane + 1] = z[i][1];
+        }
         __syncthreads();
-        if (warp != 0) continue;
-        z0 = part[0][2 * lane];
-        z1 = part[0][2 * lane + 1];
+        if ((uint32_t)warp >= cnt) continue;
+        uint64_t row = rows[0];
+#pragma unroll
+        for (int i = 1; i < R; i++)
+            if (warp == i) row = rows[i];
+        float z0 = part[0][warp][2 * lane], z1 = part[0][warp][2 * lane + 1];
 #pragma unroll
         for (int w = 1; w < 8; w++) {
-            z0 += part[w][2 * lane];
-            z1 += part[w][2 * lane + 1];
+            z0 += part[w][warp][2 * lane];
+            z1 += part[w][warp][2 * lane + 1];
         }
         const ReadoutPick pk = picks[row];
         if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
