@@ -199,12 +199,28 @@ __device__ __forceinline__ void acc_rebase_ref(Acc& a, float mn) {
 // row, so one vote per vector keeps the rebase (an accurate expf), the −inf handling and the
 // first-data case off the common path; with per-lane maxima a warp would take that path at
 // almost every step. The common path is packed f32x2 arithmetic and 3-input min/max.
-template <bool REF, bool LOG>
-__device__ __forceinline__ void accumulate(Acc& a, float z[8], float zr[8]) {
-    float vmax = fmax3_nan(fmax3_nan(fmax3_nan(z[0], z[1], z[2]), z[3], z[4]), fmax3_nan(z[5], z[6], z[7]), z[0]);
-    const float vmin = fmin3(fmin3(fmin3(z[0], z[1], z[2]), z[3], z[4]), fmin3(z[5], z[6], z[7]), z[0]);
+template <int N>
+__device__ __forceinline__ float vec_max_nan(const float* z) {
+    float m = fmax3_nan(fmax3_nan(fmax3_nan(z[0], z[1], z[2]), z[3], z[4]), fmax3_nan(z[5], z[6], z[7]), z[0]);
+    if constexpr (N == 16) m = fmax3_nan(m, fmax3_nan(fmax3_nan(z[8], z[9], z[10]), z[11], z[12]), fmax3_nan(z[13], z[14], z[15]));
+    return m;
+}
+template <int N>
+__device__ __forceinline__ float vec_min(const float* z) {
+    float m = fmin3(fmin3(fmin3(z[0], z[1], z[2]), z[3], z[4]), fmin3(z[5], z[6], z[7]), z[0]);
+    if constexpr (N == 16) m = fmin3(m, fmin3(fmin3(z[8], z[9], z[10]), z[11], z[12]), fmin3(z[13], z[14], z[15]));
+    return m;
+}
+
+// N = 8: one vector per lane. N = 16: the lane's vectors of two consecutive tiles folded as one step (one vote, one
+// bookkeeping step for both).
+template <bool REF, bool LOG, int N = 8>
+__device__ __forceinline__ void accumulate(Acc& a, float* z, float* zr) {
+    static_assert(N == 8 || N == 16, "one or two vectors");
+    float vmax = vec_max_nan<N>(z);
+    const float vmin = vec_min<N>(z);
     float rmax = NRL_NEG_INF;
-    if (REF) rmax = fmax3_nan(fmax3_nan(fmax3_nan(zr[0], zr[1], zr[2]), zr[3], zr[4]), fmax3_nan(zr[5], zr[6], zr[7]), zr[0]);
+    if (REF) rmax = vec_max_nan<N>(zr);
     const bool slow = !(vmax <= a.m) || vmin == NRL_NEG_INF || (REF && !(rmax <= a.mr));
     if (__any_sync(0xffffffffu, slow)) {
         if (vmin == NRL_NEG_INF) {
@@ -213,7 +229,7 @@ __device__ __forceinline__ void accumulate(Acc& a, float z[8], float zr[8]) {
             // touched where the policy's was −inf, so a token the policy can draw but the
             // reference excludes still gives KL = +inf.
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
+            for (int i = 0; i < N; i++) {
                 if (z[i] == NRL_NEG_INF) {
                     z[i] = -FLT_MAX;
                     if (REF) zr[i] = fmaxf(zr[i], -FLT_MAX);
@@ -233,7 +249,7 @@ __device__ __forceinline__ void accumulate(Acc& a, float z[8], float zr[8]) {
         const f32x2 m2 = pack2(a.m, a.m);
         const f32x2 before = a.S2;
 #pragma unroll
-        for (int i = 0; i < 8; i += 2) {
+        for (int i = 0; i < N; i += 2) {
             const f32x2 zz = pack2(z[i], z[i + 1]);
             const f32x2 t = sub2(zz, m2);
             float a0, a1;
@@ -255,7 +271,7 @@ __device__ __forceinline__ void accumulate(Acc& a, float z[8], float zr[8]) {
             // term of the row by the rounding of that product, and ln Zr with it
             const f32x2 mr2 = pack2(a.mr, a.mr);
 #pragma unroll
-            for (int i = 0; i < 8; i += 2) {
+            for (int i = 0; i < N; i += 2) {
                 float a0, a1;
                 unpack2(mul2(sub2(pack2(zr[i], zr[i + 1]), mr2), l2e), a0, a1);
                 a.Sr2 = add2(a.Sr2, pack2(ex2_approx(a0), ex2_approx(a1)));
@@ -345,13 +361,21 @@ typedef SampleLog<kLogCompact, true> CompactLog;
 // ring of kRingRows × 32 16-byte slots. With LOG, `sink(chunk, acc)` is called by all 32 lanes at
 // the end of every chunk of `tiles_per_chunk` tiles (acc.G is the lane's mass in the chunk at
 // maximum acc.m). Returns the part's partial (valid in lane 0).
+#ifndef NRL_PAIR_TILES
+#define NRL_PAIR_TILES 1
+#endif
 template <int DT, bool REF, bool LOG, class Sink>
 __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_t row, uint32_t part_index, uint4* wring, Sink&& sink, uint32_t& chunks, uint32_t& tiles_per_chunk) {
     const int lane = threadIdx.x & 31;
+    // 2-byte elements: a step takes two consecutive tiles (the lane's two vectors are folded together: one vote,
+    // one round of pipeline bookkeeping for 16 elements; the loop is bound by instruction issue, not by memory)
+    constexpr int kT = (DT == NRL_BF16 && NRL_PAIR_TILES) ? 2 : 1;  // tiles per step
+    constexpr bool kWide = kT == 2 && !REF;  // with a reference stream 32 values at once do not fit the registers: two folds of 8 + 8 per step
     constexpr int kPer = (DT == NRL_F32 ? 2 : 1);     // 16-byte pieces per lane per stream per tile
-    constexpr int kRows = kPer * (REF ? 2 : 1);       // ring rows one tile takes
-    constexpr int kSlots = kRingRows / kRows;         // tiles in flight
+    constexpr int kRows = kPer * (REF ? 2 : 1) * kT;  // ring rows one step takes
+    constexpr int kSlots = kRingRows / kRows;         // steps in flight
     constexpr uint32_t kEsize = (DT == NRL_F32 ? 4 : 2);
+    constexpr uint32_t kStep = kT * kTile;            // elements per step
     uint32_t begin, end;
     part_range(p, part_index, begin, end);
     Acc acc = acc_empty();
@@ -360,13 +384,14 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     // 8 elements of the tile; with 4-byte elements a lane takes two pieces of 4 elements, 128
     // elements apart (lane·4 … and 128 + lane·4 …), so that neither copy touches half sectors.
     constexpr uint32_t kLaneElems = 16 / kEsize;  // elements per 16-byte piece
-    constexpr uint32_t kPieceGap = 128;           // F32: elements between a lane's two pieces
+    constexpr uint32_t kPieceGap = kT == 2 ? kTile : 128;  // elements between a lane's two pieces: the next tile (bf16 pairs) or half a tile (f32)
+    constexpr int kPieces = kPer * kT;                     // pieces per lane per stream per step
     const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kLaneElems) * kEsize;
     const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kLaneElems) * kEsize : nullptr;
-    uint32_t v = begin + lane * kLaneElems;  // this lane's first element of the tile it consumes next
-    // sampling log: chunks of `gsz` tiles, at most kLogDense of them
+    uint32_t v = begin + lane * kLaneElems;  // this lane's first element of the step it consumes next
+    // sampling log: chunks of `gsz` tiles (a whole number of steps), at most kLogDense of them
     const uint32_t ntiles = (end - begin + kTile - 1) / kTile;
-    const uint32_t gsz = (ntiles + kLogDense - 1) / kLogDense;
+    const uint32_t gsz = ((ntiles + kLogDense - 1) / kLogDense + kT - 1) / kT * kT;
     uint32_t left = gsz, chunk = 0;
     auto flush = [&]() {
         sink(chunk, acc);
@@ -376,54 +401,84 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     };
     auto issue = [&](int slot, uint32_t vv, const char* xq, const char* rq) {
 #pragma unroll
-        for (int k = 0; k < kPer; k++) {
+        for (int k = 0; k < kPieces; k++) {
             if (vv + k * kPieceGap < end) {
-                cp_async16(base + (slot * kRows + k) * 512, xq + 512 * k);
-                if (REF) cp_async16(base + (slot * kRows + kPer + k) * 512, rq + 512 * k);
+                cp_async16(base + (slot * kRows + k) * 512, xq + kPieceGap * kEsize * k);
+                if (REF) cp_async16(base + (slot * kRows + kPieces + k) * 512, rq + kPieceGap * kEsize * k);
             }
         }
-        cp_async_commit();  // one group per tile, empty or not, so that the group count stays in step
+        cp_async_commit();  // one group per step, empty or not, so that the group count stays in step
     };
 #pragma unroll
-    for (int s = 0; s < kSlots; s++) issue(s, v + s * kTile, xp + (size_t)s * kTile * kEsize, REF ? rp + (size_t)s * kTile * kEsize : nullptr);
-    for (uint32_t t0 = begin; t0 < end; t0 += kSlots * kTile) {  // warp-uniform
-        // not unrolled: one copy of the per-tile arithmetic keeps the loop inside the instruction cache
+    for (int s = 0; s < kSlots; s++) issue(s, v + s * kStep, xp + (size_t)s * kStep * kEsize, REF ? rp + (size_t)s * kStep * kEsize : nullptr);
+    for (uint32_t t0 = begin; t0 < end; t0 += kSlots * kStep) {  // warp-uniform
+        // not unrolled: one copy of the per-step arithmetic keeps the loop inside the instruction cache
         // (measured 4 % faster with a reference stream, 8 % without, than the loop unrolled over the slots)
 #pragma unroll 1
         for (int s = 0; s < kSlots; s++) {
-            cp_async_wait<kSlots - 1>();  // the oldest tile has landed
-            if (t0 + s * kTile < end) {  // warp-uniform: the tile exists
-                Raw<DT> x, r;
+            cp_async_wait<kSlots - 1>();  // the oldest step has landed
+            if (t0 + s * kStep < end) {  // warp-uniform: the step exists
                 if constexpr (DT == NRL_F32) {
+                    float z[8], zr[8];
+                    Raw<DT> x, r;
                     x.a = lds16(base + (s * kRows) * 512);
                     x.b = lds16(base + (s * kRows + 1) * 512);
+                    x.unpack(z);
                     if (REF) {
                         r.a = lds16(base + (s * kRows + 2) * 512);
                         r.b = lds16(base + (s * kRows + 3) * 512);
+                        r.unpack(zr);
                     }
+                    // a piece past the end of a ragged last tile: nothing was copied, nothing to add
+#pragma unroll
+                    for (int k = 0; k < kPer; k++) {
+                        if (v + k * kPieceGap >= end) {
+#pragma unroll
+                            for (int i = k * 4; i < (k + 1) * 4; i++) z[i] = zr[i] = -FLT_MAX;
+                        }
+                    }
+                    accumulate<REF, LOG>(acc, z, zr);
+                } else if constexpr (kWide) {
+                    float z[16], zr[16];
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        Raw<DT> x;
+                        x.q = lds16(base + (s * kRows + k) * 512);
+                        x.unpack(z + 8 * k);
+                        if (v + k * kTile >= end) {
+#pragma unroll
+                            for (int i = 8 * k; i < 8 * k + 8; i++) z[i] = -FLT_MAX;
+                        }
+                    }
+                    accumulate<false, LOG, 16>(acc, z, zr);
                 } else {
-                    x.q = lds16(base + (s * kRows) * 512);
-                    if (REF) r.q = lds16(base + (s * kRows + 1) * 512);
-                }
-                float z[8], zr[8];
-                x.unpack(z);
-                if (REF) r.unpack(zr);
-                // a piece past the end of a ragged last tile: nothing was copied, nothing to add
 #pragma unroll
-                for (int k = 0; k < kPer; k++) {
-                    if (v + k * kPieceGap >= end) {
+                    for (int k = 0; k < kT; k++) {
+                        float z[8], zr[8];
+                        Raw<DT> x, r;
+                        x.q = lds16(base + (s * kRows + k) * 512);
+                        x.unpack(z);
+                        if (REF) {
+                            r.q = lds16(base + (s * kRows + kT + k) * 512);
+                            r.unpack(zr);
+                        }
+                        if (v + k * kTile >= end) {
 #pragma unroll
-                        for (int i = k * (8 / kPer); i < (k + 1) * (8 / kPer); i++) z[i] = zr[i] = -FLT_MAX;
+                            for (int i = 0; i < 8; i++) z[i] = zr[i] = -FLT_MAX;
+                        }
+                        accumulate<REF, LOG>(acc, z, zr);
                     }
                 }
-                accumulate<REF, LOG>(acc, z, zr);
-                if (LOG && --left == 0) flush();
+                if (LOG) {
+                    left -= kT;
+                    if (left == 0) flush();
+                }
             }
-            // refill the slot just consumed with the tile kSlots ahead
-            issue(s, v + kSlots * kTile, xp + (size_t)kSlots * kTile * kEsize, REF ? rp + (size_t)kSlots * kTile * kEsize : nullptr);
-            v += kTile;
-            xp += (size_t)kTile * kEsize;
-            if (REF) rp += (size_t)kTile * kEsize;
+            // refill the slot just consumed with the step kSlots ahead
+            issue(s, v + kSlots * kStep, xp + (size_t)kSlots * kStep * kEsize, REF ? rp + (size_t)kSlots * kStep * kEsize : nullptr);
+            v += kStep;
+            xp += (size_t)kStep * kEsize;
+            if (REF) rp += (size_t)kStep * kEsize;
         }
     }
     cp_async_wait<0>();
