@@ -361,16 +361,16 @@ typedef SampleLog<kLogCompact, true> CompactLog;
 // ring of kRingRows × 32 16-byte slots. With LOG, `sink(chunk, acc)` is called by all 32 lanes at
 // the end of every chunk of `tiles_per_chunk` tiles (acc.G is the lane's mass in the chunk at
 // maximum acc.m). Returns the part's partial (valid in lane 0).
-#ifndef NRL_PAIR_TILES
-#define NRL_PAIR_TILES 1
-#endif
 template <int DT, bool REF, bool LOG, class Sink>
 __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_t row, uint32_t part_index, uint4* wring, Sink&& sink, uint32_t& chunks, uint32_t& tiles_per_chunk) {
     const int lane = threadIdx.x & 31;
-    // 2-byte elements: a step takes two consecutive tiles (the lane's two vectors are folded together: one vote,
-    // one round of pipeline bookkeeping for 16 elements; the loop is bound by instruction issue, not by memory)
-    constexpr int kT = (DT == NRL_BF16 && NRL_PAIR_TILES) ? 2 : 1;  // tiles per step
-    constexpr bool kWide = kT == 2 && !REF;  // with a reference stream 32 values at once do not fit the registers: two folds of 8 + 8 per step
+    // 2-byte elements: a step takes several consecutive tiles, so that one wait and one round of ring and pointer
+    // bookkeeping serve them all (the loop is bound by instruction issue, not by memory). Without a reference stream
+    // four tiles, folded 16 elements at a time (one vote per two vectors): +26 % over one tile per step. With one, two
+    // tiles folded 8 + 8: 32 values at once do not fit 64 registers (the 16-wide fold spilled and gained nothing), and
+    // four tiles of two streams would leave the 4 KB ring a single slot: +6 %.
+    constexpr int kT = DT == NRL_BF16 ? (REF ? 2 : 4) : 1;  // tiles per step
+    constexpr bool kWide = kT >= 2 && !REF;
     constexpr int kPer = (DT == NRL_F32 ? 2 : 1);     // 16-byte pieces per lane per stream per tile
     constexpr int kRows = kPer * (REF ? 2 : 1) * kT;  // ring rows one step takes
     constexpr int kSlots = kRingRows / kRows;         // steps in flight
@@ -384,7 +384,7 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     // 8 elements of the tile; with 4-byte elements a lane takes two pieces of 4 elements, 128
     // elements apart (lane·4 … and 128 + lane·4 …), so that neither copy touches half sectors.
     constexpr uint32_t kLaneElems = 16 / kEsize;  // elements per 16-byte piece
-    constexpr uint32_t kPieceGap = kT == 2 ? kTile : 128;  // elements between a lane's two pieces: the next tile (bf16 pairs) or half a tile (f32)
+    constexpr uint32_t kPieceGap = kT >= 2 ? kTile : 128;  // elements between a lane's two pieces: the next tile (bf16 pairs) or half a tile (f32)
     constexpr int kPieces = kPer * kT;                     // pieces per lane per stream per step
     const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kLaneElems) * kEsize;
     const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kLaneElems) * kEsize : nullptr;
@@ -439,18 +439,21 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
                     }
                     accumulate<REF, LOG>(acc, z, zr);
                 } else if constexpr (kWide) {
-                    float z[16], zr[16];
 #pragma unroll
-                    for (int k = 0; k < 2; k++) {
-                        Raw<DT> x;
-                        x.q = lds16(base + (s * kRows + k) * 512);
-                        x.unpack(z + 8 * k);
-                        if (v + k * kTile >= end) {
+                    for (int h = 0; h < kT / 2; h++) {
+                        float z[16], zr[16];
 #pragma unroll
-                            for (int i = 8 * k; i < 8 * k + 8; i++) z[i] = -FLT_MAX;
+                        for (int k = 0; k < 2; k++) {
+                            Raw<DT> x;
+                            x.q = lds16(base + (s * kRows + 2 * h + k) * 512);
+                            x.unpack(z + 8 * k);
+                            if (v + (2 * h + k) * kTile >= end) {
+#pragma unroll
+                                for (int i = 8 * k; i < 8 * k + 8; i++) z[i] = -FLT_MAX;
+                            }
                         }
+                        accumulate<false, LOG, 16>(acc, z, zr);
                     }
-                    accumulate<false, LOG, 16>(acc, z, zr);
                 } else {
 #pragma unroll
                     for (int k = 0; k < kT; k++) {
