@@ -240,7 +240,8 @@ __global__ void __launch_bounds__(kLaneMaxThreads) lane_softmax_kernel(const voi
 // which it does after it has read row r's.
 constexpr int kLaneClusterThreads = 256;  // 512 measured slower
 constexpr unsigned long long kLaneWaitLimitNs = 2000000000ull;  // a CTA waits this long for its cluster's pairs
-constexpr uint32_t kLaneSliceBytes = 74 * 1024;  // a CTA's slice: three CTAs per SM
+constexpr uint32_t kLaneSliceBytes = 74 * 1024;      // a CTA's slice: three CTAs per SM
+constexpr uint32_t kLaneSliceBytesTwo = 112 * 1024;  // or, for rows that need it, two
 constexpr uint32_t kLaneMaxCluster = 8;          // the portable cluster size (clusters of 10 to 16 measured slower)
 
 // four consecutive elements of a slice in shared memory: piece q

@@ -445,6 +445,8 @@ extern "C" int nrl_lane_op(const nrl_lane_args* a, nrl_stream stream) {
         const uint32_t nvec = a->V / kVec, vec_bytes = (uint32_t)(kVec * esize);
         uint32_t csize = (uint32_t)(((uint64_t)nvec * vec_bytes + kLaneSliceBytes - 1) / kLaneSliceBytes);
         while (csize <= kLaneMaxCluster && (uint64_t)((nvec + csize - 1) / csize) * vec_bytes > kLaneSliceBytes) csize++;
+        // a little longer (V = 151 936 f32 needs 74.2 KB per CTA of 8): the largest cluster with two CTAs per SM
+        if (csize > kLaneMaxCluster && (uint64_t)((nvec + kLaneMaxCluster - 1) / kLaneMaxCluster) * vec_bytes <= kLaneSliceBytesTwo) csize = kLaneMaxCluster;
         if (csize <= kLaneMaxCluster) {
             const int rc = launch_lane_cluster(a, csize, (nvec + csize - 1) / csize, vec_bytes, st);
             if (rc != NRL_E_UNSUPPORTED) return rc;

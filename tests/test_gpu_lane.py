@@ -102,6 +102,37 @@ def test_infinities_nan_and_ties(oracle):
     assert np.array_equal(ops.argmax(bt)[0].cpu().numpy().astype(np.int64), oi)
 
 
+@pytest.mark.parametrize("V,dtype", [(32000, torch.float32), (50264, torch.float32), (128256, torch.float32), (151936, torch.float32), (65536, torch.bfloat16), (128256, torch.bfloat16), (262144, torch.bfloat16)])
+def test_long_rows_held_by_a_cluster(oracle, V, dtype):
+    """softmax / log_softmax of rows too long for L2 to keep (a thread-block cluster of 2 to 8 CTAs
+    holds the row in shared memory): values against the f64 oracle, the reference's edge rows (a NaN
+    late in the row, a row of −inf, a +inf, −inf runs as long as a CTA's slice), more rows than
+    resident clusters, and the same bits run to run."""
+    from noetic_tensor_b200 import ops
+
+    g = np.random.default_rng(V)
+    rows = 70
+    x = g.normal(0, 3, (rows, V)).astype(np.float32)
+    x[0, V - 5] = NAN
+    x[1] = -INF
+    x[2, 17] = INF
+    x[3, : V // 2] = -INF          # whole slices without a finite value
+    x[4, V // 3:] = -INF
+    x[5, 1:] = -INF                 # a single finite value
+    x[6] = 1e30                     # exp(0) everywhere
+    xt, xh = put(x, dtype)
+    for f, op in ((ops.softmax, oracle.LANE_SOFTMAX), (ops.log_softmax, oracle.LANE_LOG_SOFTMAX)):
+        y = f(xt)
+        got = y.cpu().numpy()
+        close(got[:8], oracle.lane_op(op, xh[:8], dtype=oracle.F64), "edge rows")
+        idx = g.choice(np.arange(8, rows), 4, replace=False)
+        close(got[idx], oracle.lane_op(op, xh[idx], dtype=oracle.F64), "values")
+        assert np.isnan(got[0]).all() and np.isnan(got[1]).all() and np.isnan(got[2]).all()
+        assert torch.equal(f(xt).view(torch.int32), y.view(torch.int32)), "bitwise run to run"
+    s = ops.softmax(xt)[8:].double().sum(dim=1)
+    assert ((s - 1).abs() < 1e-4).all()
+
+
 def test_many_rows_and_throughput():
     """More rows than resident blocks (the grid-stride loop), checked through properties, and the
     rate of each op at the Llama-3 vocabulary printed for the record."""
