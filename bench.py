@@ -825,6 +825,22 @@ def run_ours(args):
         bits_rate = e2e_rows / ((time.perf_counter() - t0) / e2e_steps)
         bits_ok = bool((bout["tokens"] == mout["tokens"]).all())
         cmp_bits = compare_with_resident(bout, out, e2e_rows)
+        # what the host link gives every rank at once for plain copies of whole rows: the ceiling of an upload that
+        # does not use the mask, and the yardstick for the bytes the modes above move
+        scratch = torch.empty_like(hx, device=dev)
+        scratch.copy_(hx, non_blocking=True)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            scratch.copy_(hx, non_blocking=True)
+        torch.cuda.synchronize()
+        tc = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(tc, op=dist.ReduceOp.MAX)
+        copy_gbps = world * hx.numel() * hx.element_size() / float(tc.item()) / 1e9
+        del scratch
         all_cmp = {"packed": cmp_packed, "mapped": cmp_mapped, "mapped_host_bits": cmp_hostbits, "bit_packed_masks": cmp_bits}
         e2e_matches = all(c["values_outside_tolerance"] == 0 and c["tokens_differing"] <= max(1, e2e_rows // 1000) for c in all_cmp.values())
         h2d, d2h = hf.bytes_per_row()
@@ -835,6 +851,10 @@ def run_ours(args):
         e2e = {"value": modes[best][0], "unit": "rows/s", "mode": best,
                "h2d_bytes_per_step": int(modes[best][1]), "d2h_bytes_per_step": e2e_rows * d2h,
                "host_bytes_per_step": e2e_rows * h2d, "rows_per_step": e2e_rows, "host_cpus_near_gpu": (len(near) if near else None), "matches_resident_path": e2e_matches, "vs_resident_path": all_cmp,
+               "host_link": {"h2d_copy_GBps_all_ranks": copy_gbps, "whole_rows_per_s_at_that_rate": copy_gbps * 1e9 / (V * BYTES_PER_ELEM),
+                             "moved_GBps_estimate": modes[best][1] / e2e_rows * modes[best][0] / 1e9,
+                             "note": "every rank copies its pinned bf16 logits (2.1 GB) to its GPU at the same time, max over ranks: what uploading whole rows (logits + reference + mask, 5 B per "
+                                     "element) could reach at best, beside what the fastest mode moves by the estimate of h2d_bytes_per_step"},
                "h2d_bytes_note": "for the mapped modes an estimate: the mask bytes that are copied plus 16 B per live vector per stream; the link moves at least a 32-byte sector per isolated vector and has no counter here",
                "mapped": {"value": mapped_rate, "h2d_bytes_per_step_estimate": int(mapped_bytes),
                           "note": "nrl_row_fwd is given the pinned host logits and reference themselves (mapped into the device's address space) and fetches only the vectors the mask allows "
