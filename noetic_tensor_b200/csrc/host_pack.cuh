@@ -9,7 +9,7 @@
 // With a grammar mask that allows ~5 % of a 128 256-token vocabulary this is 82 KB per row over
 // the link instead of 641 KB.
 #pragma once
-#include <emmintrin.h>
+#include <immintrin.h>
 
 #include <thread>
 #include <vector>
@@ -18,40 +18,85 @@
 
 namespace nrl {
 
+// One 64-vector word of a mask row: bit j set iff the 8 mask bytes of vector v0 + j hold a non-zero byte.
+// `vn` ≤ 64 vectors exist from v0 on.
+static inline uint64_t live_word_scalar(const uint8_t* m, uint32_t vn) {
+    uint64_t bits = 0;
+    for (uint32_t j = 0; j < vn; j++) {
+        uint64_t m8;
+        memcpy(&m8, m + (uint64_t)j * kVec, 8);
+        bits |= (uint64_t)(m8 != 0) << j;
+    }
+    return bits;
+}
+// The same for a full word (512 mask bytes) with 32-byte compares, on CPUs that have AVX2 (looked up once).
+__attribute__((target("avx2"))) static inline uint64_t live_word_avx2(const uint8_t* m) {
+    const __m256i zero = _mm256_setzero_si256();
+    uint64_t zeros = 0;
+    for (int k = 0; k < 16; k++) {
+        const __m256i v = _mm256_loadu_si256((const __m256i*)(m + 32 * k));
+        zeros |= (uint64_t)(uint32_t)_mm256_movemask_pd(_mm256_castsi256_pd(_mm256_cmpeq_epi64(v, zero))) << (4 * k);
+    }
+    return ~zeros;
+}
+static bool host_has_avx2() {
+    static const bool yes = __builtin_cpu_supports("avx2");
+    return yes;
+}
+
+// Rows [r0, r1) of a chunk. First pass (`gather` false): the liveness words and the count of live vectors per row.
+// Second pass: the live vectors' logits, reference logits and mask bytes to their places in the packed arrays; the
+// row's live vectors are listed first, so that the lines of the vectors a few places ahead can be requested while
+// the current ones are copied (the reads are scattered over 2 × 256 KB per row: without the requests a thread waits
+// for one cache miss after another).
 template <int ESIZE, bool REF>
 static void pack_rows_range(const nrl_pack_args* a, uint64_t r0, uint64_t r1, uint32_t words_per_row, bool gather) {
     const uint32_t nvec = a->V / kVec;
+    const bool avx2 = host_has_avx2();
+    std::vector<uint16_t> list;  // V ≤ 262 144: vector indices fit 16 bits
+    constexpr uint32_t kAheadVectors = 24;
+    if (gather) list.resize((size_t)nvec + kAheadVectors);
     for (uint64_t r = r0; r < r1; r++) {
         const uint8_t* mrow = a->allow_mask + r * a->V;
         uint64_t* words = a->live_words + r * words_per_row;
         if (!gather) {
             uint32_t live = 0;
             for (uint32_t w = 0; w < words_per_row; w++) {
-                uint64_t bits = 0;
                 const uint32_t v0 = w * 64, vn = nvec - v0 < 64u ? nvec - v0 : 64u;
-                for (uint32_t j = 0; j < vn; j++) {
-                    uint64_t m8;
-                    memcpy(&m8, mrow + (uint64_t)(v0 + j) * kVec, 8);
-                    bits |= (uint64_t)(m8 != 0) << j;
-                }
+                const uint64_t bits = (avx2 && vn == 64u) ? live_word_avx2(mrow + (uint64_t)v0 * kVec) : live_word_scalar(mrow + (uint64_t)v0 * kVec, vn);
                 words[w] = bits;
                 live += (uint32_t)__builtin_popcountll(bits);
             }
             a->row_offset[r + 1] = live;  // counts for now; the caller turns them into offsets
         } else {
-            uint64_t idx = a->row_offset[r];
-            const char* xrow = (const char*)a->logits + r * a->V * ESIZE;
-            const char* rrow = REF ? (const char*)a->ref_logits + r * a->V * ESIZE : nullptr;
+            uint32_t n = 0;
             for (uint32_t w = 0; w < words_per_row; w++) {
                 uint64_t bits = words[w];
                 while (bits) {
-                    const uint32_t v = w * 64 + (uint32_t)__builtin_ctzll(bits);
+                    list[n++] = (uint16_t)(w * 64 + (uint32_t)__builtin_ctzll(bits));
                     bits &= bits - 1;
-                    memcpy((char*)a->packed_logits + idx * (kVec * ESIZE), xrow + (uint64_t)v * kVec * ESIZE, kVec * ESIZE);
-                    if (REF) memcpy((char*)a->packed_ref + idx * (kVec * ESIZE), rrow + (uint64_t)v * kVec * ESIZE, kVec * ESIZE);
-                    memcpy(a->packed_mask + idx, mrow + (uint64_t)v * kVec, 8);
-                    idx++;
                 }
+            }
+            for (uint32_t k = 0; k < kAheadVectors; k++) list[n + k] = n ? list[n - 1] : 0;  // requests past the end go to a line already held
+            const char* xrow = (const char*)a->logits + r * a->V * ESIZE;
+            const char* rrow = REF ? (const char*)a->ref_logits + r * a->V * ESIZE : nullptr;
+            char* px = (char*)a->packed_logits + (uint64_t)a->row_offset[r] * (kVec * ESIZE);
+            char* pr = REF ? (char*)a->packed_ref + (uint64_t)a->row_offset[r] * (kVec * ESIZE) : nullptr;
+            uint64_t* pm = a->packed_mask + a->row_offset[r];
+            for (uint32_t k = 0; k < n; k++) {
+                const uint64_t ahead = list[k + kAheadVectors], v = list[k];
+                _mm_prefetch(xrow + ahead * (kVec * ESIZE), _MM_HINT_T0);
+                if (REF) _mm_prefetch(rrow + ahead * (kVec * ESIZE), _MM_HINT_T0);
+                _mm_prefetch((const char*)mrow + ahead * kVec, _MM_HINT_T0);
+                if (ESIZE == 4) {
+                    _mm_prefetch(xrow + ahead * (kVec * ESIZE) + 16, _MM_HINT_T0);  // a 32-byte vector can straddle two lines
+                    if (REF) _mm_prefetch(rrow + ahead * (kVec * ESIZE) + 16, _MM_HINT_T0);
+                }
+                for (int q = 0; q < kVec * ESIZE / 16; q++) {
+                    _mm_storeu_si128((__m128i*)(px + (uint64_t)k * (kVec * ESIZE)) + q, _mm_loadu_si128((const __m128i*)(xrow + v * (kVec * ESIZE)) + q));
+                    if (REF) _mm_storeu_si128((__m128i*)(pr + (uint64_t)k * (kVec * ESIZE)) + q, _mm_loadu_si128((const __m128i*)(rrow + v * (kVec * ESIZE)) + q));
+                }
+                memcpy(pm + k, mrow + v * kVec, 8);
             }
         }
     }
