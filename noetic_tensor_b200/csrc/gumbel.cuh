@@ -8,7 +8,7 @@
 //   token = first maximum of  z_v + g_v  in f32, z = logits / τ + mask   (src/nn/rl.rs:510-529)
 //
 // The kernel is bound by integer and f64 arithmetic (one ChaCha20 block and sixteen f64
-// logarithms per eight logits), not by memory.
+// logarithms per eight logits that can win), not by memory; vectors a byte mask excludes are skipped.
 #pragma once
 #include "row_fwd.cuh"
 
@@ -61,6 +61,7 @@ template <int DT, bool ALLOW, bool VEC>
 __global__ void __launch_bounds__(kGumbelThreads) gumbel_argmax_kernel(GumbelParams p) {
     __shared__ float s_best[kGumbelThreads / 32], s_top[kGumbelThreads / 32];
     __shared__ uint32_t s_idx[kGumbelThreads / 32];
+    __shared__ uint32_t s_list[ALLOW && VEC ? kGumbelThreads / 32 : 1][ALLOW && VEC ? 16 * 32 : 1];  // a warp's live vectors of one round
     const FwdParams& f = p.in;
     const uint64_t row = blockIdx.x;
     const uint32_t V = f.V;
@@ -68,7 +69,7 @@ __global__ void __launch_bounds__(kGumbelThreads) gumbel_argmax_kernel(GumbelPar
     float best = NRL_NEG_INF, top = NRL_NEG_INF;  // best noisy value; maximum of the noise-free logits (NaN-propagating)
     uint32_t bidx = 0xffffffffu;
     VecLoader<DT, false, ALLOW, true, VEC> ld;
-    for (uint32_t v = threadIdx.x * kVec; v < V; v += kGumbelThreads * kVec) {
+    auto fold = [&](uint32_t v) {
         ld.load(f, row, v, V);
         float z[8], zr[8];
         ld.values(f, z, zr);
@@ -78,10 +79,10 @@ __global__ void __launch_bounds__(kGumbelThreads) gumbel_argmax_kernel(GumbelPar
         auto consider = [&](int i, uint32_t lo, uint32_t hi) {
             if (v + i < V) {
                 float x = z[i];
-                if (ALLOW && x == -FLT_MAX) x = NRL_NEG_INF;  // a token the byte mask excludes
+                if (ALLOW && x == -FLT_MAX) return;  // a token the byte mask excludes: −inf plus any noise never wins
                 top = fmax_nan(top, x);
                 const float y = x + gumbel_noise(lo, hi);
-                if (y > best) {  // strictly: the first maximum stays
+                if (y > best || (y == best && v + (uint32_t)i < bidx)) {  // the first maximum stays
                     best = y;
                     bidx = v + i;
                 }
@@ -99,6 +100,47 @@ __global__ void __launch_bounds__(kGumbelThreads) gumbel_argmax_kernel(GumbelPar
 #pragma unroll
             for (int i = 0; i < 8; i++) consider(i, ks[off + 2 * i], ks[off + 2 * i + 1]);
         }
+    };
+    if constexpr (ALLOW && VEC) {
+        // A vector the byte mask excludes cannot win and cannot raise `top`: its keystream block and its sixteen
+        // logarithms are not computed. Round by round a warp collects the liveness of its next 16 × 32 vectors
+        // (independent 8-byte mask loads), lists the live ones in shared memory and deals them out to its lanes one by
+        // one: every lane has a live vector at the arithmetic, instead of one or two lanes per step having work
+        // (grammar masks allow a few per cent of the vocabulary) or lanes with few live vectors waiting for lanes with
+        // many. A lane no longer sees its vectors in index order; ties are decided by the index.
+        const uint8_t* mrow = f.allow + row * f.allow_stride;
+        constexpr uint32_t kStride = kGumbelThreads * kVec, kRound = 16;
+        uint32_t* list = s_list[warp];
+        for (uint32_t base0 = (uint32_t)warp * 32u * kVec; base0 < V; base0 += kRound * kStride) {  // warp-uniform
+            const uint32_t base = base0 + (uint32_t)lane * kVec;
+            uint32_t live = 0;
+#pragma unroll
+            for (uint32_t k = 0; k < kRound; k++) {
+                const uint32_t v = base + k * kStride;
+                if (v < V) {
+                    const uint2 q = ldg_mask8(mrow, v);
+                    live |= (uint32_t)((q.x | q.y) != 0u) << k;
+                }
+            }
+            uint32_t incl = (uint32_t)__popc(live);
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t o = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += o;
+            }
+            const uint32_t total = __shfl_sync(0xffffffffu, incl, 31);
+            uint32_t pos = incl - (uint32_t)__popc(live);
+            while (live) {
+                const uint32_t k = (uint32_t)__ffs((int)live) - 1u;
+                live &= live - 1u;
+                list[pos++] = base + k * kStride;
+            }
+            __syncwarp();
+            for (uint32_t e = (uint32_t)lane; e < total; e += 32u) fold(list[e]);
+            __syncwarp();  // the list is read before the next round rewrites it
+        }
+    } else {
+        for (uint32_t v = threadIdx.x * kVec; v < V; v += kGumbelThreads * kVec) fold(v);
     }
     // the block's first maximum: larger value, then smaller index
 #pragma unroll
