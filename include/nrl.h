@@ -437,7 +437,11 @@ int nrl_unpack_rows(const nrl_unpack_args* args, nrl_stream stream);
  * x is F32 or BF16 for the forward ops and for NRL_LANE_LOGSUMEXP_BWD, F32 for the other two
  * backward ops. Outputs are F32. A row of −inf alone, or one holding NaN, gives NaN from softmax and
  * log_softmax as in the reference. `out` must not alias an input. Rows take 16-byte loads when V
- * is a multiple of 8 and x, g, out are 16-byte aligned; other shapes run an element-wise loop. */
+ * is a multiple of 8 and x, g, out are 16-byte aligned; other shapes run an element-wise loop.
+ * softmax / log_softmax of such rows longer than 42 KB (and up to 896 KB) run on thread-block
+ * clusters that hold a row in shared memory and read it from HBM once; the CTAs of a cluster wait
+ * for each other's partial sums at most two seconds, after which the CTA writes NaN rows (an internal
+ * error: it cannot happen unless a CTA of the cluster has faulted). Results do not depend on timing. */
 enum {
     NRL_LANE_SOFTMAX = 0, NRL_LANE_LOG_SOFTMAX = 1, NRL_LANE_LOGSUMEXP = 2, NRL_LANE_ARGMAX = 3, NRL_LANE_SUM = 4,
     NRL_LANE_SOFTMAX_BWD = 5, NRL_LANE_LOG_SOFTMAX_BWD = 6, NRL_LANE_LOGSUMEXP_BWD = 7
