@@ -13,9 +13,14 @@ bytes of the live vectors (nrl_host_pack), and a kernel puts them back in place 
 `run_mapped` needs no staging at all: pinned host memory is mapped into the device's address
 space, so the masked forward streams the mask from it in place and fetches only the vectors the
 mask allows, each once, over the host link; no host thread touches the rows.
+
+`run_hybrid` does both at once on two shares of the rows: the mapped path is bound by the number
+of small reads the link keeps in flight, the packed path by the host's cores and memory, so the
+two add up to more than either.
 """
 import ctypes as C
 import os
+import threading
 
 import torch
 
@@ -300,4 +305,54 @@ class HostForward:
             done.append(f)
         self.back_stream.synchronize()
         compute.synchronize()
+        return out
+
+    def run_hybrid(self, logits, uniforms, ref=None, mask=None, out=None, packed_share=0.375, mapped_chunk_rows=1184, packed_threads=None):
+        """The rows split in two: the first share through `run_mapped` (the kernel fetches the live
+        vectors over the link; host threads turn the byte mask into bits), the last `packed_share`
+        through `run` (host threads pack the live vectors, copies move them) on a second Python
+        thread and a second CUDA stream, at the same time. Same results as either (every row is
+        computed by the same kernels on the same values). `packed_threads` of this object's host
+        threads (half of them by default) go to the packing, the rest to the bit masks. Measured on
+        a B200 host with 16 cores: 3/8 of the rows packed by 8 threads gave the most."""
+        if not (self.has_mask and self.packed) or mask is None:
+            return self.run_mapped(logits, uniforms, ref=ref, mask=mask, out=out)
+        rows = logits.shape[0]
+        n_packed = int(rows * packed_share) // self.chunk * self.chunk
+        n_mapped = rows - n_packed
+        if n_packed == 0 or n_mapped == 0:
+            return self.run_mapped(logits, uniforms, ref=ref, mask=mask, out=out, chunk_rows=mapped_chunk_rows, first_chunk_rows=min(512, mapped_chunk_rows), pack_bits_on_host=True)
+        if out is None:
+            pin = lambda dt: torch.empty(rows, dtype=dt).pin_memory()
+            out = dict(tokens=pin(torch.int32), logp=pin(torch.float32), kl=pin(torch.float32), entropy=pin(torch.float32), status=pin(torch.uint8))
+        pt = int(packed_threads or max(1, self.threads // 2))
+        twin = getattr(self, "_twin", None)
+        if twin is None or twin.threads != pt:
+            twin = self._twin = HostForward(self.V, self.dtype, chunk_rows=self.chunk, ref=self.has_ref, mask=True, device=self.dev, packed=True, threads=pt)
+            self._twin_stream = torch.cuda.Stream(self.dev)
+        a, b = slice(0, n_mapped), slice(n_mapped, rows)
+        part = lambda t, s: None if t is None else t[s]
+        failure = []
+
+        def packed_side():
+            try:
+                torch.cuda.set_device(self.dev)
+                with torch.cuda.stream(self._twin_stream):
+                    twin.run(logits[b], uniforms[b], ref=part(ref, b), mask=mask[b], out={k: v[b] for k, v in out.items()})
+            except BaseException as e:  # handed to the caller below
+                failure.append(e)
+
+        worker = threading.Thread(target=packed_side)
+        worker.start()
+        keep = self.threads
+        self.threads = max(1, keep - pt)
+        try:
+            self.run_mapped(logits[a], uniforms[a], ref=part(ref, a), mask=mask[a], out={k: v[a] for k, v in out.items()}, chunk_rows=mapped_chunk_rows,
+                            first_chunk_rows=min(512, mapped_chunk_rows), pack_bits_on_host=True)
+        finally:
+            self.threads = keep
+            worker.join()
+        if failure:
+            raise failure[0]
+        self.h2d_bytes, self.live_vectors = twin.h2d_bytes, twin.live_vectors
         return out

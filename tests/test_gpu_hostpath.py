@@ -175,6 +175,42 @@ def test_mapped_host_rows_equal_the_resident_forward(dtype, ref, rows):
         ops.row_forward(x.cpu(), allow=pin(m), uniforms=u, device=dev)
 
 
+def test_hybrid_host_path_is_its_two_halves():
+    """run_hybrid: a share of the rows through the mapped path and the rest through the packed
+    path at the same time, on two threads and two streams: the bits of the two paths run one after
+    the other on the same shares, and the resident forward's values."""
+    from noetic_tensor_b200 import ops, synth
+    from noetic_tensor_b200.hostpath import HostForward
+
+    dev = torch.device("cuda:0")
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(21)
+    V, rows, chunk = 128256, 1400, 128
+    x = synth.normal_logits(rows, V, 3.0, torch.bfloat16, gen, dev)
+    r = synth.perturbed(x, 0.05, gen)
+    m = synth.grammar_masks(rows, V, gen, dev)
+    u = synth.uniforms(rows, gen, dev)
+    pin = lambda t: t.cpu().pin_memory()
+    hx, hu, hr, hm = pin(x), pin(u), pin(r), pin(m)
+    hf = HostForward(V, torch.bfloat16, chunk_rows=chunk, device=dev, threads=4)
+    got = hf.run_hybrid(hx, hu, ref=hr, mask=hm, packed_share=0.4, mapped_chunk_rows=300, packed_threads=2)
+    n_packed = int(rows * 0.4) // chunk * chunk
+    n_mapped = rows - n_packed
+    first = hf.run_mapped(hx[:n_mapped], hu[:n_mapped], ref=hr[:n_mapped], mask=hm[:n_mapped], chunk_rows=300, first_chunk_rows=300, pack_bits_on_host=True)
+    second = HostForward(V, torch.bfloat16, chunk_rows=chunk, device=dev, threads=2).run(hx[n_mapped:], hu[n_mapped:], ref=hr[n_mapped:], mask=hm[n_mapped:])
+    for name in ("tokens", "logp", "kl", "entropy", "status"):
+        assert torch.equal(_bits(got[name][:n_mapped]), _bits(first[name])), ("mapped share", name)
+        assert torch.equal(_bits(got[name][n_mapped:]), _bits(second[name])), ("packed share", name)
+    want = ops.row_forward(x, ref_logits=r, allow=m, uniforms=u)
+    assert int((got["tokens"] != want.tokens.cpu()).sum()) <= 2
+    same = got["tokens"] == want.tokens.cpu()
+    assert torch.allclose(got["logp"][same], want.logp.cpu()[same], rtol=1e-5, atol=1e-6) and torch.allclose(got["entropy"], want.entropy.cpu(), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(got["kl"], want.kl.cpu(), rtol=1e-5, atol=1e-6)
+    again = hf.run_hybrid(hx, hu, ref=hr, mask=hm, packed_share=0.4, mapped_chunk_rows=300, packed_threads=2)
+    for name in ("tokens", "logp", "kl", "entropy"):
+        assert torch.equal(_bits(again[name]), _bits(got[name])), ("run to run", name)
+
+
 @pytest.mark.parametrize("V", [1, 7, 8, 31, 32, 33, 100, 4104, 128256])
 def test_expand_bitmask(V):
     from noetic_tensor_b200 import ops
