@@ -11,12 +11,86 @@
 #pragma once
 #include <immintrin.h>
 
+#include <condition_variable>
+#include <functional>
+#include <mutex>
 #include <thread>
 #include <vector>
 
 #include "common.cuh"
 
 namespace nrl {
+
+// Host threads that stay: the packers below run twice per chunk of a few hundred rows, and starting and joining
+// sixteen threads each time cost a fifth of a chunk. One pool per calling thread (thread_local: callers on different
+// threads pack at the same time without sharing anything); its workers sleep on a condition variable between runs
+// and are joined when the calling thread ends.
+class HostPool {
+  public:
+    ~HostPool() {
+        {
+            std::lock_guard<std::mutex> hold(m_);
+            stop_ = true;
+            gen_++;
+        }
+        start_.notify_all();
+        for (auto& t : workers_) t.join();
+    }
+    // fn(t) for t in [0, nt): t = 0 on the calling thread, the rest on workers; returns when all are done
+    void run(uint32_t nt, const std::function<void(uint32_t)>& fn) {
+        if (nt <= 1) {
+            fn(0);
+            return;
+        }
+        {
+            std::lock_guard<std::mutex> hold(m_);
+            while (workers_.size() < nt - 1) {
+                const uint32_t id = (uint32_t)workers_.size() + 1;
+                const uint64_t before = gen_;  // a worker that starts late still sees this run as new
+                workers_.emplace_back([this, id, before] { work(id, before); });
+            }
+            fn_ = &fn;
+            active_ = nt;
+            pending_ = nt - 1;
+            gen_++;
+        }
+        start_.notify_all();
+        fn(0);
+        std::unique_lock<std::mutex> hold(m_);
+        done_.wait(hold, [this] { return pending_ == 0; });
+        fn_ = nullptr;
+    }
+
+  private:
+    void work(uint32_t id, uint64_t seen) {
+        for (;;) {
+            const std::function<void(uint32_t)>* fn = nullptr;
+            {
+                std::unique_lock<std::mutex> hold(m_);
+                start_.wait(hold, [&] { return gen_ != seen; });
+                seen = gen_;
+                if (stop_) return;
+                if (id < active_) fn = fn_;
+            }
+            if (fn) {
+                (*fn)(id);
+                std::lock_guard<std::mutex> hold(m_);
+                if (--pending_ == 0) done_.notify_one();
+            }
+        }
+    }
+    std::mutex m_;
+    std::condition_variable start_, done_;
+    std::vector<std::thread> workers_;
+    const std::function<void(uint32_t)>* fn_ = nullptr;
+    uint64_t gen_ = 0;
+    uint32_t active_ = 0, pending_ = 0;
+    bool stop_ = false;
+};
+static HostPool& host_pool() {
+    static thread_local HostPool pool;
+    return pool;
+}
 
 // One 64-vector word of a mask row: bit j set iff the 8 mask bytes of vector v0 + j hold a non-zero byte.
 // `vn` ≤ 64 vectors exist from v0 on.
@@ -106,15 +180,12 @@ template <int ESIZE, bool REF>
 static int host_pack_impl(nrl_pack_args* a) {
     const uint32_t nvec = a->V / kVec, words_per_row = (nvec + 63) / 64;
     const uint32_t nt = a->threads < 1 ? 1 : (a->threads > 256 ? 256 : a->threads);
+    const uint64_t per = (a->rows + nt - 1) / nt;
     auto run = [&](bool gather) {
-        std::vector<std::thread> th;
-        const uint64_t per = (a->rows + nt - 1) / nt;
-        for (uint32_t t = 1; t < nt; t++) {
+        host_pool().run(nt, [&](uint32_t t) {
             const uint64_t r0 = t * per < a->rows ? t * per : a->rows, r1 = (t + 1) * per < a->rows ? (t + 1) * per : a->rows;
-            if (r0 < r1) th.emplace_back([=] { pack_rows_range<ESIZE, REF>(a, r0, r1, words_per_row, gather); });
-        }
-        pack_rows_range<ESIZE, REF>(a, 0, per < a->rows ? per : a->rows, words_per_row, gather);
-        for (auto& x : th) x.join();
+            if (r0 < r1) pack_rows_range<ESIZE, REF>(a, r0, r1, words_per_row, gather);
+        });
     };
     run(false);
     a->row_offset[0] = 0;
@@ -157,14 +228,11 @@ static void pack_bits_range(const uint8_t* mask, uint32_t* bits, uint64_t r0, ui
 static int host_pack_bits_impl(uint64_t rows, uint32_t V, const uint8_t* mask, uint32_t* bits, uint32_t threads) {
     const uint32_t words = (V + 31) / 32;
     const uint32_t nt = threads < 1 ? 1 : (threads > 256 ? 256 : threads);
-    std::vector<std::thread> th;
     const uint64_t per = (rows + nt - 1) / nt;
-    for (uint32_t t = 1; t < nt; t++) {
+    host_pool().run(nt, [&](uint32_t t) {
         const uint64_t r0 = t * per < rows ? t * per : rows, r1 = (t + 1) * per < rows ? (t + 1) * per : rows;
-        if (r0 < r1) th.emplace_back([=] { pack_bits_range(mask, bits, r0, r1, V, words); });
-    }
-    pack_bits_range(mask, bits, 0, per < rows ? per : rows, V, words);
-    for (auto& x : th) x.join();
+        if (r0 < r1) pack_bits_range(mask, bits, r0, r1, V, words);
+    });
     return NRL_OK;
 }
 
