@@ -11,6 +11,8 @@
 #pragma once
 #include <immintrin.h>
 
+#include <unistd.h>
+
 #include <condition_variable>
 #include <functional>
 #include <mutex>
@@ -28,13 +30,15 @@ namespace nrl {
 class HostPool {
   public:
     ~HostPool() {
+        if (getpid() != pid_) return;  // a forked child inherits the object but not the threads: nothing to join
         {
-            std::lock_guard<std::mutex> hold(m_);
-            stop_ = true;
-            gen_++;
+            std::lock_guard<std::mutex> hold(s_->m);
+            s_->stop = true;
+            s_->gen++;
         }
-        start_.notify_all();
-        for (auto& t : workers_) t.join();
+        s_->start.notify_all();
+        for (auto& t : s_->workers) t.join();
+        delete s_;
     }
     // fn(t) for t in [0, nt): t = 0 on the calling thread, the rest on workers; returns when all are done
     void run(uint32_t nt, const std::function<void(uint32_t)>& fn) {
@@ -42,50 +46,59 @@ class HostPool {
             fn(0);
             return;
         }
-        {
-            std::lock_guard<std::mutex> hold(m_);
-            while (workers_.size() < nt - 1) {
-                const uint32_t id = (uint32_t)workers_.size() + 1;
-                const uint64_t before = gen_;  // a worker that starts late still sees this run as new
-                workers_.emplace_back([this, id, before] { work(id, before); });
-            }
-            fn_ = &fn;
-            active_ = nt;
-            pending_ = nt - 1;
-            gen_++;
+        if (getpid() != pid_) {  // after a fork the parent's workers do not exist here, and its mutex and condition
+            s_ = new State();    // variables remember waiters that are not there: start afresh, leave the old state alone
+            pid_ = getpid();
         }
-        start_.notify_all();
+        State* s = s_;
+        {
+            std::lock_guard<std::mutex> hold(s->m);
+            while (s->workers.size() < nt - 1) {
+                const uint32_t id = (uint32_t)s->workers.size() + 1;
+                const uint64_t before = s->gen;  // a worker that starts late still sees this run as new
+                s->workers.emplace_back([s, id, before] { work(s, id, before); });
+            }
+            s->fn = &fn;
+            s->active = nt;
+            s->pending = nt - 1;
+            s->gen++;
+        }
+        s->start.notify_all();
         fn(0);
-        std::unique_lock<std::mutex> hold(m_);
-        done_.wait(hold, [this] { return pending_ == 0; });
-        fn_ = nullptr;
+        std::unique_lock<std::mutex> hold(s->m);
+        s->done.wait(hold, [s] { return s->pending == 0; });
+        s->fn = nullptr;
     }
 
   private:
-    void work(uint32_t id, uint64_t seen) {
+    struct State {
+        std::mutex m;
+        std::condition_variable start, done;
+        std::vector<std::thread> workers;
+        const std::function<void(uint32_t)>* fn = nullptr;
+        uint64_t gen = 0;
+        uint32_t active = 0, pending = 0;
+        bool stop = false;
+    };
+    static void work(State* s, uint32_t id, uint64_t seen) {
         for (;;) {
             const std::function<void(uint32_t)>* fn = nullptr;
             {
-                std::unique_lock<std::mutex> hold(m_);
-                start_.wait(hold, [&] { return gen_ != seen; });
-                seen = gen_;
-                if (stop_) return;
-                if (id < active_) fn = fn_;
+                std::unique_lock<std::mutex> hold(s->m);
+                s->start.wait(hold, [&] { return s->gen != seen; });
+                seen = s->gen;
+                if (s->stop) return;
+                if (id < s->active) fn = s->fn;
             }
             if (fn) {
                 (*fn)(id);
-                std::lock_guard<std::mutex> hold(m_);
-                if (--pending_ == 0) done_.notify_one();
+                std::lock_guard<std::mutex> hold(s->m);
+                if (--s->pending == 0) s->done.notify_one();
             }
         }
     }
-    std::mutex m_;
-    std::condition_variable start_, done_;
-    std::vector<std::thread> workers_;
-    const std::function<void(uint32_t)>* fn_ = nullptr;
-    uint64_t gen_ = 0;
-    uint32_t active_ = 0, pending_ = 0;
-    bool stop_ = false;
+    State* s_ = new State();
+    pid_t pid_ = getpid();
 };
 static HostPool& host_pool() {
     static thread_local HostPool pool;

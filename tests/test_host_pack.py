@@ -76,3 +76,32 @@ def test_pack_bits_on_the_host(V):
         rc = capi.lib().nrl_host_pack_bits(rows, V, m.ctypes.data_as(C.c_void_p), bits.ctypes.data_as(C.c_void_p), threads)
         assert rc == 0 and np.array_equal(bits, want)
     assert capi.lib().nrl_host_pack_bits(0, V, None, None, 1) == capi.E_BAD_ARG
+
+
+def test_pack_after_fork():
+    """The packers keep worker threads between calls. A forked child inherits the pool object but
+    not its threads: it must start its own and leave cleanly, and the parent's must go on working."""
+    import os
+    import subprocess
+    import sys
+
+    here = os.path.dirname(os.path.abspath(__file__))
+    script = r"""
+import os, sys
+import numpy as np
+sys.path.insert(0, %r); sys.path.insert(0, %r)
+from test_host_pack import pack
+g = np.random.default_rng(0); rows, V = 64, 4104
+x = g.integers(0, 60000, (rows, V)).astype(np.uint16); m = (g.uniform(0, 1, (rows, V)) < 0.05).astype(np.uint8)
+live = int(m.reshape(rows, V // 8, 8).any(axis=2).sum())
+assert pack(x, None, m, 4, live + 1)[1] == live
+pid = os.fork()
+if pid == 0:
+    os._exit(0 if pack(x, None, m, 4, live + 1)[1] == live else 1)
+_, st = os.waitpid(pid, 0)
+assert os.WIFEXITED(st) and os.WEXITSTATUS(st) == 0, st
+assert pack(x, None, m, 4, live + 1)[1] == live
+print("ok")
+""" % (here, os.path.dirname(here))
+    r = subprocess.run([sys.executable, "-W", "ignore", "-c", script], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
