@@ -578,6 +578,58 @@ inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, c
     return logp;
 }
 
+// `sample_categorical(head(x), 1.0, mask, ·)` by inverse CDF against one uniform per position without
+// the [.., V] logits in between (src/nn/decoder.rs:270-279 followed by src/nn/rl.rs:490-529 with the
+// path's sampler): `hidden` BF16 [.., d], `weight` BF16 [d, V], `uniforms` F32 [..] in [0, 1),
+// `vocab_mask` an optional U8 allow-mask [.., V] or [1, V]. Returns the tokens (on the host, as
+// sample_categorical does) and, if asked, their log-probabilities and the per-position entropies.
+// Refuses a position with no allowed token with the reference's message (src/nn/rl.rs:516-519).
+inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& weight, const Tensor& uniforms, const Tensor* vocab_mask = nullptr, Tensor* logp = nullptr,
+                                         Tensor* entropy = nullptr) {
+    if (hidden.dtype() != DType::BF16 || weight.dtype() != DType::BF16) throw std::runtime_error("head_sample_categorical: BF16 hidden states and weight");
+    if (hidden.rank() < 1 || weight.rank() != 2 || weight.shape()[0] != hidden.shape().back()) throw std::runtime_error("head_sample_categorical: hidden [.., d], weight [d, V]");
+    const Shape lead(hidden.shape().begin(), hidden.shape().end() - 1);
+    const uint64_t d = weight.shape()[0], V = weight.shape()[1], rows = numel(lead);
+    if (uniforms.dtype() != DType::F32 || numel(uniforms.shape()) != rows) throw std::runtime_error("sample_categorical: one uniform per position");
+    nrl_readout_args a;
+    std::memset(&a, 0, sizeof a);
+    a.struct_size = sizeof a;
+    a.flags = NRL_READOUT_SAMPLE;
+    if (vocab_mask) {
+        if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("head_sample_categorical: a U8 allow-mask");
+        const uint64_t n = numel(vocab_mask->shape());
+        if (n != V && n != rows * V) throw std::runtime_error("rl: mask shape");
+        a.allow_mask = vocab_mask->dev();
+        a.allow_row_stride = n == V ? 0 : V;
+    }
+    Tensor tok = Tensor::empty(Shape{(size_t)rows}, DType::I32, hidden.device());
+    Tensor lp = Tensor::empty(lead, DType::F32, hidden.device());
+    Tensor status = Tensor::empty(Shape{(size_t)rows}, DType::U8, hidden.device());
+    const uint64_t need = nrl_readout_workspace_bytes(rows, (uint32_t)V, (uint32_t)d, a.flags);
+    Tensor ws = Tensor::empty(Shape{(size_t)need}, DType::U8, hidden.device());
+    a.V = (uint32_t)V; a.d = (uint32_t)d; a.rows = rows;
+    a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev(); a.uniforms = uniforms.dev();
+    a.logp = lp.dev(); a.status = status.dev();
+    if (entropy) {
+        *entropy = Tensor::empty(lead, DType::F32, hidden.device());
+        a.entropy = entropy->dev();
+    }
+    a.workspace = ws.dev(); a.workspace_bytes = need;
+    nrl(nrl_readout_fwd(&a, detail::stream()), "readout_fwd");
+    uint64_t bad = 0;
+    uint32_t bits = 0;
+    const int rc = nrl_check_status(status.dev(), rows, detail::stream(), &bad, &bits);  // a host read: the stream has drained
+    if (rc == NRL_E_ROW_STATUS) throw std::runtime_error("sample_categorical: position " + std::to_string(bad) + " has no allowed token (every logit −∞ or a NaN)");
+    nrl(rc, "check_status");
+    std::vector<int32_t> h(rows);
+    cu(cudaMemcpy(h.data(), tok.ptr(), h.size() * 4, cudaMemcpyDeviceToHost), "download tokens");
+    if (logp) *logp = lp;
+    IntTensor out;
+    out.data.assign(h.begin(), h.end());
+    out.shape = lead;
+    return out;
+}
+
 // src/nn/rl.rs:204-211: every scored log-probability (mask != 0; no mask: all) is finite. Returns
 // an empty string, or the reference's error text naming the first flat position. A host read.
 inline std::string check_scored_finite(const std::string& what, const Tensor& logp, const Tensor* mask) {

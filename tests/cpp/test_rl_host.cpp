@@ -563,6 +563,68 @@ static void test_head_token_log_probs() {
     CHECK(throws([&] { rl::head_token_log_probs(Tensor::from_f32(x, {S, B, T, d}, dev), hw, it); }, "BF16"), "f32 hidden states are refused");
 }
 
+// ---- Decoder::head fused with sample_categorical (inverse CDF), masks included ------------------------------
+static void test_head_sample_categorical() {
+    cudaDeviceProp prop;
+    cudaGetDeviceProperties(&prop, 0);
+    if (prop.major != 10) {
+        std::printf("    (skipped: needs compute capability 10.x, this device is %d.%d)\n", prop.major, prop.minor);
+        return;
+    }
+    const size_t S = 2, B = 2, T = 40, d = 64, V = 512, rows = S * B * T;
+    std::mt19937 gen(11);
+    std::normal_distribution<float> nd(0.f, 1.f);
+    std::uniform_real_distribution<float> ud(0.f, 1.f);
+    std::vector<float> x(rows * d), w(d * V), u(rows);
+    for (auto& v : x) v = through_bf16(nd(gen));
+    for (auto& v : w) v = through_bf16(nd(gen) * 0.35f);
+    for (auto& v : u) v = std::min(ud(gen), 0.99999994f);
+    std::vector<uint8_t> mask(rows * V);
+    for (size_t i = 0; i < mask.size(); i++) mask[i] = (gen() % 4) == 0;
+    for (size_t r = 0; r < rows; r++) mask[r * V + 5] = 1;
+    Tensor hx = Tensor::from_f32(x, {S, B, T, d}, dev, DType::BF16), hw = Tensor::from_f32(w, {d, V}, dev, DType::BF16);
+    Tensor hu = Tensor::from_f32(u, {S, B, T}, dev), hm = Tensor::from_u8(mask, {S, B, T, V}, dev);
+    Tensor lpt, ent;
+    const IntTensor tok = rl::head_sample_categorical(hx, hw, hu, &hm, &lpt, &ent);
+    const std::vector<float> lp = lpt.to_vec(), en = ent.to_vec();
+    CHECK(tok.shape == (Shape{S, B, T}), "token shape");
+    // f64 on the host: masked logits, the inverse CDF's interval of the drawn token must hold u (up to the f32 spread of a logit)
+    size_t outside = 0;
+    std::vector<double> want_lp(rows), want_en(rows);
+    for (size_t r = 0; r < rows; r++) {
+        std::vector<double> z(V, 0.0);
+        for (size_t k = 0; k < d; k++)
+            for (size_t v = 0; v < V; v++) z[v] += (double)x[r * d + k] * (double)w[k * V + v];
+        double m = -1e300;
+        for (size_t v = 0; v < V; v++)
+            if (mask[r * V + v]) m = std::max(m, z[v]);
+        double Z = 0.0;
+        for (size_t v = 0; v < V; v++)
+            if (mask[r * V + v]) Z += std::exp(z[v] - m);
+        const double lse = m + std::log(Z);
+        double h = 0.0, lo = 0.0;
+        const int64_t t = tok.data[r];
+        CHECK(t >= 0 && (size_t)t < V && mask[r * V + t], "row %zu: token %lld is not an allowed one", r, (long long)t);
+        for (size_t v = 0; v < V; v++) {
+            if (!mask[r * V + v]) continue;
+            const double pv = std::exp(z[v] - lse);
+            h -= pv * (z[v] - lse);
+            if ((int64_t)v < t) lo += pv;
+        }
+        const double hi = lo + std::exp(z[t] - lse);
+        if (!((double)u[r] >= lo - 1e-4 && (double)u[r] <= hi + 1e-4)) outside++;
+        want_lp[r] = z[t] - lse;
+        want_en[r] = h;
+    }
+    CHECK(outside == 0, "%zu drawn tokens whose CDF interval does not hold the uniform", outside);
+    close_all(lp, want_lp, 1e-4, "head_sample_categorical log-probs");
+    close_all(en, want_en, 2e-5, "head_sample_categorical entropy");
+    std::vector<uint8_t> none(mask);
+    for (size_t v = 0; v < V; v++) none[7 * V + v] = 0;
+    Tensor hn = Tensor::from_u8(none, {S, B, T, V}, dev);
+    CHECK(throws([&] { rl::head_sample_categorical(hx, hw, hu, &hn); }, "position 7 has no allowed token"), "a position with nothing allowed is refused by name");
+}
+
 // ---- check_scored_finite (src/nn/tests/rl.rs:837-855) -------------------------------------------
 static void test_check_scored_finite() {
     const float ninf = -std::numeric_limits<float>::infinity();
@@ -796,7 +858,7 @@ int main() {
         {"clipped_policy_loss", test_clipped_policy_loss}, {"categorical_kl / entropy / reference_kl", test_kl_entropy},
         {"kl_estimate", test_kl_estimate}, {"sample_categorical", test_sample_categorical},
         {"sample_categorical (reference noise)", test_sample_categorical_reference},
-        {"group_advantages", test_group_advantages}, {"check_scored_finite", test_check_scored_finite}, {"head + token_log_probs (readout-fused)", test_head_token_log_probs}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
+        {"group_advantages", test_group_advantages}, {"check_scored_finite", test_check_scored_finite}, {"head + token_log_probs (readout-fused)", test_head_token_log_probs}, {"head + sample_categorical (readout-fused)", test_head_sample_categorical}, {"lane operations", test_lane_ops}, {"bit-packed masks", test_bit_masks}, {"ppo step", test_ppo_step},
         {"nn::loss cross-entropy family", test_loss_family},
     };
     for (auto& t : tests) {
