@@ -429,13 +429,11 @@ extern "C" int nrl_lane_op(const nrl_lane_args* a, nrl_stream stream) {
     const bool vec = a->V % kVec == 0 && aligned16(a->x) && aligned16(a->out) && (!bwd_y || aligned16(a->g));
     // The backward rules read two [rows, V] inputs twice: when the rows that 8 blocks of 256 threads
     // per SM would hold in flight outgrow L2, one block of 1024 threads per SM runs instead
-    // (measured: +8 % there; the forward softmax is faster with the many small blocks).
+    // (measured: +8 % there). The forward softmax of such rows runs on clusters (below); on this
+    // kernel it is faster with the many small blocks.
     const uint64_t row_bytes = (uint64_t)a->V * esize * 2;
-#ifndef NRL_SOFTMAX_WIDE
-#define NRL_SOFTMAX_WIDE 0
-#endif
     const bool fwd_full = a->op == NRL_LANE_SOFTMAX || a->op == NRL_LANE_LOG_SOFTMAX;
-    const bool wide = (bwd_y || (NRL_SOFTMAX_WIDE && fwd_full)) && row_bytes * 1184ull > (96ull << 20);
+    const bool wide = bwd_y && row_bytes * 1184ull > (96ull << 20);
     const unsigned threads = wide ? kLaneMaxThreads : kLaneThreads;
     const uint64_t cap = wide ? 148ull : 148ull * 8ull;
     const unsigned grid = (unsigned)(a->rows < cap ? a->rows : cap);
