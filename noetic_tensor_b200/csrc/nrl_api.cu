@@ -659,13 +659,14 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream);
 extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
-    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA | NRL_READOUT_SAMPLE)) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA | NRL_READOUT_SAMPLE | NRL_READOUT_GREEDY)) return NRL_E_BAD_ARG;
     // TMA wants 16-byte aligned bases and row pitches
     if (a->V % 8 != 0 || a->d % 8 != 0 || ((a->hidden | a->weights) & 15u)) return NRL_E_UNSUPPORTED;
     if ((a->tokens & 3u) || (a->logp & 3u) || (a->entropy & 3u) || (a->rowstats & 15u) || (a->logits_out & 3u) || (a->workspace & 15u)) return NRL_E_BAD_ARG;
     if (a->logp && !a->tokens) return NRL_E_BAD_ARG;
     const bool sample = (a->flags & NRL_READOUT_SAMPLE) != 0;
     if (sample && (!a->uniforms || (a->uniforms & 3u) || !a->tokens)) return NRL_E_BAD_ARG;
+    if ((a->flags & NRL_READOUT_GREEDY) && (sample || !a->tokens)) return NRL_E_BAD_ARG;
     if (a->allow_mask && a->allow_row_stride != 0 && a->allow_row_stride != a->V) return NRL_E_BAD_ARG;
     int dev = 0, cc_major = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -720,7 +721,8 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream) {
     if (p.group_blocks > p.row_blocks) p.group_blocks = p.row_blocks;
     p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
     p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
-    p.tokens = sample ? nullptr : (const int32_t*)a->tokens;
+    p.greedy = (a->flags & NRL_READOUT_GREEDY) ? 1u : 0u;
+    p.tokens = (sample || p.greedy) ? nullptr : (const int32_t*)a->tokens;
     if (!a->workspace || a->workspace_bytes < readout_workspace_one(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
     p.parts = (float*)a->workspace;
     p.allow = (const uint8_t*)a->allow_mask;
@@ -774,6 +776,6 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream) {
         readout_draw_kernel<<<dim3(kRoDrawParts, (unsigned)nslabs), 256, 0, st>>>(p, picks, bucket_start, order, (int32_t*)a->tokens, (float*)a->logp, (const uint16_t*)a->hidden, (const uint16_t*)a->weights);
         return after_launch();
     }
-    readout_finish_kernel<<<(unsigned)((a->rows + 127) / 128), 128, 0, st>>>(a->rows, p.nsplit, p.parts, p.tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats, (uint8_t*)a->status);
+    readout_finish_kernel<<<(unsigned)((a->rows + 127) / 128), 128, 0, st>>>(a->rows, p.nsplit, p.parts, (int32_t*)a->tokens, (float*)a->logp, (float*)a->entropy, (float*)a->rowstats, (uint8_t*)a->status, p.greedy);
     return after_launch();
 }

@@ -55,6 +55,7 @@ struct ReadoutParams {
     uint32_t group_blocks; // row blocks whose CTAs (all column ranges) are launched next to each other
     uint32_t w_is_vd;      // W given as [V, d] (K-major B) instead of [d, V] (N-major B)
     uint32_t round_bf16;   // fold the logits after rounding them to bf16 (what a bf16 logits tensor would hold)
+    uint32_t greedy;       // the token is the row's first maximum: its index travels in the part's token-logit slot
     const int32_t* tokens; // [rows] or null
     float* parts;          // scratch [rows, nsplit, 4]
     uint16_t* logits_out;  // optional bf16 [rows, V]
@@ -214,6 +215,13 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
                 if (EXTRA) qs *= sc;
             }
             m = cm;
+            if (p.greedy) {  // the first column that holds the new maximum (ties with an earlier chunk never come here)
+                uint32_t first = 31u;
+#pragma unroll
+                for (int i = 30; i >= 0; i--)
+                    if (z[i] == cm) first = (uint32_t)i;
+                ztok = __uint_as_float(col0 + first);
+            }
         }
         // three levels of sums (32 columns, a tile, the range) keep the rounding of the long f32 sums small
         float cs = 0.f, cw = 0.f;
@@ -599,7 +607,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kRoThreads, 1)
 
 // Merge the column ranges of each row in index order (f64, as the row kernels finalise) and write
 // the outputs: rowstats (m, ln Z, 0, 0), entropy = ln Z − W / Z, logp = z_tok − m − ln Z.
-__global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const float* parts, const int32_t* tokens, float* logp, float* entropy, float* rowstats, uint8_t* status) {
+// `greedy`: tokens is an output, the index kept by the first range (in column order) that reached the row's maximum.
+__global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const float* parts, int32_t* tokens, float* logp, float* entropy, float* rowstats, uint8_t* status, uint32_t greedy) {
     const uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (row >= rows) return;
     const float4* pr = reinterpret_cast<const float4*>(parts) + row * nsplit;
@@ -614,7 +623,13 @@ __global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const floa
             Z += c * (double)a.y;
             Wt += c * ((double)a.z + (double)a.y * dm);
         }
-        if (a.w == a.w) ztok = a.w;
+        if (!greedy && a.w == a.w) ztok = a.w;
+    }
+    int32_t picked = -1;
+    if (greedy) {
+        for (uint32_t s = 0; s < nsplit && picked < 0; s++)
+            if (pr[s].x == m && pr[s].y > 0.f) picked = (int32_t)__float_as_uint(pr[s].w);
+        ztok = m;
     }
     uint32_t st = 0u;
     for (uint32_t s = 0; s < nsplit; s++)
@@ -622,6 +637,7 @@ __global__ void readout_finish_kernel(uint64_t rows, uint32_t nsplit, const floa
     if (m != m) st |= 2u;
     else if (m == NRL_NEG_INF || m <= -FLT_MAX) st |= 1u;
     const double lnZ = log(Z);
+    if (greedy) tokens[row] = st ? -1 : picked;
     if (st) {
         const float nan = __int_as_float(0x7fc00000);
         if (logp) logp[row] = nan;

@@ -421,13 +421,14 @@ class Readout:
     __slots__ = ("logp", "entropy", "rowstats", "status", "logits", "tokens")
 
 
-def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None):
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None, greedy=False):
     """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
     `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
     `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
     the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]. With
     `uniforms` (float32 [rows]) the tokens are drawn by inverse CDF instead of given (`tokens` of the
-    result); `allow` is a uint8 allow-mask [rows, V] or [1, V]."""
+    result), with `greedy` they are each row's first maximum; `allow` is a uint8 allow-mask [rows, V]
+    or [1, V]."""
     dev = hidden.device
     if dev.type != "cuda":
         raise ValueError("readout_forward needs CUDA tensors: this library has no CPU path")
@@ -437,16 +438,20 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     _need(weights, torch.bfloat16, (V, d) if weights_are_vd else (d, V), "weights", dev)
     a = capi.ReadoutArgs()
     a.struct_size = C.sizeof(a)
-    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0) | (capi.READOUT_SAMPLE if uniforms is not None else 0)
+    a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0) | (capi.READOUT_SAMPLE if uniforms is not None else 0) | (capi.READOUT_GREEDY if greedy else 0)
     a.V, a.d, a.rows = V, d, rows
     a.hidden, a.weights = _p(hidden), _p(weights)
     out = Readout()
     out.logp = out.tokens = None
     if uniforms is not None:
-        if tokens is not None:
-            raise ValueError("give `tokens` or `uniforms`, not both")
+        if tokens is not None or greedy:
+            raise ValueError("give one of `tokens`, `uniforms`, `greedy`")
         _need(uniforms, torch.float32, (rows,), "uniforms", dev)
         a.uniforms = _p(uniforms)
+        tokens = out.tokens = torch.empty(rows, dtype=torch.int32, device=dev)
+    elif greedy:
+        if tokens is not None:
+            raise ValueError("give `tokens` or `greedy`, not both")
         tokens = out.tokens = torch.empty(rows, dtype=torch.int32, device=dev)
     elif tokens is not None:
         _need(tokens, torch.int32, (rows,), "tokens", dev)

@@ -272,8 +272,8 @@ def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
 
 def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None):
     """`sample_categorical(head(x), 1.0, mask, ·)` by inverse CDF against `uniforms` (one per
-    position) without the logits in between: tokens [...] (int32), their log-probs and the
-    per-position entropies. `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
+    position; None: temperature 0, the first maximum) without the logits in between: tokens [...]
+    (int32), their log-probs and the per-position entropies. `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
     position with no allowed token with the reference's message (src/nn/rl.rs:516-519)."""
     lead = hidden.shape[:-1]
     V = weight.shape[1]
@@ -281,6 +281,7 @@ def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None):
     if vocab_mask is not None:
         allow = vocab_mask.reshape(-1, V)
         allow = (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous()
-    o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow)
+    x = hidden.reshape(-1, hidden.shape[-1]).contiguous()
+    o = ops.readout_forward(x, weight, greedy=True, allow=allow) if uniforms is None else ops.readout_forward(x, weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow)
     ops.check_status(o.status)
     return o.tokens.reshape(lead), o.logp.reshape(lead), o.entropy.reshape(lead)

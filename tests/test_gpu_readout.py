@@ -271,3 +271,38 @@ def test_readout_batches_beyond_one_launch():
     assert int(differ.sum()) <= rows // 100, f"{int(differ.sum())} of {rows} tokens differ from nrl_row_fwd's sampler"
     assert allow[torch.arange(rows, device=dev())[keep], s.tokens.long()[keep]].all()
     close(s.entropy[keep].cpu().numpy(), fs.entropy[keep].cpu().numpy(), "entropy vs nrl_row_fwd")
+
+
+@pytest.mark.parametrize("rows,d,V,keep", [(300, 4096, 128256, None), (1000, 512, 4104, 0.3), (129, 64, 512, 0.05), (30000, 64, 1000, 0.5)])
+@pytest.mark.parametrize("layout", ["dV", "Vd"])
+def test_readout_greedy_is_the_first_maximum(rows, d, V, keep, layout):
+    """NRL_READOUT_GREEDY (sample_categorical at temperature 0, src/nn/rl.rs:510-529): the first
+    maximum of the logits the kernel folded (rounded to bf16 and written, so ties exist and the
+    comparison is exact), under an allow-mask too; log-prob = −ln Z at the maximum; a row with
+    nothing allowed is refused."""
+    from noetic_tensor_b200 import ops
+
+    x, w, _ = make(rows, d, V, 19 * rows + V)
+    wa = w.t().contiguous() if layout == "Vd" else w
+    allow = None
+    if keep is not None:
+        g = torch.Generator(device=dev())
+        g.manual_seed(V)
+        allow = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
+        allow[:, V // 3] = 1
+        allow[11] = 0
+    o = ops.readout_forward(x, wa, greedy=True, allow=allow, weights_are_vd=(layout == "Vd"), round_bf16=True, want_logits=True)
+    z = o.logits.float()
+    if allow is not None:
+        z = torch.where(allow.bool(), z, torch.full_like(z, float("-inf")))
+    zmax = z.max(dim=1, keepdim=True).values
+    first = (z == zmax).float().argmax(dim=1)
+    ok = torch.ones(rows, dtype=torch.bool, device=dev())
+    if allow is not None:
+        ok[11] = False
+        assert o.status[11] == 1 and o.tokens[11] == -1
+    assert (o.status[ok] == 0).all()
+    assert torch.equal(o.tokens.long()[ok], first[ok]), f"{int((o.tokens.long()[ok] != first[ok]).sum())} rows are not the first maximum"
+    f = ops.row_forward(o.logits, allow=allow, tokens=o.tokens.clamp_min(0))
+    close(o.logp[ok].cpu().numpy(), f.logp[ok].cpu().numpy(), "logp of the maximum vs nrl_row_fwd")
+    close(o.logp[ok].cpu().numpy(), (-o.rowstats[ok, 1]).cpu().numpy(), "logp = -ln Z", rel=0, abs_=0)
