@@ -584,17 +584,20 @@ inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, c
 // `vocab_mask` an optional U8 allow-mask [.., V] or [1, V]. Returns the tokens (on the host, as
 // sample_categorical does) and, if asked, their log-probabilities and the per-position entropies.
 // Refuses a position with no allowed token with the reference's message (src/nn/rl.rs:516-519).
+// `temperature` 1 (sampling) or 0 (the first maximum; `uniforms` is not read then).
 inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& weight, const Tensor& uniforms, const Tensor* vocab_mask = nullptr, Tensor* logp = nullptr,
-                                         Tensor* entropy = nullptr) {
+                                         Tensor* entropy = nullptr, double temperature = 1.0) {
+    if (temperature != 0.0 && temperature != 1.0) throw std::runtime_error("head_sample_categorical: temperature 1 or 0 (other temperatures scale the logits: sample from them)");
+    const bool greedy = temperature == 0.0;
     if (hidden.dtype() != DType::BF16 || weight.dtype() != DType::BF16) throw std::runtime_error("head_sample_categorical: BF16 hidden states and weight");
     if (hidden.rank() < 1 || weight.rank() != 2 || weight.shape()[0] != hidden.shape().back()) throw std::runtime_error("head_sample_categorical: hidden [.., d], weight [d, V]");
     const Shape lead(hidden.shape().begin(), hidden.shape().end() - 1);
     const uint64_t d = weight.shape()[0], V = weight.shape()[1], rows = numel(lead);
-    if (uniforms.dtype() != DType::F32 || numel(uniforms.shape()) != rows) throw std::runtime_error("sample_categorical: one uniform per position");
+    if (!greedy && (uniforms.dtype() != DType::F32 || numel(uniforms.shape()) != rows)) throw std::runtime_error("sample_categorical: one uniform per position");
     nrl_readout_args a;
     std::memset(&a, 0, sizeof a);
     a.struct_size = sizeof a;
-    a.flags = NRL_READOUT_SAMPLE;
+    a.flags = greedy ? NRL_READOUT_GREEDY : NRL_READOUT_SAMPLE;
     if (vocab_mask) {
         if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("head_sample_categorical: a U8 allow-mask");
         const uint64_t n = numel(vocab_mask->shape());
@@ -608,7 +611,8 @@ inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& wei
     const uint64_t need = nrl_readout_workspace_bytes(rows, (uint32_t)V, (uint32_t)d, a.flags);
     Tensor ws = Tensor::empty(Shape{(size_t)need}, DType::U8, hidden.device());
     a.V = (uint32_t)V; a.d = (uint32_t)d; a.rows = rows;
-    a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev(); a.uniforms = uniforms.dev();
+    a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev();
+    if (!greedy) a.uniforms = uniforms.dev();
     a.logp = lp.dev(); a.status = status.dev();
     if (entropy) {
         *entropy = Tensor::empty(lead, DType::F32, hidden.device());

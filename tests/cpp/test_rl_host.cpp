@@ -619,6 +619,21 @@ static void test_head_sample_categorical() {
     CHECK(outside == 0, "%zu drawn tokens whose CDF interval does not hold the uniform", outside);
     close_all(lp, want_lp, 1e-4, "head_sample_categorical log-probs");
     close_all(en, want_en, 2e-5, "head_sample_categorical entropy");
+    // temperature 0: the first maximum among the allowed tokens (f64 logits; an f32 near-tie may pick a neighbour of equal value only)
+    const IntTensor top = rl::head_sample_categorical(hx, hw, hu, &hm, nullptr, nullptr, 0.0);
+    size_t off_max = 0;
+    for (size_t r = 0; r < rows; r++) {
+        double best = -1e300, mine = 0.0;
+        for (size_t v = 0; v < V; v++) {
+            if (!mask[r * V + v]) continue;
+            double z = 0.0;
+            for (size_t k = 0; k < d; k++) z += (double)x[r * d + k] * (double)w[k * V + v];
+            best = std::max(best, z);
+            if ((int64_t)v == top.data[r]) mine = z;
+        }
+        if (!(top.data[r] >= 0 && mask[r * V + top.data[r]] && best - mine <= 1e-4)) off_max++;
+    }
+    CHECK(off_max == 0, "%zu greedy tokens are not a maximum of the allowed logits", off_max);
     std::vector<uint8_t> none(mask);
     for (size_t v = 0; v < V; v++) none[7 * V + v] = 0;
     Tensor hn = Tensor::from_u8(none, {S, B, T, V}, dev);
