@@ -546,6 +546,9 @@ typedef struct nrl_readout_args {
     nrl_devptr allow_mask;   /* u8 allow-mask as in nrl_row_fwd ([rows, V], or [1, V] with stride 0), or 0 */
     uint64_t allow_row_stride; /* V or 0 */
     nrl_devptr uniforms;     /* f32 [rows] in [0,1), for NRL_READOUT_SAMPLE; else 0 */
+    float temperature;       /* τ > 0: the logits are divided by it before they are folded (tempered_logits, src/nn/rl.rs:475-486;
+                                `logits_out` keeps the undivided ones); 0 means 1 */
+    uint32_t reserved;       /* 0 */
 } nrl_readout_args;
 
 /* scratch for a call with these flags (sampling adds 32 bytes per row and vocabulary tile). More than

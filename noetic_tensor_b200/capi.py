@@ -99,7 +99,7 @@ class ReadoutArgs(C.Structure):
     _fields_ = [
         ("struct_size", u32), ("flags", u32), ("V", u32), ("d", u32), ("rows", u64),
         ("hidden", ptr), ("weights", ptr), ("tokens", ptr), ("logp", ptr), ("entropy", ptr), ("rowstats", ptr), ("status", ptr), ("logits_out", ptr),
-        ("workspace", ptr), ("workspace_bytes", u64), ("allow_mask", ptr), ("allow_row_stride", u64), ("uniforms", ptr),
+        ("workspace", ptr), ("workspace_bytes", u64), ("allow_mask", ptr), ("allow_row_stride", u64), ("uniforms", ptr), ("temperature", C.c_float), ("reserved", u32),
     ]
 
 

@@ -667,6 +667,7 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     const bool sample = (a->flags & NRL_READOUT_SAMPLE) != 0;
     if (sample && (!a->uniforms || (a->uniforms & 3u) || !a->tokens)) return NRL_E_BAD_ARG;
     if ((a->flags & NRL_READOUT_GREEDY) && (sample || !a->tokens)) return NRL_E_BAD_ARG;
+    if (a->reserved != 0 || !(a->temperature >= 0.f) || !isfinite(a->temperature)) return NRL_E_BAD_ARG;
     if (a->allow_mask && a->allow_row_stride != 0 && a->allow_row_stride != a->V) return NRL_E_BAD_ARG;
     int dev = 0, cc_major = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -722,6 +723,7 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream) {
     p.w_is_vd = (a->flags & NRL_READOUT_W_VD) ? 1u : 0u;
     p.round_bf16 = (a->flags & NRL_READOUT_ROUND_BF16) ? 1u : 0u;
     p.greedy = (a->flags & NRL_READOUT_GREEDY) ? 1u : 0u;
+    p.tau = a->temperature == 0.f ? 1.f : a->temperature;
     p.tokens = (sample || p.greedy) ? nullptr : (const int32_t*)a->tokens;
     if (!a->workspace || a->workspace_bytes < readout_workspace_one(a->rows, a->V, a->d, a->flags)) return NRL_E_WORKSPACE;
     p.parts = (float*)a->workspace;

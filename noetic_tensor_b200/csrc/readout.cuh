@@ -56,6 +56,7 @@ struct ReadoutParams {
     uint32_t w_is_vd;      // W given as [V, d] (K-major B) instead of [d, V] (N-major B)
     uint32_t round_bf16;   // fold the logits after rounding them to bf16 (what a bf16 logits tensor would hold)
     uint32_t greedy;       // the token is the row's first maximum: its index travels in the part's token-logit slot
+    float tau;             // temperature: every logit is divided by it (IEEE division, as tempered_logits does) before it is folded
     const int32_t* tokens; // [rows] or null
     float* parts;          // scratch [rows, nsplit, 4]
     uint16_t* logits_out;  // optional bf16 [rows, V]
@@ -193,6 +194,11 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
                     p.logits_out[row * p.V + col0 + i] = (uint16_t)(__float_as_uint(round_through_bf16(z[i])) >> 16);
                 }
             }
+        }
+        if (p.tau != 1.f) {  // logits / τ (src/nn/rl.rs:475-486); excluded columns stay −FLT_MAX
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (!(z[i] <= -FLT_MAX)) z[i] = __fdiv_rn(z[i], p.tau);
         }
         if (tok >= (int32_t)col0 && tok < (int32_t)(col0 + 32)) {
 #pragma unroll
@@ -902,6 +908,7 @@ __global__ void __launch_bounds__(256) readout_draw_kernel(ReadoutParams p, cons
         }
         const ReadoutPick pk = picks[row];
         if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
+        if (p.tau != 1.f) { z0 = __fdiv_rn(z0, p.tau); z1 = __fdiv_rn(z1, p.tau); }
         bool ok0 = ca < p.V, ok1 = ca + 1 < p.V;
         if (p.allow) {
             const uint8_t* mp = p.allow + row * p.allow_stride;

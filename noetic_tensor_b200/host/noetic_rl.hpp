@@ -584,10 +584,10 @@ inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, c
 // `vocab_mask` an optional U8 allow-mask [.., V] or [1, V]. Returns the tokens (on the host, as
 // sample_categorical does) and, if asked, their log-probabilities and the per-position entropies.
 // Refuses a position with no allowed token with the reference's message (src/nn/rl.rs:516-519).
-// `temperature` 1 (sampling) or 0 (the first maximum; `uniforms` is not read then).
+// `temperature` > 0 divides the logits (tempered_logits); 0 takes the first maximum (`uniforms` is not read then).
 inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& weight, const Tensor& uniforms, const Tensor* vocab_mask = nullptr, Tensor* logp = nullptr,
                                          Tensor* entropy = nullptr, double temperature = 1.0) {
-    if (temperature != 0.0 && temperature != 1.0) throw std::runtime_error("head_sample_categorical: temperature 1 or 0 (other temperatures scale the logits: sample from them)");
+    if (!(temperature >= 0.0 && std::isfinite(temperature))) throw std::runtime_error("sample_categorical: temperature (must be >= 0)");
     const bool greedy = temperature == 0.0;
     if (hidden.dtype() != DType::BF16 || weight.dtype() != DType::BF16) throw std::runtime_error("head_sample_categorical: BF16 hidden states and weight");
     if (hidden.rank() < 1 || weight.rank() != 2 || weight.shape()[0] != hidden.shape().back()) throw std::runtime_error("head_sample_categorical: hidden [.., d], weight [d, V]");
@@ -612,7 +612,10 @@ inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& wei
     Tensor ws = Tensor::empty(Shape{(size_t)need}, DType::U8, hidden.device());
     a.V = (uint32_t)V; a.d = (uint32_t)d; a.rows = rows;
     a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev();
-    if (!greedy) a.uniforms = uniforms.dev();
+    if (!greedy) {
+        a.uniforms = uniforms.dev();
+        a.temperature = (float)temperature;
+    }
     a.logp = lp.dev(); a.status = status.dev();
     if (entropy) {
         *entropy = Tensor::empty(lead, DType::F32, hidden.device());

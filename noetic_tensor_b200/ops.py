@@ -421,14 +421,15 @@ class Readout:
     __slots__ = ("logp", "entropy", "rowstats", "status", "logits", "tokens")
 
 
-def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None, greedy=False):
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None, greedy=False, temperature=1.0):
     """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
     `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
     `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
     the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]. With
     `uniforms` (float32 [rows]) the tokens are drawn by inverse CDF instead of given (`tokens` of the
     result), with `greedy` they are each row's first maximum; `allow` is a uint8 allow-mask [rows, V]
-    or [1, V]."""
+    or [1, V]; `temperature` divides the logits before they are folded (the returned `logits` are the
+    undivided ones)."""
     dev = hidden.device
     if dev.type != "cuda":
         raise ValueError("readout_forward needs CUDA tensors: this library has no CPU path")
@@ -439,7 +440,7 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     a = capi.ReadoutArgs()
     a.struct_size = C.sizeof(a)
     a.flags = (capi.READOUT_W_VD if weights_are_vd else 0) | (capi.READOUT_ROUND_BF16 if round_bf16 else 0) | (capi.READOUT_ONE_CTA if one_cta else 0) | (capi.READOUT_SAMPLE if uniforms is not None else 0) | (capi.READOUT_GREEDY if greedy else 0)
-    a.V, a.d, a.rows = V, d, rows
+    a.V, a.d, a.rows, a.temperature = V, d, rows, float(temperature)
     a.hidden, a.weights = _p(hidden), _p(weights)
     out = Readout()
     out.logp = out.tokens = None

@@ -270,10 +270,10 @@ def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
     return o.logp.reshape(lead), o.entropy.reshape(lead)
 
 
-def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None):
-    """`sample_categorical(head(x), 1.0, mask, ·)` by inverse CDF against `uniforms` (one per
-    position; None: temperature 0, the first maximum) without the logits in between: tokens [...]
-    (int32), their log-probs and the per-position entropies. `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
+def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None, temperature=1.0):
+    """`sample_categorical(head(x), temperature, mask, ·)` by inverse CDF against `uniforms` (one per
+    position; None or temperature 0: the first maximum) without the logits in between: tokens [...]
+    (int32), their log-probs and the per-position entropies (of the tempered distribution). `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
     position with no allowed token with the reference's message (src/nn/rl.rs:516-519)."""
     lead = hidden.shape[:-1]
     V = weight.shape[1]
@@ -282,6 +282,11 @@ def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None):
         allow = vocab_mask.reshape(-1, V)
         allow = (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous()
     x = hidden.reshape(-1, hidden.shape[-1]).contiguous()
-    o = ops.readout_forward(x, weight, greedy=True, allow=allow) if uniforms is None else ops.readout_forward(x, weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow)
+    if not (temperature >= 0.0 and temperature == temperature and temperature != float("inf")):
+        raise ValueError("sample_categorical: temperature (must be >= 0)")
+    if uniforms is None or temperature == 0.0:
+        o = ops.readout_forward(x, weight, greedy=True, allow=allow)
+    else:
+        o = ops.readout_forward(x, weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow, temperature=temperature)
     ops.check_status(o.status)
     return o.tokens.reshape(lead), o.logp.reshape(lead), o.entropy.reshape(lead)

@@ -43,7 +43,7 @@ def test_struct_layouts():
     assert C.sizeof(capi.LaneArgs) == 4 * 4 + 8 + 5 * 8
     assert C.sizeof(capi.PackArgs) == 4 * 4 + 8 + 3 * 8 + 8 + 5 * 8 + 8
     assert C.sizeof(capi.UnpackArgs) == 4 * 4 + 8 + 8 * 8
-    assert C.sizeof(capi.ReadoutArgs) == 4 * 4 + 8 + 9 * 8 + 8 + 3 * 8
+    assert C.sizeof(capi.ReadoutArgs) == 4 * 4 + 8 + 9 * 8 + 8 + 3 * 8 + 4 + 4
     assert C.sizeof(capi.TokenObjectiveArgs) == 8 + C.sizeof(capi.TokenLossArgs) + 11 * 8
 
 

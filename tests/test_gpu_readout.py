@@ -306,3 +306,44 @@ def test_readout_greedy_is_the_first_maximum(rows, d, V, keep, layout):
     f = ops.row_forward(o.logits, allow=allow, tokens=o.tokens.clamp_min(0))
     close(o.logp[ok].cpu().numpy(), f.logp[ok].cpu().numpy(), "logp of the maximum vs nrl_row_fwd")
     close(o.logp[ok].cpu().numpy(), (-o.rowstats[ok, 1]).cpu().numpy(), "logp = -ln Z", rel=0, abs_=0)
+
+
+@pytest.mark.parametrize("tau", [0.7, 1.5])
+@pytest.mark.parametrize("rows,d,V,keep", [(300, 4096, 128256, None), (1000, 512, 4104, 0.3)])
+def test_readout_temperature(oracle, rows, d, V, keep, tau):
+    """logits / τ inside the fused pass (tempered_logits, src/nn/rl.rs:475-486): given tokens,
+    sampling and the first maximum against nrl_row_fwd at the same temperature on the (undivided)
+    logits the call wrote, and against the oracle on a sample of rows."""
+    from noetic_tensor_b200 import ops
+
+    x, w, tok = make(rows, d, V, 23 * rows + V)
+    g = torch.Generator(device=dev())
+    g.manual_seed(V + rows)
+    u = torch.rand(rows, generator=g, device=dev())
+    allow = None
+    if keep is not None:
+        allow = (torch.rand(rows, V, generator=g, device=dev()) < keep).to(torch.uint8)
+        allow[:, V // 3] = 1
+    o = ops.readout_forward(x, w, tokens=tok, allow=allow, round_bf16=True, want_logits=True, temperature=tau)
+    f = ops.row_forward(o.logits, allow=allow, tokens=tok, temperature=tau)
+    close(o.logp.cpu().numpy(), f.logp.cpu().numpy(), "logp vs nrl_row_fwd")
+    close(o.entropy.cpu().numpy(), f.entropy.cpu().numpy(), "entropy vs nrl_row_fwd")
+    assert torch.equal(o.rowstats[:, 0], f.rowstats[:, 0]), "the row maximum is exact"
+    idx = np.random.default_rng(rows).choice(rows, 16, replace=False)
+    bits = o.logits[idx].view(torch.int16).cpu().numpy().view(np.uint16)
+    orc = oracle.sample_inverse_cdf(bits, tau, None, allow=None if allow is None else allow[idx].cpu().numpy(), given_tokens=tok[idx].cpu().numpy().astype(np.int64))
+    close(o.entropy[idx].cpu().numpy(), orc["entropy"], "entropy vs oracle")
+    lp = o.logp[idx].cpu().numpy()
+    finite = np.isfinite(orc["logp"])
+    close(lp[finite], orc["logp"][finite], "logp vs oracle")
+    s = ops.readout_forward(x, w, uniforms=u, allow=allow, round_bf16=True, want_logits=True, temperature=tau)
+    fs = ops.row_forward(s.logits, allow=allow, uniforms=u, temperature=tau)
+    assert int((s.tokens != fs.tokens).sum()) <= max(2, rows // 100)
+    same = s.tokens == fs.tokens
+    d_lp = (s.logp[same] - fs.logp[same]).abs()
+    zt = s.logits[torch.arange(rows, device=dev()), s.tokens.long()][same].float().abs()
+    assert (d_lp <= 1e-5 * fs.logp[same].abs() + 1e-6 + 2.0 ** -7 * zt / tau).all() and int((d_lp > 1e-4).sum()) <= max(2, rows // 100)
+    gr = ops.readout_forward(x, w, greedy=True, allow=allow, round_bf16=True, want_logits=True, temperature=tau)
+    fg = ops.row_forward(gr.logits, allow=allow, greedy=True, temperature=tau)
+    assert torch.equal(gr.tokens, fg.tokens)
+    close(gr.logp.cpu().numpy(), fg.logp.cpu().numpy(), "greedy logp vs nrl_row_fwd")
