@@ -273,8 +273,9 @@ def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
 def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None, temperature=1.0):
     """`sample_categorical(head(x), temperature, mask, ·)` by inverse CDF against `uniforms` (one per
     position; None or temperature 0: the first maximum) without the logits in between: tokens [...]
-    (int32), their log-probs and the per-position entropies (of the tempered distribution). `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a
-    position with no allowed token with the reference's message (src/nn/rl.rs:516-519)."""
+    (int32), their log-probs and the per-position entropies (of the tempered distribution).
+    `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a position with no allowed token
+    with the reference's message (src/nn/rl.rs:516-519)."""
     lead = hidden.shape[:-1]
     V = weight.shape[1]
     allow = None

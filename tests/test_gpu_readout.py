@@ -347,3 +347,51 @@ def test_readout_temperature(oracle, rows, d, V, keep, tau):
     fg = ops.row_forward(gr.logits, allow=allow, greedy=True, temperature=tau)
     assert torch.equal(gr.tokens, fg.tokens)
     close(gr.logp.cpu().numpy(), fg.logp.cpu().numpy(), "greedy logp vs nrl_row_fwd")
+
+
+def test_head_functions_of_the_rl_module():
+    """rl.head_token_log_probs / rl.head_sample_categorical (the Python mirrors of Decoder::head
+    followed by token_log_probs / sample_categorical): leading shapes, a [1, V] and a per-position
+    mask, temperature, temperature 0, and the reference's refusal text; values against the f64
+    log-softmax of the f64 product."""
+    from noetic_tensor_b200 import rl
+
+    S, B, T, d, V = 2, 3, 20, 64, 512
+    g = torch.Generator(device=dev())
+    g.manual_seed(3)
+    h = torch.randn(S, B, T, d, generator=g, device=dev()).bfloat16()
+    w = (torch.randn(d, V, generator=g, device=dev()) * 0.4).bfloat16()
+    tok = torch.randint(0, V, (S, B, T), generator=g, device=dev())
+    z = h.double() @ w.double()
+    lp, ent = rl.head_token_log_probs(h, w, tok)
+    want = torch.log_softmax(z, -1)
+    assert lp.shape == (S, B, T) and ent.shape == (S, B, T)
+    close(lp.cpu().numpy(), want.gather(-1, tok[..., None])[..., 0].cpu().numpy(), "head_token_log_probs", rel=5e-5, abs_=5e-6)
+    close(ent.cpu().numpy(), (-(want.exp() * want).sum(-1)).cpu().numpy(), "entropy", rel=5e-5, abs_=5e-6)
+    u = torch.rand(S, B, T, generator=g, device=dev())
+    shared = torch.ones(1, V, dtype=torch.bool, device=dev())
+    shared[0, ::3] = False
+    for tau, mask in ((1.0, None), (0.8, shared), (1.3, torch.rand(S, B, T, V, generator=g, device=dev()) < 0.4)):
+        if mask is not None and mask.dim() == 4:
+            mask[..., 7] = True
+        tk, lps, en = rl.head_sample_categorical(h, w, u, vocab_mask=mask, temperature=tau)
+        zt = z / tau
+        if mask is not None:
+            zt = torch.where(mask.expand(S, B, T, V), zt, torch.full_like(zt, float("-inf")))
+        p = torch.softmax(zt, -1)
+        cdf = p.cumsum(-1)
+        hi = cdf.gather(-1, tk.long()[..., None])[..., 0]
+        lo = hi - p.gather(-1, tk.long()[..., None])[..., 0]
+        assert tk.shape == (S, B, T) and ((u.double() >= lo - 1e-4) & (u.double() <= hi + 1e-4)).all(), tau
+        if mask is not None:
+            assert mask.expand(S, B, T, V).gather(-1, tk.long()[..., None]).all()
+        close(lps.cpu().numpy(), torch.log_softmax(zt, -1).gather(-1, tk.long()[..., None])[..., 0].cpu().numpy(), "log-probs of drawn tokens", rel=5e-5, abs_=1e-4)
+        lw = torch.log_softmax(zt, -1)
+        close(en.cpu().numpy(), (-(p * torch.where(p > 0, lw, torch.zeros_like(lw))).sum(-1)).cpu().numpy(), "entropy of the tempered distribution", rel=5e-5, abs_=5e-6)
+    tk0, lp0, _ = rl.head_sample_categorical(h, w, None, vocab_mask=shared)
+    z0 = torch.where(shared.expand(S, B, T, V), z, torch.full_like(z, float("-inf")))
+    assert ((z0.max(-1).values - z0.gather(-1, tk0.long()[..., None])[..., 0]) <= 1e-4).all()
+    none = torch.ones(S, B, T, V, dtype=torch.bool, device=dev())
+    none[0, 0, 5] = False
+    with pytest.raises(RuntimeError, match="position 5 has no allowed token"):
+        rl.head_sample_categorical(h, w, u, vocab_mask=none)
