@@ -492,15 +492,22 @@ def run_readout_variant(args):
     hx = torch.randn(rows, d, generator=gen, device=dev).to(torch.bfloat16)
     wt = (torch.randn(d, V, generator=gen, device=dev) * (3.0 / d ** 0.5)).to(torch.bfloat16)
     tk = torch.randint(0, V, (rows,), generator=gen, device=dev, dtype=torch.int32)
-    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d, 0), dtype=torch.uint8, device=dev)
+    ws = torch.empty(capi.lib().nrl_readout_workspace_bytes(rows, V, d, capi.READOUT_SAMPLE if args.readout_sample else 0), dtype=torch.uint8, device=dev)
+    if args.readout_sample:  # masked sampling fused: the tensor-core pass with the mass log, then pick, grouping and draw
+        from noetic_tensor_b200 import synth
+
+        am, un = synth.grammar_masks(rows, V, gen, dev), synth.uniforms(rows, gen, dev)
+        call = lambda: ops.readout_forward(hx, wt, uniforms=un, allow=am, workspace=ws, one_cta=args.readout_one_cta)
+    else:
+        call = lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws, one_cta=args.readout_one_cta)
     for _ in range(max(1, args.warmup)):
-        ops.readout_forward(hx, wt, tokens=tk, workspace=ws, one_cta=args.readout_one_cta)
+        call()
     torch.cuda.synchronize()
     launches0 = capi.lib().nrl_launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        o = ops.readout_forward(hx, wt, tokens=tk, workspace=ws, one_cta=args.readout_one_cta)
+        o = call()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
@@ -510,7 +517,7 @@ def run_readout_variant(args):
     except Exception:
         peak, kind = 1400.0, "fallback"
     tf = 2.0 * rows * d * V / (ms * 1e-3) / 1e12
-    print(json.dumps({"metric": "rows/s readout-fused log-prob + entropy, d=4096, V=128256 bf16 (profiling variant, not the headline)", "value": rows / (ms * 1e-3), "unit": "rows/s",
+    print(json.dumps({"metric": "rows/s readout-fused " + ("masked sampling + " if args.readout_sample else "") + "log-prob + entropy, d=4096, V=128256 bf16 (profiling variant, not the headline)", "value": rows / (ms * 1e-3), "unit": "rows/s",
                       "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "dtype": "bf16 operands, f32 accumulators",
                       "config": {"workload": f"hidden [{rows}, {d}] x W [{d}, {V}] -> row statistics"}, "gpu_launches": int(capi.lib().nrl_launch_count() - launches0),
                       "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_kind": kind, "kernel": "readout_fwd_kernel<false>" if (args.readout_one_cta or rows <= 128) else "readout_fwd_pair_kernel<false>", "traffic": None},
@@ -946,6 +953,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the secondary measurements (backward, PPO step, other configs)")
     ap.add_argument("--l2-fetch-granularity", type=int, default=0, help="set cudaLimitMaxL2FetchGranularity (32, 64, 128) for this process: an experiment switch for profiler captures")
     ap.add_argument("--readout-one-cta", action="store_true", help="--variant readout: one CTA per 128 rows (NRL_READOUT_ONE_CTA) instead of CTA pairs")
+    ap.add_argument("--readout-sample", action="store_true", help="--variant readout: U8 grammar masks and inverse-CDF sampling fused (NRL_READOUT_SAMPLE) instead of given tokens")
     ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling measurement and the cross-rank TokenReduction check")
     ap.add_argument("--rows", type=int, default=0, help="cap the resident rows per GPU (small cases for profiler captures)")
     args = ap.parse_args()
