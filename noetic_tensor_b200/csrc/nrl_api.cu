@@ -396,11 +396,22 @@ static int launch_lane_cluster_as(const nrl_lane_args* a, uint32_t csize, uint32
     cfg.stream = st;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    int resident = 0;
-    e = cudaOccupancyMaxActiveClusters(&resident, kernel, &cfg);
-    if (e != cudaSuccess || resident < 1) {
-        (void)cudaGetLastError();
-        return NRL_E_UNSUPPORTED;  // the caller falls back to the kernel that reads the row twice
+    // how many clusters of this shape the device holds at once: asked once per (device, shape) and kernel
+    static std::atomic<uint64_t> known{0};  // device << 56 | cluster size << 48 | shared memory << 16 | resident clusters
+    int dev = 0, resident = 0;
+    e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    const uint64_t key = ((uint64_t)(dev & 0xff) << 56) | ((uint64_t)csize << 48) | ((uint64_t)smem << 16);
+    const uint64_t seen = known.load(std::memory_order_relaxed);
+    if ((seen & ~0xffffull) == key && (seen & 0xffffull) != 0) {
+        resident = (int)(seen & 0xffffull);
+    } else {
+        e = cudaOccupancyMaxActiveClusters(&resident, kernel, &cfg);
+        if (e != cudaSuccess || resident < 1) {
+            (void)cudaGetLastError();
+            return NRL_E_UNSUPPORTED;  // the caller falls back to the kernel that reads the row twice
+        }
+        known.store(key | (uint64_t)(resident > 0xffff ? 0xffff : resident), std::memory_order_relaxed);
     }
     const uint64_t clusters = a->rows < (uint64_t)resident ? a->rows : (uint64_t)resident;
     cfg.gridDim = dim3((unsigned)(clusters * csize), 1, 1);
