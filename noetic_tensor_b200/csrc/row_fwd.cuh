@@ -369,7 +369,8 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     // four tiles, folded 16 elements at a time (one vote per two vectors): +26 % over one tile per step. With one, two
     // tiles folded 8 + 8: 32 values at once do not fit 64 registers (the 16-wide fold spilled and gained nothing), and
     // four tiles of two streams would leave the 4 KB ring a single slot: +6 %.
-    constexpr int kT = DT == NRL_BF16 ? (REF ? 2 : 4) : 1;  // tiles per step
+    // 4-byte elements without a reference stream: two tiles, one 16-wide fold (+3 %).
+    constexpr int kT = DT == NRL_BF16 ? (REF ? 2 : 4) : (REF ? 1 : 2);  // tiles per step
     constexpr bool kWide = kT >= 2 && !REF;
     constexpr int kPer = (DT == NRL_F32 ? 2 : 1);     // 16-byte pieces per lane per stream per tile
     constexpr int kRows = kPer * (REF ? 2 : 1) * kT;  // ring rows one step takes
@@ -384,7 +385,7 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
     // 8 elements of the tile; with 4-byte elements a lane takes two pieces of 4 elements, 128
     // elements apart (lane·4 … and 128 + lane·4 …), so that neither copy touches half sectors.
     constexpr uint32_t kLaneElems = 16 / kEsize;  // elements per 16-byte piece
-    constexpr uint32_t kPieceGap = kT >= 2 ? kTile : 128;  // elements between a lane's two pieces: the next tile (bf16 pairs) or half a tile (f32)
+    constexpr uint32_t kPieceGap = DT == NRL_F32 ? 128 : kTile;  // elements between a lane's two pieces: the next tile (bf16 pairs) or half a tile (f32)
     constexpr int kPieces = kPer * kT;                     // pieces per lane per stream per step
     const char* xp = (const char*)p.logits + (row * p.V + begin + lane * kLaneElems) * kEsize;
     const char* rp = REF ? (const char*)p.ref + (row * p.V + begin + lane * kLaneElems) * kEsize : nullptr;
@@ -419,25 +420,23 @@ __device__ __forceinline__ Partial stream_part_async(const FwdParams& p, uint64_
             cp_async_wait<kSlots - 1>();  // the oldest step has landed
             if (t0 + s * kStep < end) {  // warp-uniform: the step exists
                 if constexpr (DT == NRL_F32) {
-                    float z[8], zr[8];
-                    Raw<DT> x, r;
-                    x.a = lds16(base + (s * kRows) * 512);
-                    x.b = lds16(base + (s * kRows + 1) * 512);
-                    x.unpack(z);
-                    if (REF) {
-                        r.a = lds16(base + (s * kRows + 2) * 512);
-                        r.b = lds16(base + (s * kRows + 3) * 512);
-                        r.unpack(zr);
-                    }
-                    // a piece past the end of a ragged last tile: nothing was copied, nothing to add
+                    // four floats per piece; without a reference stream a step is two tiles, folded 16 at a time
+                    float z[8 * kT], zr[8 * kT];
 #pragma unroll
-                    for (int k = 0; k < kPer; k++) {
+                    for (int k = 0; k < kPieces; k++) {
+                        const uint4 q = lds16(base + (s * kRows + k) * 512);
+                        z[4 * k] = __uint_as_float(q.x); z[4 * k + 1] = __uint_as_float(q.y); z[4 * k + 2] = __uint_as_float(q.z); z[4 * k + 3] = __uint_as_float(q.w);
+                        if (REF) {
+                            const uint4 r = lds16(base + (s * kRows + kPieces + k) * 512);
+                            zr[4 * k] = __uint_as_float(r.x); zr[4 * k + 1] = __uint_as_float(r.y); zr[4 * k + 2] = __uint_as_float(r.z); zr[4 * k + 3] = __uint_as_float(r.w);
+                        }
+                        // a piece past the end of a ragged last tile: nothing was copied, nothing to add
                         if (v + k * kPieceGap >= end) {
 #pragma unroll
-                            for (int i = k * 4; i < (k + 1) * 4; i++) z[i] = zr[i] = -FLT_MAX;
+                            for (int i = 4 * k; i < 4 * k + 4; i++) z[i] = zr[i] = -FLT_MAX;
                         }
                     }
-                    accumulate<REF, LOG>(acc, z, zr);
+                    accumulate<REF, LOG, 8 * kT>(acc, z, zr);
                 } else if constexpr (kWide) {
 #pragma unroll
                     for (int h = 0; h < kT / 2; h++) {
