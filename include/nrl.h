@@ -522,6 +522,8 @@ enum {
                                      computes those 64 logits again (f32) to walk to the token */
     NRL_READOUT_GREEDY = 1u << 4,  /* the token is the row's first maximum (sample_categorical at temperature 0, src/nn/rl.rs:510-529): `tokens` is an
                                      output, `logp` its log-prob; the allow-mask applies; not together with NRL_READOUT_SAMPLE */
+    NRL_READOUT_MASK_BITS = 1u << 5,  /* `allow_mask` holds one bit per token (u32 words, bit v mod 32 of word v / 32, as NRL_FWD_MASK_BITS);
+                                        `allow_row_stride` then counts words per row (≥ ceil(V / 32), or 0 for one row shared by all) */
     NRL_READOUT_ONE_CTA = 1u << 2 /* one CTA per 128-row block (tcgen05 cta_group::1) instead of CTA pairs on 256-row blocks
                                     (cta_group::2, the default for more than 128 rows), and one launch however many rows: the same bits up to
                                     24 576 rows; beyond, the count of column ranges, and with it the last bits of the sums, may differ */

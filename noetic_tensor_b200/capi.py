@@ -103,7 +103,7 @@ class ReadoutArgs(C.Structure):
     ]
 
 
-READOUT_W_VD, READOUT_ROUND_BF16, READOUT_ONE_CTA, READOUT_SAMPLE, READOUT_GREEDY = 1, 2, 4, 8, 16
+READOUT_W_VD, READOUT_ROUND_BF16, READOUT_ONE_CTA, READOUT_SAMPLE, READOUT_GREEDY, READOUT_MASK_BITS = 1, 2, 4, 8, 16, 32
 
 LANE_SOFTMAX, LANE_LOG_SOFTMAX, LANE_LOGSUMEXP, LANE_ARGMAX, LANE_SUM, LANE_SOFTMAX_BWD, LANE_LOG_SOFTMAX_BWD, LANE_LOGSUMEXP_BWD = range(8)
 

@@ -670,7 +670,7 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream);
 extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (!a || a->struct_size != sizeof(nrl_readout_args)) return NRL_E_BAD_ARG;
     if (a->rows == 0 || a->V == 0 || a->d == 0 || !a->hidden || !a->weights) return NRL_E_BAD_ARG;
-    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA | NRL_READOUT_SAMPLE | NRL_READOUT_GREEDY)) return NRL_E_BAD_ARG;
+    if (a->flags & ~(uint32_t)(NRL_READOUT_W_VD | NRL_READOUT_ROUND_BF16 | NRL_READOUT_ONE_CTA | NRL_READOUT_SAMPLE | NRL_READOUT_GREEDY | NRL_READOUT_MASK_BITS)) return NRL_E_BAD_ARG;
     // TMA wants 16-byte aligned bases and row pitches
     if (a->V % 8 != 0 || a->d % 8 != 0 || ((a->hidden | a->weights) & 15u)) return NRL_E_UNSUPPORTED;
     if ((a->tokens & 3u) || (a->logp & 3u) || (a->entropy & 3u) || (a->rowstats & 15u) || (a->logits_out & 3u) || (a->workspace & 15u)) return NRL_E_BAD_ARG;
@@ -679,7 +679,11 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
     if (sample && (!a->uniforms || (a->uniforms & 3u) || !a->tokens)) return NRL_E_BAD_ARG;
     if ((a->flags & NRL_READOUT_GREEDY) && (sample || !a->tokens)) return NRL_E_BAD_ARG;
     if (a->reserved != 0 || !(a->temperature >= 0.f) || !isfinite(a->temperature)) return NRL_E_BAD_ARG;
-    if (a->allow_mask && a->allow_row_stride != 0 && a->allow_row_stride != a->V) return NRL_E_BAD_ARG;
+    if (a->flags & NRL_READOUT_MASK_BITS) {  // bit-packed: the row stride counts u32 words (0: one row for all)
+        if (!a->allow_mask || (a->allow_mask & 3u) || (a->allow_row_stride != 0 && a->allow_row_stride < (a->V + 31u) / 32u)) return NRL_E_BAD_ARG;
+    } else if (a->allow_mask && a->allow_row_stride != 0 && a->allow_row_stride != a->V) {
+        return NRL_E_BAD_ARG;
+    }
     int dev = 0, cc_major = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&cc_major, cudaDevAttrComputeCapabilityMajor, dev);
@@ -699,7 +703,7 @@ extern "C" int nrl_readout_fwd(const nrl_readout_args* a, nrl_stream stream) {
         if (a->rowstats) c.rowstats = a->rowstats + r0 * 16;
         if (a->status) c.status = a->status + r0;
         if (a->logits_out) c.logits_out = a->logits_out + r0 * a->V * 2;
-        if (a->allow_mask) c.allow_mask = a->allow_mask + r0 * a->allow_row_stride;
+        if (a->allow_mask) c.allow_mask = a->allow_mask + r0 * a->allow_row_stride * ((a->flags & NRL_READOUT_MASK_BITS) ? 4u : 1u);
         if (a->uniforms) c.uniforms = a->uniforms + r0 * 4;
         const int rc = readout_fwd_one(&c, stream);
         if (rc) return rc;
@@ -740,6 +744,7 @@ static int readout_fwd_one(const nrl_readout_args* a, nrl_stream stream) {
     p.parts = (float*)a->workspace;
     p.allow = (const uint8_t*)a->allow_mask;
     p.allow_stride = a->allow_row_stride;
+    p.allow_bits = (a->flags & NRL_READOUT_MASK_BITS) ? 1u : 0u;
     p.slog = sample ? (float2*)(a->workspace + readout_parts_bytes(a->rows, a->V, a->d)) : nullptr;
     const bool extra = sample || a->allow_mask != 0;
     p.logits_out = (uint16_t*)a->logits_out;

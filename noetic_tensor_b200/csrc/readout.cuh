@@ -56,6 +56,7 @@ struct ReadoutParams {
     uint32_t w_is_vd;      // W given as [V, d] (K-major B) instead of [d, V] (N-major B)
     uint32_t round_bf16;   // fold the logits after rounding them to bf16 (what a bf16 logits tensor would hold)
     uint32_t greedy;       // the token is the row's first maximum: its index travels in the part's token-logit slot
+    uint32_t allow_bits;   // the allow-mask is one bit per token: u32 words, bit v mod 32 of word v / 32; allow_stride counts words
     float tau;             // temperature: every logit is divided by it (IEEE division, as tempered_logits does) before it is folded
     const int32_t* tokens; // [rows] or null
     float* parts;          // scratch [rows, nsplit, 4]
@@ -140,7 +141,7 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
     // EXTRA: the mask bytes of a whole tile inside the vocabulary, 16-byte aligned, are fetched one chunk ahead
     uint4 mq[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
     bool mask_fast = false;
-    if (EXTRA && p.allow && live) {
+    if (EXTRA && p.allow && !p.allow_bits && live) {
         const uint8_t* mp0 = p.allow + row * p.allow_stride + (uint64_t)t * kRoBN;
         mask_fast = (uint64_t)(t + 1) * kRoBN <= p.V && (reinterpret_cast<uintptr_t>(mp0) & 15u) == 0;
         if (mask_fast) {
@@ -161,7 +162,12 @@ __device__ __forceinline__ void readout_fold_tile(const ReadoutParams& p, uint32
             if (ROUND) v = round_through_bf16(v);
             z[i] = v;
         }
-        if (EXTRA && p.allow && live && col0 < p.V) {  // 32 mask bytes of this row: one sector
+        if (EXTRA && p.allow && p.allow_bits && live && col0 < p.V) {  // the 32 columns' bits are one word of this row
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.allow) + row * p.allow_stride + (col0 >> 5));
+#pragma unroll
+            for (int i = 0; i < 32; i++)
+                if (!((word >> i) & 1u)) z[i] = -FLT_MAX;
+        } else if (EXTRA && p.allow && live && col0 < p.V) {  // 32 mask bytes of this row: one sector
             const uint8_t* mp = p.allow + row * p.allow_stride + col0;
             if (mask_fast) {
                 // this chunk's bytes were loaded one chunk ahead; the next chunk's go out now
@@ -910,7 +916,11 @@ __global__ void __launch_bounds__(256) readout_draw_kernel(ReadoutParams p, cons
         if (p.round_bf16) { z0 = round_through_bf16(z0); z1 = round_through_bf16(z1); }
         if (p.tau != 1.f) { z0 = __fdiv_rn(z0, p.tau); z1 = __fdiv_rn(z1, p.tau); }
         bool ok0 = ca < p.V, ok1 = ca + 1 < p.V;
-        if (p.allow) {
+        if (p.allow && p.allow_bits) {
+            const uint32_t word = __ldg(reinterpret_cast<const uint32_t*>(p.allow) + row * p.allow_stride + (ca >> 5));
+            ok0 = ok0 && ((word >> (ca & 31u)) & 1u);
+            ok1 = ok1 && ((word >> ((ca + 1) & 31u)) & 1u);
+        } else if (p.allow) {
             const uint8_t* mp = p.allow + row * p.allow_stride;
             ok0 = ok0 && mp[ca] != 0;
             ok1 = ok1 && mp[ca + 1] != 0;

@@ -598,13 +598,21 @@ inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& wei
     std::memset(&a, 0, sizeof a);
     a.struct_size = sizeof a;
     a.flags = greedy ? NRL_READOUT_GREEDY : NRL_READOUT_SAMPLE;
-    if (vocab_mask) {
-        if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("head_sample_categorical: a U8 allow-mask");
+    uint32_t mask_flag = 0u;
+    if (vocab_mask && vocab_mask->dtype() == DType::I32) {  // one bit per token: [.., W] or [1, W] words, W ≥ ceil(V / 32)
+        const uint64_t words = vocab_mask->shape().back(), n = numel(vocab_mask->shape());
+        if (words < (V + 31) / 32 || (n != words && n != rows * words)) throw std::runtime_error("rl: mask shape");
+        a.allow_mask = vocab_mask->dev();
+        a.allow_row_stride = n == words ? 0 : words;
+        mask_flag = NRL_READOUT_MASK_BITS;
+    } else if (vocab_mask) {
+        if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("head_sample_categorical: a U8 allow-mask or I32 words of bits");
         const uint64_t n = numel(vocab_mask->shape());
         if (n != V && n != rows * V) throw std::runtime_error("rl: mask shape");
         a.allow_mask = vocab_mask->dev();
         a.allow_row_stride = n == V ? 0 : V;
     }
+    a.flags |= mask_flag;
     Tensor tok = Tensor::empty(Shape{(size_t)rows}, DType::I32, hidden.device());
     Tensor lp = Tensor::empty(lead, DType::F32, hidden.device());
     Tensor status = Tensor::empty(Shape{(size_t)rows}, DType::U8, hidden.device());

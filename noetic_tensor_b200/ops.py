@@ -421,14 +421,15 @@ class Readout:
     __slots__ = ("logp", "entropy", "rowstats", "status", "logits", "tokens")
 
 
-def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None, greedy=False, temperature=1.0):
+def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round_bf16=False, want_logits=False, workspace=None, one_cta=False, uniforms=None, allow=None, greedy=False, temperature=1.0, allow_bits=None):
     """Row statistics of logits = hidden [rows, d] · W without writing the logits (nrl_readout_fwd):
     `hidden` bf16 [rows, d]; `weights` bf16 [d, V] (the reference's Linear layout) or, with
     `weights_are_vd`, [V, d]; `tokens` int32 [rows] (given tokens) for `logp`. `round_bf16` folds
     the logits rounded to bf16; `want_logits` also returns those bf16 logits [rows, V]. With
     `uniforms` (float32 [rows]) the tokens are drawn by inverse CDF instead of given (`tokens` of the
     result), with `greedy` they are each row's first maximum; `allow` is a uint8 allow-mask [rows, V]
-    or [1, V]; `temperature` divides the logits before they are folded (the returned `logits` are the
+    or [1, V], `allow_bits` the same as int32 words [rows, ceil(V/32)] or [1, ceil(V/32)] (bit v of a row =
+    bit v mod 32 of word v / 32); `temperature` divides the logits before they are folded (the returned `logits` are the
     undivided ones)."""
     dev = hidden.device
     if dev.type != "cuda":
@@ -459,9 +460,17 @@ def readout_forward(hidden, weights, *, tokens=None, weights_are_vd=False, round
     if tokens is not None:
         a.tokens = _p(tokens)
         out.logp = torch.empty(rows, dtype=torch.float32, device=dev)
+    if allow is not None and allow_bits is not None:
+        raise ValueError("give `allow` or `allow_bits`, not both")
     if allow is not None:
         allow, a.allow_row_stride, _, _ = _masks(V, rows, allow, None, dev)
         a.allow_mask = _p(allow)
+    if allow_bits is not None:
+        words = (V + 31) // 32
+        if allow_bits.dtype != torch.int32 or allow_bits.dim() != 2 or allow_bits.shape[0] not in (1, rows) or allow_bits.shape[1] < words or allow_bits.device != dev or not allow_bits.is_contiguous():
+            raise ValueError("allow_bits: contiguous int32 [rows, >= ceil(V/32)] or [1, ...] on the logits' device")
+        a.allow_mask, a.allow_row_stride = _p(allow_bits), (0 if allow_bits.shape[0] == 1 else allow_bits.shape[1])
+        a.flags |= capi.READOUT_MASK_BITS
     out.entropy = torch.empty(rows, dtype=torch.float32, device=dev)
     out.rowstats = torch.empty(rows, 4, dtype=torch.float32, device=dev)
     out.status = torch.empty(rows, dtype=torch.uint8, device=dev)

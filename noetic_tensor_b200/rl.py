@@ -274,20 +274,23 @@ def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None, temperatu
     """`sample_categorical(head(x), temperature, mask, ·)` by inverse CDF against `uniforms` (one per
     position; None or temperature 0: the first maximum) without the logits in between: tokens [...]
     (int32), their log-probs and the per-position entropies (of the tempered distribution).
-    `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V]. Refuses a position with no allowed token
+    `vocab_mask`: a uint8/bool allow-mask [..., V] or [1, V], or int32 words of one bit per token
+    [..., ceil(V/32)] or [1, ceil(V/32)]. Refuses a position with no allowed token
     with the reference's message (src/nn/rl.rs:516-519)."""
     lead = hidden.shape[:-1]
     V = weight.shape[1]
-    allow = None
-    if vocab_mask is not None:
+    allow = bits = None
+    if vocab_mask is not None and vocab_mask.dtype == torch.int32:  # bit-packed: [..., ceil(V/32)] words
+        bits = vocab_mask.reshape(-1, vocab_mask.shape[-1]).contiguous()
+    elif vocab_mask is not None:
         allow = vocab_mask.reshape(-1, V)
         allow = (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous()
     x = hidden.reshape(-1, hidden.shape[-1]).contiguous()
     if not (temperature >= 0.0 and temperature == temperature and temperature != float("inf")):
         raise ValueError("sample_categorical: temperature (must be >= 0)")
     if uniforms is None or temperature == 0.0:
-        o = ops.readout_forward(x, weight, greedy=True, allow=allow)
+        o = ops.readout_forward(x, weight, greedy=True, allow=allow, allow_bits=bits)
     else:
-        o = ops.readout_forward(x, weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow, temperature=temperature)
+        o = ops.readout_forward(x, weight, uniforms=uniforms.reshape(-1).contiguous(), allow=allow, allow_bits=bits, temperature=temperature)
     ops.check_status(o.status)
     return o.tokens.reshape(lead), o.logp.reshape(lead), o.entropy.reshape(lead)

@@ -388,6 +388,11 @@ def test_head_functions_of_the_rl_module():
         close(lps.cpu().numpy(), torch.log_softmax(zt, -1).gather(-1, tk.long()[..., None])[..., 0].cpu().numpy(), "log-probs of drawn tokens", rel=5e-5, abs_=1e-4)
         lw = torch.log_softmax(zt, -1)
         close(en.cpu().numpy(), (-(p * torch.where(p > 0, lw, torch.zeros_like(lw))).sum(-1)).cpu().numpy(), "entropy of the tempered distribution", rel=5e-5, abs_=5e-6)
+    # the shared mask as int32 words of bits: the byte mask's draws
+    words = torch.from_numpy(np.packbits(shared.cpu().numpy().astype(np.uint8), axis=1, bitorder="little").view(np.int32)).to(dev())
+    tb, lb, eb = rl.head_sample_categorical(h, w, u, vocab_mask=words, temperature=0.8)
+    ta, la, ea = rl.head_sample_categorical(h, w, u, vocab_mask=shared, temperature=0.8)
+    assert torch.equal(ta, tb) and torch.equal(la.view(torch.int32), lb.view(torch.int32)) and torch.equal(ea.view(torch.int32), eb.view(torch.int32))
     tk0, lp0, _ = rl.head_sample_categorical(h, w, None, vocab_mask=shared)
     z0 = torch.where(shared.expand(S, B, T, V), z, torch.full_like(z, float("-inf")))
     assert ((z0.max(-1).values - z0.gather(-1, tk0.long()[..., None])[..., 0]) <= 1e-4).all()
@@ -395,3 +400,33 @@ def test_head_functions_of_the_rl_module():
     none[0, 0, 5] = False
     with pytest.raises(RuntimeError, match="position 5 has no allowed token"):
         rl.head_sample_categorical(h, w, u, vocab_mask=none)
+
+
+@pytest.mark.parametrize("rows,d,V", [(300, 4096, 128256), (1000, 512, 4104), (30000, 64, 1000)])
+def test_readout_bit_packed_masks(rows, d, V):
+    """NRL_READOUT_MASK_BITS: the allow-mask as one bit per token (what grammar engines emit), per row
+    and shared by all rows, padded word counts too: the byte mask's results bit for bit, for given
+    tokens, sampling and the first maximum."""
+    from noetic_tensor_b200 import ops
+
+    x, w, tok = make(rows, d, V, 29 * rows + V)
+    g = torch.Generator(device=dev())
+    g.manual_seed(rows + V)
+    u = torch.rand(rows, generator=g, device=dev())
+    for shared in (False, True):
+        n = 1 if shared else rows
+        allow = (torch.rand(n, V, generator=g, device=dev()) < 0.2).to(torch.uint8)
+        allow[:, V // 3] = 1
+        words = (V + 31) // 32 + (3 if shared else 0)  # a padded row stride is allowed
+        packed = np.packbits(np.pad(allow.cpu().numpy(), ((0, 0), (0, words * 32 - V))), axis=1, bitorder="little").view(np.int32)
+        bits = torch.from_numpy(packed).to(dev()).contiguous()
+        for kw in (dict(tokens=tok), dict(uniforms=u), dict(greedy=True)):
+            a = ops.readout_forward(x, w, allow=allow, temperature=0.9, **kw)
+            b = ops.readout_forward(x, w, allow_bits=bits, temperature=0.9, **kw)
+            assert torch.equal(a.status, b.status) and (a.status == 0).all()
+            if a.tokens is not None:
+                assert torch.equal(a.tokens, b.tokens), kw.keys()
+            for name in ("logp", "entropy", "rowstats"):
+                assert torch.equal(getattr(a, name).view(torch.int32), getattr(b, name).view(torch.int32)), (name, list(kw))
+    with pytest.raises(Exception):
+        ops.readout_forward(x, w, tokens=tok, allow_bits=bits[:, :2].contiguous())
