@@ -450,7 +450,7 @@ def run_extras(dev, peak):
         return ops.row_forward(lg, allow=am, uniforms=un)
 
     # These run at the power cap: the clock, and with it every figure, drops by about a tenth between the first
-    # second and the later ones. The modes are therefore timed in turn, three rounds over all of them, and each
+    # second and the later ones. The modes are therefore timed in turn, three passes over all of them, and each
     # mode's median is reported: one measured after another would favour whichever came first.
     modes = {"fused": lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws),
              "round": lambda: ops.readout_forward(hx, wt, tokens=tk, workspace=ws, round_bf16=True),
@@ -467,7 +467,7 @@ def run_extras(dev, peak):
     f2 = ops.row_forward(fo.logits, tokens=tk)
     res["readout_fused"] = {"what": "nrl_readout_fwd: logits = hidden [8192, 4096] x W [4096, 128256] (bf16, f32 accumulators in tensor memory) folded to log-prob of given tokens + entropy + row "
                                     "statistics without writing the logits; two_step = torch.matmul (cuBLAS, bf16 logits written) + nrl_row_fwd on them",
-                            "rows": rows, "d": d6, "V": V, "timing": "modes timed in turn, 3 rounds of 4 launches each, median per mode", "ms": t_fused, "ms_round_bf16": t_round, "TFLOPs": fl / t_fused / 1e9, "frac_of_sustained_bf16_peak": fl / t_fused / 1e9 / tf_sustained,
+                            "rows": rows, "d": d6, "V": V, "timing": "modes timed in turn, 3 passes of 4 launches each, median per mode", "ms": t_fused, "ms_round_bf16": t_round, "TFLOPs": fl / t_fused / 1e9, "frac_of_sustained_bf16_peak": fl / t_fused / 1e9 / tf_sustained,
                             "frac_of_burst_bf16_peak": fl / t_fused / 1e9 / tf_burst, "peak_kind": tf_kind, "cublas_product_alone_ms": t_mm, "cublas_TFLOPs": fl / t_mm / 1e9,
                             "two_step_ms": t_two, "speedup_vs_two_step": t_two / t_fused, "rows_per_s": rows / (t_fused * 1e-3),
                             "values_outside_tolerance_vs_row_fwd_on_its_logits": close(fo.logp, f2.logp) + close(fo.entropy, f2.entropy),
