@@ -546,7 +546,31 @@ inline Tensor token_log_probs(const Tensor& logits, const IntTensor& tokens) {
 // tokens [..]. Returns the log-probabilities [..] and, if asked, the per-position entropies.
 // Untracked: the backward of the fused form (d hidden, d weight) is not built; needs a
 // compute-capability-10 device (tcgen05). `round_bf16`: statistics of the logits rounded to bf16.
-inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, const IntTensor& tokens, Tensor* entropy = nullptr, bool round_bf16 = false) {
+namespace detail {
+// the allow-mask of a fused head call: U8 [.., V] or [1, V], or I32 words of one bit per token [.., W] or [1, W]
+inline void head_mask(nrl_readout_args& a, const Tensor* vocab_mask, uint64_t rows, uint64_t V) {
+    if (!vocab_mask) return;
+    if (vocab_mask->dtype() == DType::I32) {
+        const uint64_t words = vocab_mask->shape().back(), n = numel(vocab_mask->shape());
+        if (words < (V + 31) / 32 || (n != words && n != rows * words)) throw std::runtime_error("rl: mask shape");
+        a.allow_mask = vocab_mask->dev();
+        a.allow_row_stride = n == words ? 0 : words;
+        a.flags |= NRL_READOUT_MASK_BITS;
+        return;
+    }
+    if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("rl: a U8 allow-mask or I32 words of bits");
+    const uint64_t n = numel(vocab_mask->shape());
+    if (n != V && n != rows * V) throw std::runtime_error("rl: mask shape");
+    a.allow_mask = vocab_mask->dev();
+    a.allow_row_stride = n == V ? 0 : V;
+}
+}  // namespace detail
+
+// `vocab_mask` / `temperature`: the logits are the tempered ones (src/nn/rl.rs:475-486), what a rollout drawn by
+// head_sample_categorical under the same mask and temperature is scored with.
+inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, const IntTensor& tokens, Tensor* entropy = nullptr, bool round_bf16 = false, const Tensor* vocab_mask = nullptr,
+                                   double temperature = 1.0) {
+    if (!(temperature > 0.0 && std::isfinite(temperature))) throw std::runtime_error("tempered_logits: temperature must be > 0");
     if (hidden.dtype() != DType::BF16 || weight.dtype() != DType::BF16) throw std::runtime_error("head_token_log_probs: BF16 hidden states and weight");
     if (hidden.rank() < 1 || weight.rank() != 2 || weight.shape()[0] != hidden.shape().back()) throw std::runtime_error("head_token_log_probs: hidden [.., d], weight [d, V]");
     const Shape lead(hidden.shape().begin(), hidden.shape().end() - 1);
@@ -565,6 +589,8 @@ inline Tensor head_token_log_probs(const Tensor& hidden, const Tensor& weight, c
     std::memset(&a, 0, sizeof a);
     a.struct_size = sizeof a;
     a.flags = round_bf16 ? NRL_READOUT_ROUND_BF16 : 0u;
+    a.temperature = (float)temperature;
+    detail::head_mask(a, vocab_mask, rows, V);
     a.V = (uint32_t)V; a.d = (uint32_t)d; a.rows = rows;
     a.hidden = hidden.dev(); a.weights = weight.dev(); a.tokens = tok.dev();
     a.logp = logp.dev(); a.status = status.dev();
@@ -598,21 +624,7 @@ inline IntTensor head_sample_categorical(const Tensor& hidden, const Tensor& wei
     std::memset(&a, 0, sizeof a);
     a.struct_size = sizeof a;
     a.flags = greedy ? NRL_READOUT_GREEDY : NRL_READOUT_SAMPLE;
-    uint32_t mask_flag = 0u;
-    if (vocab_mask && vocab_mask->dtype() == DType::I32) {  // one bit per token: [.., W] or [1, W] words, W ≥ ceil(V / 32)
-        const uint64_t words = vocab_mask->shape().back(), n = numel(vocab_mask->shape());
-        if (words < (V + 31) / 32 || (n != words && n != rows * words)) throw std::runtime_error("rl: mask shape");
-        a.allow_mask = vocab_mask->dev();
-        a.allow_row_stride = n == words ? 0 : words;
-        mask_flag = NRL_READOUT_MASK_BITS;
-    } else if (vocab_mask) {
-        if (vocab_mask->dtype() != DType::U8) throw std::runtime_error("head_sample_categorical: a U8 allow-mask or I32 words of bits");
-        const uint64_t n = numel(vocab_mask->shape());
-        if (n != V && n != rows * V) throw std::runtime_error("rl: mask shape");
-        a.allow_mask = vocab_mask->dev();
-        a.allow_row_stride = n == V ? 0 : V;
-    }
-    a.flags |= mask_flag;
+    detail::head_mask(a, vocab_mask, rows, V);
     Tensor tok = Tensor::empty(Shape{(size_t)rows}, DType::I32, hidden.device());
     Tensor lp = Tensor::empty(lead, DType::F32, hidden.device());
     Tensor status = Tensor::empty(Shape{(size_t)rows}, DType::U8, hidden.device());

@@ -259,13 +259,28 @@ def categorical_entropy(logits, mask=None, reduction=TOKEN_MEAN):
     return _row_level("entropy", logits, None, mask, reduction)
 
 
-def head_token_log_probs(hidden, weight, tokens, round_bf16=False):
+def _vocab_mask_args(vocab_mask, V):
+    """(allow bytes, allow bits) for ops.readout_forward from a bool/uint8 mask [..., V] / [1, V] or
+    int32 words of one bit per token [..., ceil(V/32)] / [1, ceil(V/32)]."""
+    if vocab_mask is None:
+        return None, None
+    if vocab_mask.dtype == torch.int32:
+        return None, vocab_mask.reshape(-1, vocab_mask.shape[-1]).contiguous()
+    allow = vocab_mask.reshape(-1, V)
+    return (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous(), None
+
+
+def head_token_log_probs(hidden, weight, tokens, round_bf16=False, vocab_mask=None, temperature=1.0):
     """`token_log_probs(head(x), tokens)` and `categorical_entropy(head(x))` per position without the
     logits in between (src/nn/decoder.rs:270-279, then src/nn/rl.rs:134-141, 405-414): `hidden`
-    bf16 [..., d], `weight` bf16 [d, V] (the Linear's [in, out] layout), tokens [...]. Returns
-    (log-probs [...], entropies [...]). Untracked; needs a compute-capability-10 device."""
+    bf16 [..., d], `weight` bf16 [d, V] (the Linear's [in, out] layout), tokens [...]. With
+    `vocab_mask` / `temperature` the logits are the tempered ones (src/nn/rl.rs:475-486): what a
+    rollout drawn by `head_sample_categorical` under the same mask and temperature is scored with.
+    Returns (log-probs [...], entropies [...]). Untracked; needs a compute-capability-10 device."""
     lead = hidden.shape[:-1]
-    o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, tokens=tokens.reshape(-1).to(torch.int32).contiguous(), round_bf16=round_bf16)
+    allow, bits = _vocab_mask_args(vocab_mask, weight.shape[1])
+    o = ops.readout_forward(hidden.reshape(-1, hidden.shape[-1]).contiguous(), weight, tokens=tokens.reshape(-1).to(torch.int32).contiguous(), round_bf16=round_bf16, allow=allow, allow_bits=bits,
+                            temperature=temperature)
     ops.check_status(o.status)
     return o.logp.reshape(lead), o.entropy.reshape(lead)
 
@@ -279,12 +294,7 @@ def head_sample_categorical(hidden, weight, uniforms, vocab_mask=None, temperatu
     with the reference's message (src/nn/rl.rs:516-519)."""
     lead = hidden.shape[:-1]
     V = weight.shape[1]
-    allow = bits = None
-    if vocab_mask is not None and vocab_mask.dtype == torch.int32:  # bit-packed: [..., ceil(V/32)] words
-        bits = vocab_mask.reshape(-1, vocab_mask.shape[-1]).contiguous()
-    elif vocab_mask is not None:
-        allow = vocab_mask.reshape(-1, V)
-        allow = (allow.view(torch.uint8) if allow.dtype == torch.bool else allow).contiguous()
+    allow, bits = _vocab_mask_args(vocab_mask, V)
     x = hidden.reshape(-1, hidden.shape[-1]).contiguous()
     if not (temperature >= 0.0 and temperature == temperature and temperature != float("inf")):
         raise ValueError("sample_categorical: temperature (must be >= 0)")

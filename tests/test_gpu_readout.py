@@ -388,6 +388,11 @@ def test_head_functions_of_the_rl_module():
         close(lps.cpu().numpy(), torch.log_softmax(zt, -1).gather(-1, tk.long()[..., None])[..., 0].cpu().numpy(), "log-probs of drawn tokens", rel=5e-5, abs_=1e-4)
         lw = torch.log_softmax(zt, -1)
         close(en.cpu().numpy(), (-(p * torch.where(p > 0, lw, torch.zeros_like(lw))).sum(-1)).cpu().numpy(), "entropy of the tempered distribution", rel=5e-5, abs_=5e-6)
+    # scoring under the mask and temperature the tokens were drawn with gives the sampler's log-probs
+    tk_s, lp_s, en_s = rl.head_sample_categorical(h, w, u, vocab_mask=shared, temperature=0.8)
+    lp_g, en_g = rl.head_token_log_probs(h, w, tk_s, vocab_mask=shared, temperature=0.8)
+    close(lp_g.cpu().numpy(), lp_s.cpu().numpy(), "scored vs sampled log-probs", rel=1e-5, abs_=1e-4)
+    assert torch.equal(en_g.view(torch.int32), en_s.view(torch.int32))
     # the shared mask as int32 words of bits: the byte mask's draws
     words = torch.from_numpy(np.packbits(shared.cpu().numpy().astype(np.uint8), axis=1, bitorder="little").view(np.int32)).to(dev())
     tb, lb, eb = rl.head_sample_categorical(h, w, u, vocab_mask=words, temperature=0.8)
